@@ -1,0 +1,499 @@
+"""Headline benchmark: INT4 decode tokens/s of a Llama-3-8B-shaped model on B200(s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+N=1 workload: BASELINE config "Llama-3-8B-architecture INT4 decode" - hidden 4096,
+32 layers, 32 q / 8 kv heads, head_dim 128, intermediate 14336, vocab 128256,
+group 32, random init (std 0.02), fp32 KV cache pre-filled to a context of 4096,
+batch 1.  For N>1 (launched by torchrun, one rank per GPU) the same model is sharded
+tensor-parallel over the N GPUs ("strong" scaling: the work per token is fixed).
+
+One step = one decode step (all layers + lm_head) for `batch` sequences.
+ * value        : tokens/s with everything resident in HBM, K steps enqueued back to
+                  back (the device-side greedy generate loop), CUDA events on the
+                  decoder's stream, max over ranks.
+ * e2e          : the same metric through tb_decoder_step with HOST buffers: every
+                  step copies the token id in (pinned) and the [vocab] fp32 logits out.
+ * roofline     : the dominant kernel (fused RMSNorm + gate/up GEMV + SwiGLU), timed
+                  alone over the 32 layers' distinct weights (2.3 GB, far above L2).
+ * cpu_baseline : the CPU oracle's SIMD path on this box's host cores, on a bounded
+                  sample (2 of 32 layers + 1/8 of lm_head), scaled to a full step.
+`--impl reference` prints the CPU arm alone in the same JSON shape.
+
+Synthetic data throughout (no checkpoints or datasets are involved): weights
+N(0, 0.02) quantized with the reference's quantizer arithmetic, token ids uniform,
+KV pre-filled with seeded N(0,1) values.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+
+LLAMA8B = dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_layers=32, num_heads=32,
+               num_kv_heads=8, head_dim=128, group_size=32, rms_norm_eps=1e-6, rope_theta=500000.0)
+CONTEXT = 4096
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
+# ncu capture summarised under profiles/ (None until a capture exists for this kernel).
+DOMINANT_KERNEL_DRAM_TRAFFIC = None
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def weight_bytes(n, k, g):
+    return n * k // 2 + n * (k // g) * 4
+
+
+def step_weight_bytes(c, tp=1):
+    H, I, V, G = c["hidden_size"], c["intermediate_size"], c["vocab_size"], c["group_size"]
+    q_dim = c["num_heads"] * c["head_dim"]
+    tq = q_dim + 2 * c["num_kv_heads"] * c["head_dim"]
+    per_layer = weight_bytes(tq, H, G) + weight_bytes(H, q_dim, G) + 2 * weight_bytes(I, H, G) + weight_bytes(H, I, G) + 2 * H * 4
+    return c["num_layers"] * per_layer + weight_bytes(V, H, G) + H * 4
+
+
+def kv_bytes_per_seq(c, ctx):
+    return c["num_layers"] * 2 * c["num_kv_heads"] * ctx * c["head_dim"] * 4
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons during the timed region (read-only NVML)."""
+
+    REASONS = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+               0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+               0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)))
+                mask = int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------- CPU arm
+def cpu_decode_sample(c, ctx, threads=None, seed=0, reps=3):
+    """Times the CPU oracle (the reference's SIMD path restated in C) on a bounded
+    sample of the Llama-3-8B step and scales it to a full step.  Returns a dict."""
+    from oracle import oracle as o
+
+    if threads:
+        o.set_threads(threads)
+    rng = np.random.default_rng(seed)
+    H, I, G = c["hidden_size"], c["intermediate_size"], c["group_size"]
+    nh, nkv, hd = c["num_heads"], c["num_kv_heads"], c["head_dim"]
+    n_layers, lm_frac = 2, 8
+    small = dict(c, num_layers=n_layers, vocab_size=64, max_seq_len=ctx)
+
+    def qlin(n, k):
+        w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+        return o.quantize_int4_grouped(w, G)
+
+    layers = []
+    for _ in range(n_layers):
+        lw = {"input_norm_w": np.ones(H, np.float32), "post_norm_w": np.ones(H, np.float32), "qkv_b": None}
+        lw["qkv_w"], lw["qkv_s"] = qlin((nh + 2 * nkv) * hd, H)
+        lw["o_w"], lw["o_s"] = qlin(H, nh * hd)
+        lw["gate_w"], lw["gate_s"] = qlin(I, H)
+        lw["up_w"], lw["up_s"] = qlin(I, H)
+        lw["down_w"], lw["down_s"] = qlin(H, I)
+        layers.append(lw)
+    embed = rng.standard_normal((64, H), dtype=np.float32) * np.float32(0.02)
+    lm_w, lm_s = qlin(64, H)
+    dec = o.OracleDecoder(small, embed, layers, np.ones(H, np.float32), lm_w, lm_s)
+    for l in range(n_layers):  # context pre-filled with seeded values
+        k, v = dec.kv_cache(l)
+        k[:, : ctx - 1] = rng.standard_normal((nkv, ctx - 1, hd), dtype=np.float32) * np.float32(0.5)
+        v[:, : ctx - 1] = rng.standard_normal((nkv, ctx - 1, hd), dtype=np.float32)
+    dec.set_kv_len(ctx - 1)
+    v_s = c["vocab_size"] // lm_frac
+    hw, hs = qlin(v_s, H)
+    x = rng.standard_normal(H, dtype=np.float32)
+    dec.step(3, ctx - 1)  # warm-up
+    o.gemm_w4a32_grouped(x, hw, hs, None, G)
+    t_layers, t_head = [], []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        dec.step(5, ctx - 1)
+        t_layers.append(time.perf_counter() - t0)
+        t0 = time.perf_counter()
+        o.gemm_w4a32_grouped(x, hw, hs, None, G)
+        t_head.append(time.perf_counter() - t0)
+    step_s = min(t_layers) * (c["num_layers"] / n_layers) + min(t_head) * lm_frac
+    return {
+        "value": 1.0 / step_s, "unit": "tokens/s", "cores": o.get_threads(), "kind": "port",
+        "tier": o.TIER_NAMES.get(o.best_tier(), "?"),
+        "sample": (f"{n_layers} of {c['num_layers']} layers at full width with a {ctx}-token fp32 KV cache + 1/{lm_frac} "
+                   f"of lm_head, best of {reps}; scaled linearly to a full step ({step_s * 1e3:.1f} ms/step)"),
+        "ms_per_step": step_s * 1e3,
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    c = dict(LLAMA8B)
+    t0 = time.perf_counter()
+    best = None
+    for _ in range(max(1, min(args.steps, 2))):
+        r = cpu_decode_sample(c, CONTEXT, reps=max(1, min(args.warmup, 2)) + 1)
+        if best is None or r["value"] > best["value"]:
+            best = r
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": best["value"] * args.batch / args.batch,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": workload_config(c, 1, args.gpus),
+        "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample", "tier")},
+        "e2e": {"value": best["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+        "note": "CPU restatement of the reference's SIMD path (the Rust reference cannot be built here); batch 1",
+    }
+    print(json.dumps(line))
+
+
+def workload_config(c, batch, n_gpus):
+    return {
+        "workload": f"llama-3-8b-shaped INT4 (group {c['group_size']}) W4A32 decode, batch {batch}, fp32 KV at context {CONTEXT}",
+        "hidden": c["hidden_size"], "layers": c["num_layers"], "heads": f"{c['num_heads']}q/{c['num_kv_heads']}kv",
+        "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
+        "batch": batch, "context": CONTEXT, "parallelism": f"tp{n_gpus}",
+        "l2": "per-step working set (4.7 GB weights + 1.07 GB KV per sequence) exceeds the 126 MB L2; no flush needed",
+    }
+
+
+# ----------------------------------------------------------------- GPU arm
+def build_model(torch, tb, c, device, tp, rank, seed=1234):
+    """Random-init Llama-shaped weights generated and quantized on the GPU; under
+    tensor parallelism every rank generates the same full matrix and keeps its shard."""
+    gen = torch.Generator(device).manual_seed(seed)
+    H, I, V, G = c["hidden_size"], c["intermediate_size"], c["vocab_size"], c["group_size"]
+    nh, nkv, hd = c["num_heads"], c["num_kv_heads"], c["head_dim"]
+    q_dim, kv_dim = nh * hd, nkv * hd
+
+    def qlin(n, k):
+        w = torch.randn(n, k, device=device, generator=gen) * 0.02
+        return tb.quantize_weight_int4_grouped(w, group_size=G)
+
+    def rows(p, s, r0, n):
+        return p[r0:r0 + n].contiguous(), s[r0:r0 + n].contiguous()
+
+    def cols(p, s, c0, n):
+        return p[:, c0 // 2:(c0 + n) // 2].contiguous(), s[:, c0 // G:(c0 + n) // G].contiguous()
+
+    layers = []
+    for _ in range(c["num_layers"]):
+        qkv_p, qkv_s = qlin(q_dim + 2 * kv_dim, H)
+        o_p, o_s = qlin(H, q_dim)
+        g_p, g_s = qlin(I, H)
+        u_p, u_s = qlin(I, H)
+        d_p, d_s = qlin(H, I)
+        if tp > 1:
+            ql, kl, il = q_dim // tp, kv_dim // tp, I // tp
+            idx = torch.cat([torch.arange(rank * ql, (rank + 1) * ql), q_dim + torch.arange(rank * kl, (rank + 1) * kl),
+                             q_dim + kv_dim + torch.arange(rank * kl, (rank + 1) * kl)]).to(device)
+            qkv_p, qkv_s = qkv_p[idx].contiguous(), qkv_s[idx].contiguous()
+            o_p, o_s = cols(o_p, o_s, rank * ql, ql)
+            g_p, g_s = rows(g_p, g_s, rank * il, il)
+            u_p, u_s = rows(u_p, u_s, rank * il, il)
+            d_p, d_s = cols(d_p, d_s, rank * il, il)
+        ones = torch.ones(H, device=device)
+        layers.append([ones, qkv_p, qkv_s, o_p, o_s, ones, g_p, g_s, u_p, u_s, d_p, d_s])
+    embed = torch.randn(V, H, device=device, generator=gen) * 0.02
+    lm_p, lm_s = qlin(V, H)
+    if tp > 1:
+        lm_p, lm_s = rows(lm_p, lm_s, rank * (V // tp), V // tp)
+    return embed, layers, torch.ones(H, device=device), lm_p, lm_s
+
+
+def prefill_kv(torch, dec, c, device, ctx, batch, tp, rank, seed=99):
+    gen = torch.Generator(device).manual_seed(seed)
+    nkv_l = c["num_kv_heads"] // tp
+    for b in range(batch):
+        ks, vs = [], []
+        for _ in range(c["num_layers"]):
+            k = torch.randn(c["num_kv_heads"], ctx, c["head_dim"], device=device, generator=gen) * 0.5
+            v = torch.randn(c["num_kv_heads"], ctx, c["head_dim"], device=device, generator=gen)
+            ks.append(k[rank * nkv_l:(rank + 1) * nkv_l].contiguous())
+            vs.append(v[rank * nkv_l:(rank + 1) * nkv_l].contiguous())
+        dec.copy_kv_cache_from_tensors(ks, vs, ctx, seq=b)
+
+
+def time_dominant_kernel(torch, tb, c, layers, device, tp, passes=5):
+    """gate/up GEMV + SwiGLU alone, over all layers' weights, CUDA events on the launch stream."""
+    H, G = c["hidden_size"], c["group_size"]
+    I_l = c["intermediate_size"] // tp
+    x = torch.randn(1, H, device=device)
+    h = torch.empty(1, I_l, device=device)
+    L = tb.lib()
+    st = torch.cuda.current_stream(device)
+
+    def one_pass():
+        for lw in layers:
+            rc = L.tb_swiglu_gemv_w4a32(x.data_ptr(), lw[6].data_ptr(), lw[7].data_ptr(), None, lw[8].data_ptr(),
+                                        lw[9].data_ptr(), None, h.data_ptr(), 1, I_l, H, G, st.cuda_stream)
+            assert rc == 0, tb.last_error()
+
+    for _ in range(3):
+        one_pass()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    e0.record(st)
+    for _ in range(passes):
+        one_pass()
+    e1.record(st)
+    torch.cuda.synchronize(device)
+    launches = passes * len(layers)
+    sec = e0.elapsed_time(e1) * 1e-3 / launches
+    alg = 2 * weight_bytes(I_l, H, G) + H * 4 + I_l * 4
+    return alg, sec, launches
+
+
+def time_c1_gemv(torch, tb, device, copies=64, passes=5):
+    """BASELINE config 1: a single 4096x4096 group-32 GEMV, rotating over `copies` distinct
+    weight copies (672 MB, > 5x L2) so every launch streams from HBM."""
+    n = k = 4096
+    g = 32
+    gen = torch.Generator(device).manual_seed(7)
+    ws = []
+    for _ in range(copies):
+        w = torch.randn(n, k, device=device, generator=gen) * 0.02
+        ws.append(tb.quantize_weight_int4_grouped(w, group_size=g))
+    x = torch.randn(1, k, device=device, generator=gen)
+    out = torch.empty(1, n, device=device)
+    L = tb.lib()
+    st = torch.cuda.current_stream(device)
+
+    def one_pass():
+        for p, s in ws:
+            rc = L.tb_gemv_w4a32_grouped(x.data_ptr(), p.data_ptr(), s.data_ptr(), None, out.data_ptr(), n, k, g, st.cuda_stream)
+            assert rc == 0, tb.last_error()
+
+    for _ in range(3):
+        one_pass()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    e0.record(st)
+    for _ in range(passes):
+        one_pass()
+    e1.record(st)
+    torch.cuda.synchronize(device)
+    sec = e0.elapsed_time(e1) * 1e-3 / (passes * copies)
+    alg = weight_bytes(n, k, g) + k * 4 + n * 4
+    return alg, sec
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    tp = world
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if tp > 1:
+        dist.init_process_group("nccl", device_id=device)
+    import torchburn_b200 as tb
+
+    c = dict(LLAMA8B)
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    max_seq = CONTEXT + 64 * ((K + W + 63) // 64) + 64
+    embed, layers, fnorm, lm_p, lm_s = build_model(torch, tb, c, device, tp, rank)
+    dec = tb.B200QwenDecoder(embed, layers, fnorm, lm_p, lm_s, c["num_layers"], c["hidden_size"],
+                             c["intermediate_size"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["group_size"],
+                             c["rms_norm_eps"], max_seq, c["rope_theta"], max_batch=B, tp_size=tp, tp_rank=rank,
+                             vocab_size=c["vocab_size"], nccl_only=args.nccl_only)
+    if tp > 1:
+        from torchburn_b200.tp import init_tensor_parallel
+
+        init_tensor_parallel(dec, dist, device)
+    prefill_kv(torch, dec, c, device, CONTEXT, B, tp, rank)
+    stream = torch.cuda.ExternalStream(lib_stream(tb, dec), device=device)
+    L = tb.lib()
+    import ctypes as C
+
+    def barrier():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---- device-resident: greedy generate loop, K steps enqueued back to back ----
+    out_tokens = np.empty(max(K, W), np.int64)
+
+    def generate(first, start, n):
+        if B == 1:
+            tb._lib.check(L.tb_decoder_generate_greedy(dec.handle, first, start, n, out_tokens.ctypes.data))
+        else:
+            toks = np.full(B, first, np.int64)
+            for i in range(n):
+                offs = np.full(B, start + i, np.int64)
+                tb._lib.check(L.tb_decoder_step_batch(dec.handle, toks.ctypes.data, offs.ctypes.data, B, None))
+
+    generate(11, CONTEXT, W)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record(stream)
+        generate(12, CONTEXT + W, K)
+        e1.record(stream)
+        barrier()
+    ms = e0.elapsed_time(e1)
+    if tp > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / K
+    value = B * 1e3 / ms_per_step
+
+    # ---- end to end through the C ABI with host buffers ----
+    logits_host = torch.empty(B, c["vocab_size"], dtype=torch.float32).pin_memory()
+    toks = np.full(B, 5, np.int64)
+    offs = np.full(B, CONTEXT, np.int64)
+
+    def e2e_step(i):
+        offs[:] = CONTEXT + (i % 32)
+        tb._lib.check(L.tb_decoder_step_batch(dec.handle, toks.ctypes.data, offs.ctypes.data, B, logits_host.data_ptr()))
+        toks[:] = int(logits_host[0, :1024].argmax())  # the host consumes the result
+
+    for i in range(W):
+        e2e_step(i)
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e2.record(stream)
+    for i in range(K):
+        e2e_step(i)
+    e3.record(stream)
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max(e2.elapsed_time(e3), 0.0)
+    if tp > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = B * 1e3 / (e2e_ms / K)
+
+    if rank != 0:
+        if tp > 1:
+            dist.barrier()
+        return
+    # ---- rank 0: roofline of the dominant kernel, config-1 GEMV, CPU baseline ----
+    peak, peak_kind = measured_peak()
+    alg, sec, _ = time_dominant_kernel(torch, tb, c, layers, device, tp)
+    achieved = alg / sec / 1e9
+    roofline = {"bound": "hbm", "kernel": "w4_gemv_kernel<M=1, SwiGLU> (gate/up GEMV + SwiGLU)", "achieved": achieved,
+                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": DOMINANT_KERNEL_DRAM_TRAFFIC,
+                "algorithmic_bytes_per_launch": alg, "us_per_launch": sec * 1e6}
+    c1_alg, c1_sec = time_c1_gemv(torch, tb, device)
+    wb = step_weight_bytes(c) / tp
+    kvb = kv_bytes_per_seq(c, CONTEXT) / tp
+    step_s = ms_per_step * 1e-3
+    line = {
+        "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": tp, "steps": K, "warmup": W,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(c, B, tp),
+        "roofline": roofline,
+        "step_roofline": {
+            "weight_bytes_per_step_per_gpu": wb, "kv_bytes_per_step_per_gpu": kvb * B,
+            "weights_only_frac": wb / step_s / 1e9 / peak, "weights_plus_kv_frac": (wb + kvb * B) / step_s / 1e9 / peak,
+            "peak_kind": f"of {peak_kind}"},
+        "gemv_config1": {"shape": "4096x4096 group 32, M=1", "algorithmic_bytes": c1_alg, "us_per_launch": c1_sec * 1e6,
+                         "achieved_gbs": c1_alg / c1_sec / 1e9, "frac_of_measured": c1_alg / c1_sec / 1e9 / peak,
+                         "frac_of_nominal_8TBs": c1_alg / c1_sec / 1e9 / NOMINAL_HBM_GBS,
+                         "note": "64 rotating weight copies (672 MB) launched back to back"},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 16 * B, "d2h_bytes_per_step": 4 * B * c["vocab_size"],
+                "ms_per_step": e2e_ms / K, "wall_ms_per_step": wall_ms / K},
+        "gpu_launches": (dec.launches_per_step() + 1) * K,
+        "clocks": clocks.summary(),
+    }
+    if args.cpu_baseline:
+        line["cpu_baseline"] = {k: v for k, v in cpu_decode_sample(c, CONTEXT).items() if k != "ms_per_step"}
+    print(json.dumps(line))
+    if tp > 1:
+        dist.barrier()
+
+
+def lib_stream(tb, dec):
+    return tb.lib().tb_decoder_stream(dec.handle)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: plain ncclAllReduce instead of the fused kernel")
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,339 @@
+/*
+ * torchburn_b200 - C ABI of the B200 (sm_100a) implementation of torchburn's
+ * quantized decode hot path: the grouped INT4 W4A32 linear and the LLM decoder
+ * step built around it.
+ *
+ * Every entry point is plain C: pointers, sizes, an opaque handle, an integer
+ * status.  No C++ exception crosses this boundary.  Each declaration names the
+ * interface of the reference (kuntal-devrat/torchburn, paths relative to its
+ * source tree) that it stands in for.
+ *
+ * Memory spaces.  Weights are handed over once (host or device memory, stated
+ * by a tb_space argument) and copied into device memory owned by the handle,
+ * like RustQwenDecoder::new copies every weight into its own Vec
+ * (src/llm/decoder.rs:235-332).  Activations and results are host or device
+ * pointers as stated per call.  `stream` arguments are a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).
+ *
+ * Threading.  Stateless functions and tb_linear handles may be used from
+ * several host threads on distinct streams.  A tb_decoder is not re-entrant
+ * (the reference's decoder methods take &mut self).
+ *
+ * Errors.  Functions return TB_OK or a negative-free small status code;
+ * tb_last_error_string() gives the message of the calling thread's last
+ * failure.  There is no CPU fallback: without a usable CUDA device every
+ * compute entry point fails with TB_ERR_CUDA.
+ */
+#ifndef TORCHBURN_B200_H
+#define TORCHBURN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The library is built with hidden visibility; only this ABI is exported. */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef int32_t tb_status;
+enum {
+  TB_OK = 0,
+  TB_ERR_ARG = 1,         /* NULL pointer / bad enum: PyValueError in the reference */
+  TB_ERR_SHAPE = 2,       /* "TB_UNSUPPORTED:" shape errors, src/quantization/packed_v2.rs:566-596 */
+  TB_ERR_DTYPE = 3,       /* kept for ABI completeness; this ABI is typed */
+  TB_ERR_OOM = 4,         /* PyMemoryError, src/llm/decoder.rs:239-246 */
+  TB_ERR_CUDA = 5,        /* any CUDA runtime failure */
+  TB_ERR_NCCL = 6,
+  TB_ERR_TIMEOUT = 7,     /* a bounded device-side wait ran out */
+  TB_ERR_DEVICE_LOST = 8, /* sticky, src/wgpu/decode.rs:692-716 */
+  TB_ERR_UNSUPPORTED = 9
+};
+
+typedef enum tb_space { TB_HOST = 0, TB_DEVICE = 1 } tb_space;
+
+#define TB_ABI_VERSION 1
+
+int32_t tb_abi_version(void);
+/* Message of the calling thread's most recent failure ("" if none). */
+const char* tb_last_error_string(void);
+/* One-line JSON description of the current CUDA device (name, SM count, ...).
+ * Stands in for cpu_features_report, src/ffi/debug_ffi.rs:12-22. */
+tb_status tb_device_report(char* buf, size_t cap);
+
+/* ------------------------------------------------------------------------
+ * Raw kernel surface on DEVICE pointers: the counterpart of the pointer-level
+ * functions re-exported for benches and parity tests, src/kernels/mod.rs:16-25.
+ * All tensors are contiguous and row-major.
+ * ---------------------------------------------------------------------- */
+
+/* out[j] = sum_g scales[j,g] * sum_{i in g} x[i] * code(w[j,i]) + bias[j].
+ * x [k] f32, w [n, k/2] u8 (element i of a row in byte i/2, low nibble for
+ * even i, code = nibble - 8), scales [n, k/group_size] f32, bias [n] or NULL.
+ * Replaces gemv_w4a32_grouped, src/quantization/gemv.rs:1514-1684.
+ * group_size must be 32 or 64 and divide k (the reference's SIMD tiers make the
+ * same assumption, gemv.rs:1579-1600). */
+tb_status tb_gemv_w4a32_grouped(const float* x, const uint8_t* w, const float* scales,
+                                const float* bias, float* out, int64_t n, int64_t k,
+                                int32_t group_size, void* stream);
+
+/* x [m,k] -> out [m,n]; same arithmetic per row of x.
+ * Replaces gemm_w4a32_grouped, src/quantization/gemv.rs:1690-1725. */
+tb_status tb_gemm_w4a32_grouped(const float* x, const uint8_t* w, const float* scales,
+                                const float* bias, float* out, int64_t m, int64_t n, int64_t k,
+                                int32_t group_size, void* stream);
+
+/* h[r,j] = silu(gate_j(x_r)) * up_j(x_r), silu(g) = g / (1 + exp(-g)).
+ * Replaces the SwiGLU neuron loop, src/llm/decoder.rs:1280-1328 and
+ * src/quantization/gemv/swiglu.rs:205-289. gate_b/up_b may be NULL. */
+tb_status tb_swiglu_gemv_w4a32(const float* x, const uint8_t* gate_w, const float* gate_s,
+                               const float* gate_b, const uint8_t* up_w, const float* up_s,
+                               const float* up_b, float* h, int64_t m, int64_t n, int64_t k,
+                               int32_t group_size, void* stream);
+
+/* out[r,i] = x[r,i] * (1/sqrt(mean(x[r]^2) + eps)) * w[i], rows = m.
+ * Replaces fast_rms_norm, src/quantization/fused_ops.rs:1066-1117. */
+tb_status tb_fast_rms_norm(const float* x, const float* w, float* out, int64_t m, int64_t n,
+                           float eps, void* stream);
+
+/* Per (row, group): scale = max(absmax/7, 1e-8); code = clamp(rint(w/scale), -8, 7);
+ * byte j = (code[2j]+8) | (code[2j+1]+8) << 4.  All pointers DEVICE.
+ * Replaces quantize_weight_int4_grouped, python/torchburn/quantization.py:53-118
+ * (bit-exact, including round-half-to-even and fp32 division). */
+tb_status tb_quantize_weight_int4_grouped(const float* w, int64_t n, int64_t k,
+                                          int32_t group_size, uint8_t* packed, float* scales,
+                                          void* stream);
+
+/* GQA decode attention for one new position per sequence.
+ * qkv [b, (Hq+2Hkv)*d] f32 = [q | k | v] of the new token BEFORE RoPE.  The
+ * call rotates q and k (rotate-half, tables cos/sin [max_seq_len, d]), writes
+ * k,v into the caches at [seq, kv_h, offset, :] and computes, per q head h
+ * (kv_h = h / (Hq/Hkv)), softmax((q.k_t)/sqrt(d)) over t in [0, offset] times V.
+ * k_cache, v_cache: [b, Hkv, max_seq_len, d] f32.  offsets [b] int32 DEVICE.
+ * out [b, Hq*d].  `scratch` is device memory of tb_attention_scratch_bytes(),
+ * zero-filled once before its first use (the kernel leaves its counters zero).
+ * Replaces steps C-E of step_internal, src/llm/decoder.rs:1127-1213
+ * (src/shaders/rope_append.wgsl + attn_decode.wgsl on the wgpu path). */
+size_t tb_attention_scratch_bytes(int32_t batch, int32_t num_heads, int32_t num_kv_heads,
+                                  int32_t head_dim, int64_t max_seq_len);
+tb_status tb_attention_decode(const float* qkv, float* k_cache, float* v_cache,
+                              const float* cos_table, const float* sin_table,
+                              const int32_t* offsets, float* out, void* scratch, int32_t batch,
+                              int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                              int64_t max_seq_len, void* stream);
+
+/* Tuning hook: positions of the KV sequence handled per attention CTA (a power
+ * of two in [32, 256]; 0 = choose from the shape).  Process-wide; plays the role
+ * of TORCHBURN_ROWS_PER_WG, src/wgpu/backend.rs:428-437. */
+void tb_set_attention_chunk(int32_t positions);
+
+/* ------------------------------------------------------------------------
+ * QuantizedLinear (python/torchburn/quantization.py:756-869) as a handle.
+ * ---------------------------------------------------------------------- */
+typedef struct tb_linear tb_linear;
+
+/* qweight [out_features, in_features/2] u8, scales [out_features,
+ * in_features/group_size] f32, bias [out_features] or NULL; copied to device.
+ * Shape rules of w4a32_grouped_linear, src/quantization/packed_v2.rs:573-596. */
+tb_status tb_linear_create(tb_linear** out, const uint8_t* qweight, const float* scales,
+                           const float* bias, int64_t out_features, int64_t in_features,
+                           int32_t group_size, tb_space weight_space);
+void tb_linear_destroy(tb_linear* lin);
+/* QuantizedLinear.forward -> w4a32_grouped_linear (quantization.py:826-866,
+ * src/ffi/quantization_ffi.rs:56-85): x [m, in_features] -> out [m, out_features].
+ * io_space says where x and out live; host buffers are staged through pinned
+ * memory owned by the handle and the call returns after the result is in `out`. */
+tb_status tb_linear_forward(tb_linear* lin, const float* x, int64_t m, float* out,
+                            tb_space io_space, void* stream);
+/* Device views of the handle's operands (for the raw kernel surface). */
+tb_status tb_linear_device_ptrs(const tb_linear* lin, const uint8_t** qweight,
+                                const float** scales, const float** bias);
+
+/* fused_swiglu_mlp / fused_swiglu_mlp_batched: out = down(silu(gate(x)) * up(x)),
+ * x [m, hidden] -> out [m, hidden].  src/ffi/quantization_ffi.rs:203-218, 517-532;
+ * src/quantization/fused_ops.rs:138-424, 1267-1319. */
+tb_status tb_fused_swiglu_mlp(tb_linear* gate, tb_linear* up, tb_linear* down, const float* x,
+                              int64_t m, float* out, tb_space io_space, void* stream);
+
+/* fused_attention_step_w4a32 (src/ffi/quantization_ffi.rs:344-363,
+ * src/quantization/fused_ops.rs:891-1062): QKV GEMV -> RoPE with the given
+ * cos/sin (length head_dim, for this position) -> write K,V into the caller's
+ * caches [1, Hkv, max_seq_len, d] (DEVICE, mutated) -> attention -> O GEMV.
+ * x [hidden], cos/sin and out [hidden] in io_space. */
+tb_status tb_fused_attention_step(tb_linear* qkv, tb_linear* o, const float* x, float* k_cache,
+                                  float* v_cache, const float* cos_p, const float* sin_p,
+                                  int64_t offset, int32_t num_heads, int32_t num_kv_heads,
+                                  int32_t head_dim, int64_t max_seq_len, float* out,
+                                  tb_space io_space, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Decoder: RustQwenDecoder / WgpuQwenDecoder (src/llm/decoder.rs:111-171,
+ * src/wgpu/decode.rs:297-334) as a handle.
+ * ---------------------------------------------------------------------- */
+
+/* Constructor arguments, src/llm/decoder.rs:176-210 (defaults there:
+ * group_size 64, rms_norm_eps 1e-6, max_seq_len 2048, rope_theta 1e6).
+ * max_batch > 1 and tp_size > 1 have no counterpart in the reference. */
+typedef struct tb_model_config {
+  int64_t vocab_size;
+  int64_t hidden_size;
+  int64_t intermediate_size;
+  int32_t num_layers;
+  int32_t num_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;
+  int32_t group_size;
+  float rms_norm_eps;
+  int64_t max_seq_len;
+  double rope_theta;
+  int32_t max_batch; /* independent sequences decoded together; 0 means 1 */
+  int32_t tp_size;   /* tensor-parallel ranks; 0 means 1 */
+  int32_t tp_rank;
+  int32_t flags;     /* TB_DECODER_* */
+} tb_model_config;
+
+enum {
+  TB_DECODER_NO_GRAPH = 1,   /* launch kernels directly instead of replaying a CUDA graph */
+  TB_DECODER_NCCL_ONLY = 2   /* tensor parallel: use ncclAllReduce, not the fused peer-memory kernel */
+};
+
+/* Per-layer weights in the capsule order of create_rust_qwen_decoder,
+ * python/torchburn/quantization.py:603-621.  With tp_size > 1 these are the
+ * rank's shards (see tb_shard_*). */
+typedef struct tb_layer_weights {
+  const float* input_norm_w;
+  const uint8_t* qkv_w;
+  const float* qkv_s;
+  const uint8_t* o_w;
+  const float* o_s;
+  const float* post_norm_w;
+  const uint8_t* gate_w;
+  const float* gate_s;
+  const uint8_t* up_w;
+  const float* up_s;
+  const uint8_t* down_w;
+  const float* down_s;
+  const float* qkv_b; /* NULL when the architecture has no qkv bias */
+} tb_layer_weights;
+
+typedef struct tb_decoder tb_decoder;
+
+/* RustQwenDecoder::new, src/llm/decoder.rs:175-424: validates the dimensions
+ * (:214-233 -> TB_ERR_ARG), copies all weights to the device, builds the RoPE
+ * tables in float64 (:336-350), allocates zeroed KV caches [Hkv, max_seq_len, d]
+ * per layer and sequence (:353-359) and all scratch. */
+tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
+                            const float* embed_tokens, const tb_layer_weights* layers,
+                            const float* final_norm_w, const uint8_t* lm_head_w,
+                            const float* lm_head_s, tb_space weight_space);
+void tb_decoder_destroy(tb_decoder* dec);
+
+/* step(token_id, offset) -> logits, src/llm/decoder.rs:538-541 / decode_step
+ * :729-750.  logits_host [vocab] may be NULL (logits stay on the device; read
+ * them with tb_decoder_get_logits).  An out-of-range token or offset yields
+ * all-zero logits and TB_OK (decoder.rs:1066-1078). */
+tb_status tb_decoder_step(tb_decoder* dec, int64_t token_id, int64_t offset, float* logits_host);
+/* `batch` independent sequences advance one token each (sequence b uses KV
+ * slot b).  logits_host [batch, vocab] or NULL.  The reference batches by
+ * running one decoder object per sequence (python/torchburn/llm/speculative.py:293-379). */
+tb_status tb_decoder_step_batch(tb_decoder* dec, const int64_t* token_ids, const int64_t* offsets,
+                                int32_t batch, float* logits_host);
+/* prefill_tokens, src/llm/decoder.rs:431-447: sequential steps; *end_offset =
+ * start_offset + n; TB_ERR_ARG when it would pass max_seq_len. */
+tb_status tb_decoder_prefill_tokens(tb_decoder* dec, const int64_t* tokens, int64_t n,
+                                    int64_t start_offset, int64_t* end_offset);
+/* prefill, src/llm/decoder.rs:545-558: tokens at offsets 0..n-1, last logits out. */
+tb_status tb_decoder_prefill(tb_decoder* dec, const int64_t* tokens, int64_t n, float* logits_host);
+/* verify_tokens, src/llm/decoder.rs:565-582: logits_host [n, vocab]. */
+tb_status tb_decoder_verify_tokens(tb_decoder* dec, int64_t start_offset, const int64_t* tokens,
+                                   int64_t n, float* logits_host);
+/* reset_kv_cache, src/llm/decoder.rs:449-477 (clears the written prefix). */
+tb_status tb_decoder_reset_kv_cache(tb_decoder* dec);
+/* copy_kv_cache_from_tensors, src/llm/decoder.rs:479-523: per layer l <
+ * num_given, k[l]/v[l] are [Hkv, src_max_len, d] f32 in `space`; the first
+ * seq_len positions of every head are copied into sequence slot `seq`. */
+tb_status tb_decoder_copy_kv_cache_from(tb_decoder* dec, const float* const* k,
+                                        const float* const* v, int32_t num_given, int64_t seq_len,
+                                        int64_t src_max_len, int32_t seq, tb_space space);
+/* Reads back layer `layer`'s caches of sequence `seq`: [Hkv, max_seq_len, d] each. */
+tb_status tb_decoder_read_kv_cache(tb_decoder* dec, int32_t layer, int32_t seq, float* k_host,
+                                   float* v_host);
+/* kv_len, src/llm/decoder.rs:527. */
+int64_t tb_decoder_kv_len(const tb_decoder* dec);
+/* get_logits, src/llm/decoder.rs:532: logits of the last step, [batch, vocab]. */
+tb_status tb_decoder_get_logits(tb_decoder* dec, float* logits_host);
+/* Device pointer of the logits buffer [max_batch, vocab] (valid until destroy). */
+const float* tb_decoder_logits_device(const tb_decoder* dec);
+/* decode_and_sample with greedy settings (temperature <= 0 or top_k == 1),
+ * src/llm/decoder.rs:753-789, 895-906: argmax on the device, 8 bytes read back. */
+tb_status tb_decoder_decode_greedy(tb_decoder* dec, int64_t token_id, int64_t offset,
+                                   int64_t* next_token);
+/* generate_loop with greedy settings, src/llm/decoder.rs:791-832: feeds each
+ * argmax back as the next token without leaving the device; out_tokens [n_new]. */
+tb_status tb_decoder_generate_greedy(tb_decoder* dec, int64_t first_token, int64_t start_offset,
+                                     int64_t n_new, int64_t* out_tokens);
+/* Layer-0 intermediates of the last step by name, like debug_step_stages,
+ * src/wgpu/profiler.rs:75: "embed", "normed", "qkv", "attn", "x_attn", "h",
+ * "x_out".  Only recorded when the decoder was created with TB_DECODER_NO_GRAPH.
+ * Writes up to cap floats (sequence 0); *n = element count of the stage. */
+tb_status tb_decoder_debug_stage(tb_decoder* dec, const char* name, float* out_host, int64_t cap,
+                                 int64_t* n);
+/* profile_step_breakdown, src/wgpu/profiler.rs:14-73: CUDA-event milliseconds of
+ * one step split into (layers, lm_head, readback). */
+tb_status tb_decoder_step_timed(tb_decoder* dec, int64_t token_id, int64_t offset,
+                                float* logits_host, float ms_out[3]);
+/* is_device_lost / mark_device_lost, src/wgpu/decode.rs:692-699. */
+int32_t tb_decoder_is_device_lost(const tb_decoder* dec);
+void tb_decoder_mark_device_lost(tb_decoder* dec);
+/* Number of kernels one step launches (for accounting). */
+int32_t tb_decoder_launches_per_step(const tb_decoder* dec);
+/* The decoder's CUDA stream (cudaStream_t as void*). */
+void* tb_decoder_stream(const tb_decoder* dec);
+
+/* ------------------------------------------------------------------------
+ * Tensor parallelism over one NVLink/NVSwitch box.  No counterpart in the
+ * reference (it has no multi-device code); the layout is Megatron style:
+ * QKV and gate/up split by output rows (whole heads per rank), o_proj and down
+ * split by input columns, one all-reduce of [batch, hidden] after each.
+ * ---------------------------------------------------------------------- */
+
+/* Host-side shard helpers (pure byte slicing; no GPU needed).
+ * Rows [row0, row0+rows) of a packed matrix / its scales. */
+tb_status tb_shard_rows(const uint8_t* packed, const float* scales, int64_t n, int64_t k,
+                        int32_t group_size, int64_t row0, int64_t rows, uint8_t* packed_out,
+                        float* scales_out);
+/* Input columns [col0, col0+cols) of every row; col0 and cols must be
+ * multiples of group_size. */
+tb_status tb_shard_cols(const uint8_t* packed, const float* scales, int64_t n, int64_t k,
+                        int32_t group_size, int64_t col0, int64_t cols, uint8_t* packed_out,
+                        float* scales_out);
+/* Rank `rank` of `size`'s slice of a fused [q;k;v] projection (whole heads):
+ * output rows [q heads of the rank | k heads | v heads].  bias/bias_out may be NULL. */
+tb_status tb_shard_qkv(const uint8_t* packed, const float* scales, const float* bias,
+                       int64_t hidden, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                       int32_t group_size, int32_t rank, int32_t size, uint8_t* packed_out,
+                       float* scales_out, float* bias_out);
+
+/* 128-byte NCCL unique id for tb_decoder_tp_init (rank 0 makes it, the caller
+ * distributes it by any means). */
+tb_status tb_tp_unique_id(uint8_t id[128]);
+/* Joins the decoder (created with tp_size > 1) to its communicator.  Collective:
+ * every rank calls it.  peer_exchange, when not NULL, is a callback the library
+ * uses to all-gather `bytes` bytes per rank among the ranks (the caller's own
+ * transport, e.g. torch.distributed); it enables the fused peer-memory
+ * all-reduce.  Without it every all-reduce is ncclAllReduce. */
+typedef int32_t (*tb_allgather_fn)(void* user, const void* send, void* recv, size_t bytes);
+tb_status tb_decoder_tp_init(tb_decoder* dec, const uint8_t id[128], tb_allgather_fn allgather,
+                             void* user);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TORCHBURN_B200_H */

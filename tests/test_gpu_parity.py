@@ -1,0 +1,551 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle
+on the same seeded inputs.  Integer work (quantizer codes, nibble unpacking,
+cache slots) must match bit for bit; fp32 results within 1e-4 per stage and
+1e-3 on final logits, on the reference's metric max|a-e| / max|e|."""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import GOLDEN, load_decoder_golden, max_rel_err, synth_model
+
+pytestmark = pytest.mark.gpu
+
+STAGE_TOL = 1e-4   # per layer / stage
+LOGIT_TOL = 1e-3   # final logits
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("no CUDA device: GPU tests need a B200")
+    return torch
+
+
+@pytest.fixture(scope="module")
+def tb(torch):
+    import torchburn_b200 as tb
+
+    rep = tb.device_report()
+    assert rep["built_for"] == "sm_100a"
+    return tb
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+# ------------------------------------------------------------------ quantizer
+def test_quantizer_bit_exact_vs_reference_golden(torch, tb):
+    z = np.load(os.path.join(GOLDEN, "quantizer_golden.npz"))
+    for name in sorted({f.split("__")[0] for f in z.files}):
+        w, g = z[f"{name}__w"], int(z[f"{name}__g"])
+        if name == "huge_g32":
+            continue  # 1e30 / 3.4e38 inputs: covered against the oracle below
+        packed, scales = tb.quantize_weight_int4_grouped(dev(torch, w), group_size=g)
+        assert np.array_equal(packed.cpu().numpy(), z[f"{name}__packed"]), name
+        assert np.array_equal(scales.cpu().numpy().view(np.uint32), z[f"{name}__scales"].view(np.uint32)), name
+
+
+@pytest.mark.parametrize("g", [32, 64, 128])
+def test_quantizer_bit_exact_vs_oracle(torch, tb, oracle, g):
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((300, 1024)) * 0.02).astype(np.float32)
+    w[3, :64] = 0.0
+    w[7, 5] = 1e30
+    packed, scales = tb.quantize_weight_int4_grouped(dev(torch, w), group_size=g)
+    ep, es = oracle.quantize_int4_grouped(w, g)
+    assert np.array_equal(packed.cpu().numpy(), ep)
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), es.view(np.uint32))
+
+
+def test_quantizer_errors(torch, tb):
+    with pytest.raises(ValueError):
+        tb.quantize_weight_int4_grouped(torch.zeros(4, 48), group_size=32)
+    with pytest.raises(ValueError):
+        tb.quantize_weight_int4_grouped(torch.zeros(4), group_size=32)
+
+
+# --------------------------------------------------------- nibble unpacking
+@pytest.mark.parametrize("g", [32, 64])
+def test_unpack_every_byte_value_exact(torch, tb, g):
+    # scales = 1 and one-hot x: the output IS the integer code.  Row r holds byte value r
+    # everywhere, so even positions read the low nibble and odd positions the high nibble.
+    k = 128
+    packed = np.repeat(np.arange(256, dtype=np.uint8)[:, None], k // 2, axis=1)
+    scales = np.ones((256, k // g), np.float32)
+    for pos in (0, 1, 6, 7, 37, 64, 127):
+        x = np.zeros((1, k), np.float32)
+        x[0, pos] = 1.0
+        out = tb.w4a32_grouped_linear(dev(torch, x), dev(torch, packed), dev(torch, scales), None, g).cpu().numpy()[0]
+        b = np.arange(256)
+        want = ((b & 15) - 8) if pos % 2 == 0 else ((b >> 4) - 8)
+        assert np.array_equal(out, want.astype(np.float32)), pos
+
+
+def test_scale_indexing_exact(torch, tb):
+    # codes all +1 (nibble 9), x one-hot at i: out[j] = scales[j, i // g] exactly
+    n, k, g = 40, 256, 32
+    packed = np.full((n, k // 2), 0x99, np.uint8)
+    rng = np.random.default_rng(1)
+    scales = rng.random((n, k // g), dtype=np.float32)
+    for i in (0, 31, 32, 100, 255):
+        x = np.zeros((1, k), np.float32)
+        x[0, i] = 1.0
+        out = tb.w4a32_grouped_linear(dev(torch, x), dev(torch, packed), dev(torch, scales), None, g).cpu().numpy()[0]
+        assert np.array_equal(out, scales[:, i // g])
+
+
+# ------------------------------------------------------------- GEMV / GEMM
+def _linear_case(rng, n, k, g, m, bias):
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32) if bias else None
+    return w, x, b
+
+
+@pytest.mark.parametrize("n,k,g,m,bias", [
+    (4096, 4096, 32, 1, False),   # config 1
+    (4096, 4096, 64, 1, False),   # config 1 at the reference's default group size
+    (2688, 896, 32, 1, True),     # Qwen qkv with bias
+    (896, 4864, 32, 1, False),    # Qwen down
+    (1000, 1024, 32, 1, True),    # ragged N
+    (7, 64, 32, 1, False), (1, 32, 32, 1, False), (33, 2048, 128, 1, False),
+    (1024, 4096, 32, 2, True), (1024, 4096, 64, 3, False), (515, 896, 32, 4, True),
+    (512, 14336, 32, 8, False), (640, 1024, 32, 16, True), (300, 512, 64, 19, False),
+])
+def test_linear_matches_oracle(torch, tb, oracle, n, k, g, m, bias):
+    rng = np.random.default_rng(n * 7 + k + g + m)
+    w, x, b = _linear_case(rng, n, k, g, m, bias)
+    packed, scales = oracle.quantize_int4_grouped(w, g)
+    out = tb.w4a32_grouped_linear(dev(torch, x), dev(torch, packed), dev(torch, scales),
+                                  dev(torch, b) if bias else None, g).cpu().numpy()
+    want = oracle.gemm_w4a32_grouped(x, packed, scales, b, g)
+    exact = oracle.gemm_w4a32_f64(x, packed, scales, b, g)
+    assert out.shape == (m, n)
+    assert max_rel_err(out, want) < STAGE_TOL
+    # and no further from the float64 result than the reference's own fp32 kernel is (x4 slack)
+    assert max_rel_err(out, exact) <= max(4 * max_rel_err(want, exact), 2e-6)
+
+
+def test_linear_int4_rs_known_answer(torch, tb, oracle):
+    # tests/parity/int4.rs:172-215 restated for the CUDA path (n=64, k=896, g=64)
+    from helpers import rust_test_quantize_grouped
+
+    n, k, g = 64, 896, 64
+    x = (np.sin(np.arange(k, dtype=np.float32) * np.float32(0.13)) * 2).astype(np.float32)
+    w = (np.cos(np.arange(n * k, dtype=np.float32) * np.float32(0.29)) * np.float32(1.5)).astype(np.float32)
+    packed, scales = rust_test_quantize_grouped(w, k, g)
+    out = tb.w4a32_grouped_linear(dev(torch, x[None]), dev(torch, packed), dev(torch, scales), None, g).cpu().numpy()[0]
+    assert max_rel_err(out, oracle.gemm_w4a32_f64(x, packed, scales, None, g)) < 1e-3
+
+
+def test_linear_config2_shapes_and_linearity(torch, tb, oracle):
+    # BASELINE config 2 (Llama-3-8B MLP shapes).  M=1 and 4 against the oracle on the first
+    # 2048 rows; the full sizes through linearity: W(a*x1 + x2) = a*W x1 + W x2.
+    rng = np.random.default_rng(2)
+    for (k, n) in [(4096, 14336), (14336, 4096)]:
+        w = torch.randn(n, k, device="cuda", generator=torch.Generator("cuda").manual_seed(k)) * 0.02
+        packed, scales = tb.quantize_weight_int4_grouped(w, group_size=32)
+        p_h, s_h = packed[:2048].cpu().numpy(), scales[:2048].cpu().numpy()
+        for m in (1, 4, 16, 64):
+            x = rng.standard_normal((m, k)).astype(np.float32)
+            out = tb.w4a32_grouped_linear(dev(torch, x), packed, scales, None, 32)
+            assert out.shape == (m, n)
+            if m <= 4:
+                assert max_rel_err(out[:, :2048].cpu().numpy(), oracle.gemm_w4a32_grouped(x, p_h, s_h, None, 32)) < STAGE_TOL
+            x2 = rng.standard_normal((m, k)).astype(np.float32)
+            lhs = tb.w4a32_grouped_linear(dev(torch, 0.5 * x + x2), packed, scales, None, 32)
+            rhs = 0.5 * out + tb.w4a32_grouped_linear(dev(torch, x2), packed, scales, None, 32)
+            assert max_rel_err(lhs.cpu().numpy(), rhs.cpu().numpy()) < STAGE_TOL
+
+
+def test_linear_host_tensors_and_module(torch, tb, oracle):
+    rng = np.random.default_rng(9)
+    lin = torch.nn.Linear(256, 96, bias=True)
+    ql = tb.QuantizedLinear.from_float(lin, bits=4, group_size=32)
+    assert ql.qweight.shape == (96, 128) and ql.scales.shape == (96, 8) and ql.qweight.dtype == torch.uint8
+    ep, es = oracle.quantize_int4_grouped(lin.weight.detach().numpy(), 32)
+    assert np.array_equal(ql.qweight.numpy(), ep)
+    x = torch.from_numpy(rng.standard_normal((2, 3, 256)).astype(np.float32))
+    y = ql(x)  # CPU tensors in -> CPU tensor out, computed on the GPU
+    assert y.shape == (2, 3, 96) and y.device.type == "cpu"
+    want = oracle.gemm_w4a32_grouped(x.numpy(), ep, es, lin.bias.detach().numpy(), 32)
+    assert max_rel_err(y.numpy(), want) < STAGE_TOL
+    y2 = ql.cuda()(x.cuda())
+    assert max_rel_err(y2.cpu().numpy(), want) < STAGE_TOL
+    empty = ql(torch.zeros(0, 256))
+    assert empty.shape == (0, 96)
+    with pytest.raises(Exception):
+        tb.w4a32_grouped_linear(x, ql.qweight[:, :-1], ql.scales, None, 32)
+    with pytest.raises(NotImplementedError):
+        tb.QuantizedLinear(8, 8, bits=8)
+
+
+def test_tb_linear_handle_host_io(torch, tb, oracle):
+    import ctypes as C
+
+    rng = np.random.default_rng(4)
+    n, k, g, m = 200, 512, 64, 3
+    w, x, b = _linear_case(rng, n, k, g, m, True)
+    packed, scales = oracle.quantize_int4_grouped(w, g)
+    L = tb.lib()
+    h = C.c_void_p()
+    assert L.tb_linear_create(C.byref(h), packed.ctypes.data, scales.ctypes.data, b.ctypes.data, n, k, g, 0) == 0
+    out = np.empty((m, n), np.float32)
+    assert L.tb_linear_forward(h, x.ctypes.data, m, out.ctypes.data, 0, None) == 0
+    assert max_rel_err(out, oracle.gemm_w4a32_grouped(x, packed, scales, b, g)) < STAGE_TOL
+    assert L.tb_linear_forward(h, x.ctypes.data, 0, out.ctypes.data, 0, None) == 0
+    L.tb_linear_destroy(h)
+
+
+# ------------------------------------------------------ SwiGLU / RMSNorm / MLP
+@pytest.mark.parametrize("n,k,g,m", [(4864, 896, 32, 1), (14336, 4096, 32, 1), (1000, 512, 64, 1), (777, 1024, 32, 5)])
+def test_swiglu_gemv_matches_oracle(torch, tb, oracle, n, k, g, m):
+    rng = np.random.default_rng(n + k)
+    gw, gs = oracle.quantize_int4_grouped((rng.standard_normal((n, k)) * 0.05).astype(np.float32), g)
+    uw, us = oracle.quantize_int4_grouped((rng.standard_normal((n, k)) * 0.05).astype(np.float32), g)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    h = torch.empty((m, n), device="cuda")
+    L = tb.lib()
+    t = [dev(torch, a) for a in (x, gw, gs, uw, us)]
+    assert L.tb_swiglu_gemv_w4a32(t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), None, t[3].data_ptr(),
+                                  t[4].data_ptr(), None, h.data_ptr(), m, n, k, g, None) == 0
+    torch.cuda.synchronize()
+    want = np.stack([oracle.swiglu_gemv(x[i], gw, gs, None, uw, us, None, g) for i in range(m)])
+    assert max_rel_err(h.cpu().numpy(), want) < STAGE_TOL
+
+
+def test_rms_norm_known_answer_and_oracle(torch, tb, oracle):
+    # tests/parity/decoder.rs:13-29
+    n = 896
+    i = np.arange(n, dtype=np.float32)
+    x = (np.sin(i * np.float32(0.31)) * 3).astype(np.float32)
+    w = (1 + np.float32(0.001) * i).astype(np.float32)
+    out = torch.empty(2, n, device="cuda")
+    xs = dev(torch, np.stack([x, 2 * x]))
+    assert tb.lib().tb_fast_rms_norm(xs.data_ptr(), dev(torch, w).data_ptr(), out.data_ptr(), 2, n, 1e-6, None) == 0
+    torch.cuda.synchronize()
+    want = x.astype(np.float64) / np.sqrt((x.astype(np.float64) ** 2).mean() + 1e-6) * w
+    got = out.cpu().numpy()
+    assert (np.abs(got[0] - want) / np.maximum(np.abs(want), 1e-6)).max() < 1e-4
+    assert max_rel_err(got[0], oracle.rms_norm(x, w, 1e-6)) < 1e-6
+    assert max_rel_err(got[1], oracle.rms_norm(2 * x, w, 1e-6)) < 1e-6
+
+
+@pytest.mark.parametrize("m", [1, 6])
+def test_fused_swiglu_mlp_matches_oracle(torch, tb, oracle, m):
+    rng = np.random.default_rng(12 + m)
+    H, I, g = 256, 640, 32
+
+    def ql(n, k):
+        q = tb.QuantizedLinear(k, n, bias=False, bits=4, group_size=g)
+        p, s = oracle.quantize_int4_grouped((rng.standard_normal((n, k)) * 0.05).astype(np.float32), g)
+        q.qweight.copy_(torch.from_numpy(p)); q.scales.copy_(torch.from_numpy(s))
+        return q, p, s
+
+    (gq, gp, gs), (uq, up_, us), (dq, dp, ds) = ql(I, H), ql(I, H), ql(H, I)
+    x = rng.standard_normal((1, m, H)).astype(np.float32)
+    want = oracle.fused_swiglu_mlp(x, gp, gs, None, up_, us, None, dp, ds, None, g)
+    got_host = tb.fused_swiglu_mlp(torch.from_numpy(x), gq, uq, dq)
+    assert got_host.shape == (1, m, H)
+    assert max_rel_err(got_host.numpy(), want) < STAGE_TOL
+    got_dev = tb.fused_swiglu_mlp_batched(torch.from_numpy(x).cuda(), gq.cuda(), uq.cuda(), dq.cuda())
+    assert max_rel_err(got_dev.cpu().numpy(), want) < STAGE_TOL
+
+
+# ----------------------------------------------------------------- attention
+def _attn_case(rng, nh, nkv, hd, max_seq, batch):
+    qkv = rng.standard_normal((batch, (nh + 2 * nkv) * hd)).astype(np.float32)
+    kc = (rng.standard_normal((batch, nkv, max_seq, hd)) * 0.5).astype(np.float32)
+    vc = rng.standard_normal((batch, nkv, max_seq, hd)).astype(np.float32)
+    return qkv, kc, vc
+
+
+@pytest.mark.parametrize("nh,nkv,hd,max_seq,offsets,chunk", [
+    (14, 2, 64, 1024, [1023], 0), (14, 2, 64, 1024, [0], 0), (32, 8, 128, 4096, [4095], 0),
+    (32, 8, 128, 4096, [31, 32, 33, 2000], 0), (8, 8, 32, 96, [95], 32), (8, 1, 128, 300, [257], 64),
+    (4, 2, 64, 512, [100, 511, 0], 256), (64, 8, 128, 600, [599], 128),
+])
+def test_attention_decode_matches_oracle(torch, tb, oracle, nh, nkv, hd, max_seq, offsets, chunk):
+    rng = np.random.default_rng(nh * 100 + hd + max_seq)
+    b = len(offsets)
+    qkv, kc, vc = _attn_case(rng, nh, nkv, hd, max_seq, b)
+    cos_t, sin_t = oracle.rope_tables(max_seq, hd, 1e6)
+    L = tb.lib()
+    L.tb_set_attention_chunk(chunk)
+    try:
+        sb = L.tb_attention_scratch_bytes(b, nh, nkv, hd, max_seq)
+        scratch = torch.zeros(sb, dtype=torch.uint8, device="cuda")
+        d_qkv, d_k, d_v = dev(torch, qkv), dev(torch, kc), dev(torch, vc)
+        d_cos, d_sin = dev(torch, cos_t), dev(torch, sin_t)
+        d_off = dev(torch, np.asarray(offsets, np.int32))
+        out = torch.full((b, nh * hd), float("nan"), device="cuda")
+        for _ in range(2):  # second launch reuses the self-resetting counters
+            assert L.tb_attention_decode(d_qkv.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), d_cos.data_ptr(),
+                                         d_sin.data_ptr(), d_off.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                         b, nh, nkv, hd, max_seq, None) == 0, tb.last_error()
+        torch.cuda.synchronize()
+    finally:
+        L.tb_set_attention_chunk(0)
+    got, gk, gv = out.cpu().numpy(), d_k.cpu().numpy(), d_v.cpu().numpy()
+    q_dim, kv_dim = nh * hd, nkv * hd
+    for s, off in enumerate(offsets):
+        q = qkv[s, :q_dim].reshape(nh, hd).copy()
+        k = qkv[s, q_dim:q_dim + kv_dim].reshape(nkv, hd).copy()
+        v = qkv[s, q_dim + kv_dim:].reshape(nkv, hd)
+        for h in range(nh):
+            q[h] = oracle.rope_apply_head(q[h], cos_t[off], sin_t[off])
+        for h in range(nkv):
+            k[h] = oracle.rope_apply_head(k[h], cos_t[off], sin_t[off])
+        ek, ev = kc[s].copy(), vc[s].copy()
+        ek[:, off], ev[:, off] = k, v
+        # cache slot [kv_h, offset, :] written bit-exactly, nothing else touched
+        assert np.array_equal(gk[s], ek) and np.array_equal(gv[s], ev)
+        want = oracle.attention_decode(q, ek, ev, off + 1)
+        assert max_rel_err(got[s].reshape(nh, hd), want) < STAGE_TOL, (s, off)
+
+
+def test_attention_invalid_offset_writes_zeros_and_no_cache(torch, tb, oracle):
+    rng = np.random.default_rng(3)
+    nh, nkv, hd, max_seq = 4, 2, 64, 64
+    qkv, kc, vc = _attn_case(rng, nh, nkv, hd, max_seq, 2)
+    cos_t, sin_t = oracle.rope_tables(max_seq, hd, 1e4)
+    L = tb.lib()
+    scratch = torch.zeros(L.tb_attention_scratch_bytes(2, nh, nkv, hd, max_seq), dtype=torch.uint8, device="cuda")
+    d_k, d_v = dev(torch, kc), dev(torch, vc)
+    out = torch.full((2, nh * hd), 7.0, device="cuda")
+    off = dev(torch, np.asarray([-1, 5], np.int32))
+    assert L.tb_attention_decode(dev(torch, qkv).data_ptr(), d_k.data_ptr(), d_v.data_ptr(), dev(torch, cos_t).data_ptr(),
+                                 dev(torch, sin_t).data_ptr(), off.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                 2, nh, nkv, hd, max_seq, None) == 0
+    torch.cuda.synchronize()
+    assert not out[0].any() and out[1].abs().max() > 0
+    assert np.array_equal(d_k[0].cpu().numpy(), kc[0]) and np.array_equal(d_v[0].cpu().numpy(), vc[0])
+
+
+def test_fused_attention_step_matches_oracle(torch, tb, oracle):
+    rng = np.random.default_rng(21)
+    H, nh, nkv, hd, g, max_seq, off = 256, 4, 2, 64, 32, 128, 77
+    tq = (nh + 2 * nkv) * hd
+    qkv_m = tb.QuantizedLinear(H, tq, bias=True, bits=4, group_size=g)
+    o_m = tb.QuantizedLinear(nh * hd, H, bias=False, bits=4, group_size=g)
+    qp, qs = oracle.quantize_int4_grouped((rng.standard_normal((tq, H)) * 0.05).astype(np.float32), g)
+    op, os_ = oracle.quantize_int4_grouped((rng.standard_normal((H, nh * hd)) * 0.05).astype(np.float32), g)
+    qb = (rng.standard_normal(tq) * 0.1).astype(np.float32)
+    with torch.no_grad():
+        qkv_m.qweight.copy_(torch.from_numpy(qp)); qkv_m.scales.copy_(torch.from_numpy(qs)); qkv_m.bias.copy_(torch.from_numpy(qb))
+        o_m.qweight.copy_(torch.from_numpy(op)); o_m.scales.copy_(torch.from_numpy(os_))
+    x = rng.standard_normal((1, 1, H)).astype(np.float32)
+    kc = (rng.standard_normal((1, nkv, max_seq, hd)) * 0.5).astype(np.float32)
+    vc = rng.standard_normal((1, nkv, max_seq, hd)).astype(np.float32)
+    cos_t, sin_t = oracle.rope_tables(max_seq, hd, 1e6)
+    d_k, d_v = dev(torch, kc), dev(torch, vc)
+    got = tb.fused_attention_step(torch.from_numpy(x), qkv_m, o_m, d_k, d_v, torch.from_numpy(cos_t[off]),
+                                  torch.from_numpy(sin_t[off]), off, nh, nkv, hd)
+    qkv = oracle.gemm_w4a32_grouped(x.reshape(-1), qp, qs, qb, g)
+    q = qkv[: nh * hd].reshape(nh, hd).copy(); k = qkv[nh * hd: (nh + nkv) * hd].reshape(nkv, hd).copy()
+    v = qkv[(nh + nkv) * hd:].reshape(nkv, hd)
+    for h in range(nh): q[h] = oracle.rope_apply_head(q[h], cos_t[off], sin_t[off])
+    for h in range(nkv): k[h] = oracle.rope_apply_head(k[h], cos_t[off], sin_t[off])
+    ek, ev = kc[0].copy(), vc[0].copy(); ek[:, off], ev[:, off] = k, v
+    attn = oracle.attention_decode(q, ek, ev, off + 1)
+    want = oracle.gemm_w4a32_grouped(attn.reshape(-1), op, os_, None, g)
+    assert got.shape == (1, 1, H)
+    assert max_rel_err(got.numpy(), want) < STAGE_TOL
+    gk, gv = d_k.cpu().numpy()[0], d_v.cpu().numpy()[0]
+    assert max_rel_err(gk, ek) < 1e-6 and max_rel_err(gv, ev) < 1e-6
+    mask = np.ones(max_seq, bool); mask[off] = False  # every other slot untouched, bit for bit
+    assert np.array_equal(gk[:, mask], kc[0][:, mask]) and np.array_equal(gv[:, mask], vc[0][:, mask])
+
+
+# ------------------------------------------------------------------- decoder
+def _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, **kw):
+    lay = [[lw[k] for k in ["input_norm_w", "qkv_w", "qkv_s", "o_w", "o_s", "post_norm_w", "gate_w", "gate_s",
+                            "up_w", "up_s", "down_w", "down_s"]] + ([lw["qkv_b"]] if lw.get("qkv_b") is not None else [])
+           for lw in layers]
+    return tb.B200QwenDecoder(embed, lay, fnorm, lm_w, lm_s, cfg["num_layers"], cfg["hidden_size"],
+                              cfg["intermediate_size"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"],
+                              cfg["group_size"], cfg["rms_norm_eps"], cfg["max_seq_len"], cfg["rope_theta"], **kw)
+
+
+@pytest.mark.parametrize("fixture", ["decoder_qwen_tiny_g32.npz", "decoder_llama_tiny_g64.npz"])
+@pytest.mark.parametrize("debug", [False, True])
+def test_decoder_matches_reference_python_model_golden(torch, tb, fixture, debug):
+    cfg, embed, layers, fnorm, lm_w, lm_s, z = load_decoder_golden(fixture)
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, debug=debug)
+    for off, tok in enumerate(z["tokens"]):
+        logits = dec.step(int(tok), off)
+        assert max_rel_err(logits, z["logits"][off]) < LOGIT_TOL, off
+    T = len(z["tokens"])
+    assert dec.kv_len() == T
+    k0, v0 = dec.read_kv_cache(0)
+    assert max_rel_err(k0[:, :T], z["k_cache_l0"]) < STAGE_TOL and max_rel_err(v0[:, :T], z["v_cache_l0"]) < STAGE_TOL
+    assert not k0[:, T:].any() and not v0[:, T:].any()
+
+
+def test_decoder_stages_and_logits_match_oracle_qwen_shape(torch, tb, oracle):
+    # Qwen2.5-0.5B widths (hidden 896, 14/2 heads, d 64, inter 4864), 3 layers, vocab 4096
+    cfg = dict(vocab_size=4096, hidden_size=896, intermediate_size=4864, num_layers=3, num_heads=14,
+               num_kv_heads=2, head_dim=64, group_size=32, max_seq_len=128, rms_norm_eps=1e-6, rope_theta=1e6)
+    embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 77, oracle.quantize_int4_grouped, qkv_bias=True)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, debug=True)
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, cfg["vocab_size"], 40)
+    for off, tok in enumerate(toks):
+        want = ref.step(int(tok), off)
+        got = dec.step(int(tok), off)
+        assert max_rel_err(got, want) < LOGIT_TOL, off
+        if off in (0, 1, 39):
+            for stage in ("embed", "normed", "qkv", "attn", "x_attn", "h", "x_out"):
+                assert max_rel_err(dec.debug_stage(stage), ref.debug_stage(stage)) < STAGE_TOL, (off, stage)
+    for l in range(cfg["num_layers"]):
+        gk, gv = dec.read_kv_cache(l)
+        ek, ev = ref.kv_cache(l)
+        assert max_rel_err(gk, ek) < STAGE_TOL and max_rel_err(gv, ev) < STAGE_TOL
+    assert oracle.argmax(dec.get_logits()) == oracle.argmax(ref.get_logits())
+
+
+def test_decoder_api_semantics(torch, tb, oracle):
+    cfg, embed, layers, fnorm, lm_w, lm_s, z = load_decoder_golden("decoder_qwen_tiny_g32.npz")
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    toks = [int(t) for t in z["tokens"]]
+    # out-of-range token / offset: zero logits, no error, kv_len unchanged (decoder.rs:1066-1078)
+    dec.step(toks[0], 0)
+    assert not dec.step(cfg["vocab_size"], 1).any()
+    assert not dec.step(3, cfg["max_seq_len"]).any()
+    assert not dec.step(-5, 1).any()
+    assert dec.kv_len() == 1
+    # prefill_tokens / prefill / reset (decoder.rs:431-477, 545-558)
+    dec.reset_kv_cache()
+    assert dec.kv_len() == 0
+    assert dec.prefill_tokens([], 3) == 3
+    assert dec.prefill_tokens(toks, 0) == len(toks)
+    assert max_rel_err(dec.get_logits(), z["logits"][-1]) < LOGIT_TOL
+    with pytest.raises(ValueError, match="exceeds max_seq_len"):
+        dec.prefill_tokens(toks, cfg["max_seq_len"] - 2)
+    with pytest.raises(ValueError):
+        dec.prefill([])
+    dec.reset_kv_cache()
+    k0, v0 = dec.read_kv_cache(0)
+    assert not k0.any() and not v0.any()
+    assert max_rel_err(dec.prefill(toks), z["logits"][-1]) < LOGIT_TOL
+    # verify_tokens returns one row of logits per position (decoder.rs:565-582)
+    dec.reset_kv_cache()
+    rows = dec.verify_tokens(0, toks)
+    assert rows.shape == (len(toks), cfg["vocab_size"])
+    assert max_rel_err(rows, z["logits"]) < LOGIT_TOL
+    # copy_kv_cache_from_tensors (decoder.rs:479-523): resume another decoder from a copied prefix
+    ks, vs = zip(*[dec.read_kv_cache(l) for l in range(cfg["num_layers"])])
+    dec2 = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    dec2.copy_kv_cache_from_tensors([k[:, :8] for k in ks], [v[:, :8] for v in vs], len(toks) - 1)
+    assert dec2.kv_len() == len(toks) - 1
+    assert max_rel_err(dec2.step(toks[-1], len(toks) - 1), z["logits"][-1]) < LOGIT_TOL
+    # greedy decode on the device == argmax of the logits
+    dec.reset_kv_cache()
+    dec.prefill_tokens(toks[:-1], 0)
+    nxt = dec.decode_and_sample(toks[-1], len(toks) - 1)
+    assert nxt == oracle.argmax(z["logits"][-1])
+    assert dec.decode_and_sample(cfg["vocab_size"] + 1, 3) == 0
+    # device-lost flag is sticky (src/wgpu/decode.rs:692-716)
+    assert not dec.is_device_lost()
+    dec.mark_device_lost()
+    with pytest.raises(tb.TorchBurnB200Error, match="DEVICE_LOST"):
+        dec.step(1, 0)
+
+
+def test_decoder_generate_loop_matches_oracle_chain(torch, tb, oracle):
+    cfg = dict(vocab_size=512, hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4,
+               num_kv_heads=2, head_dim=64, group_size=64, max_seq_len=64, rms_norm_eps=1e-6, rope_theta=5e5)
+    embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 5, oracle.quantize_int4_grouped, std=0.2)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    tok, want = 7, []
+    for off in range(24):
+        lg = ref.step(tok, off)
+        srt = np.sort(lg)
+        tok = oracle.argmax(lg)
+        want.append((tok, srt[-1] - srt[-2]))
+    got = dec.generate_loop(7, 0, 24)
+    for i, (g, (w, margin)) in enumerate(zip(got, want)):
+        if margin < 1e-3 * np.abs(lg).max():
+            break  # a near-tie may legitimately flip; the chains diverge after it
+        assert g == w, i
+    assert dec.kv_len() == 24
+
+
+def test_decoder_batch_matches_single_sequences(torch, tb, oracle):
+    cfg = dict(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_layers=2, num_heads=8,
+               num_kv_heads=2, head_dim=64, group_size=32, max_seq_len=96, rms_norm_eps=1e-5, rope_theta=5e5)
+    embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 9, oracle.quantize_int4_grouped)
+    B = 11  # more than one slice of 8 activation rows
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, max_batch=B)
+    refs = [oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s) for _ in range(B)]
+    rng = np.random.default_rng(1)
+    for off in range(6):
+        toks = rng.integers(0, cfg["vocab_size"], B)
+        offs = [off] * B
+        if off == 3:
+            toks[2] = cfg["vocab_size"] + 3  # one bad sequence must not disturb the others
+        got = dec.step_batch(toks, offs)
+        for b in range(B):
+            want = refs[b].step(int(toks[b]), off)
+            assert max_rel_err(got[b], want) < LOGIT_TOL, (off, b)
+    for b in (0, 5, 10):
+        gk, gv = dec.read_kv_cache(1, seq=b)
+        ek, ev = refs[b].kv_cache(1)
+        assert max_rel_err(gk, ek) < STAGE_TOL and max_rel_err(gv, ev) < STAGE_TOL
+
+
+def test_decoder_qwen05b_config3_full_width(torch, tb, oracle):
+    # BASELINE config 3: Qwen2.5-0.5B architecture at full size (24 layers, vocab 151936, tied
+    # lm_head = quantized copy of the embedding, qkv bias), int4 group 32, random init std 0.02.
+    # The KV cache is produced by sequential steps from random token ids like prefill_tokens;
+    # 1024 oracle steps would take minutes on a small host, so the oracle runs the first 96
+    # positions and the CUDA path alone continues to 1024 where determinism and the graph
+    # replay against direct launches are checked.
+    cfg = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_layers=24, num_heads=14,
+               num_kv_heads=2, head_dim=64, group_size=32, max_seq_len=1024, rms_norm_eps=1e-6, rope_theta=1e6)
+    gen = torch.Generator("cuda").manual_seed(3)
+
+    def qlin(n, k):
+        w = torch.randn(n, k, device="cuda", generator=gen) * 0.02
+        p, s = tb.quantize_weight_int4_grouped(w, group_size=32)
+        return p.cpu().numpy(), s.cpu().numpy()
+
+    embed_t = torch.randn(cfg["vocab_size"], 896, device="cuda", generator=gen) * 0.02
+    lm_w, lm_s = [t.cpu().numpy() for t in tb.quantize_weight_int4_grouped(embed_t, group_size=32)]
+    embed = embed_t.cpu().numpy()
+    layers = []
+    for _ in range(24):
+        lw = {"input_norm_w": np.ones(896, np.float32), "post_norm_w": np.ones(896, np.float32),
+              "qkv_b": np.zeros(1152, np.float32)}
+        lw["qkv_w"], lw["qkv_s"] = qlin(1152, 896)
+        lw["o_w"], lw["o_s"] = qlin(896, 896)
+        lw["gate_w"], lw["gate_s"] = qlin(4864, 896)
+        lw["up_w"], lw["up_s"] = qlin(4864, 896)
+        lw["down_w"], lw["down_s"] = qlin(896, 4864)
+        layers.append(lw)
+    fnorm = np.ones(896, np.float32)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    toks = np.random.default_rng(0).integers(0, cfg["vocab_size"], 1024)
+    n_ref = 96
+    assert ref.prefill_tokens(toks[:n_ref - 1], 0) == n_ref - 1
+    assert dec.prefill_tokens(toks[:n_ref - 1], 0) == n_ref - 1
+    want = ref.step(int(toks[n_ref - 1]), n_ref - 1)
+    got = dec.step(int(toks[n_ref - 1]), n_ref - 1)
+    assert max_rel_err(got, want) < LOGIT_TOL
+    assert oracle.argmax(got) == oracle.argmax(want)
+    assert dec.prefill_tokens(toks[n_ref:1023], n_ref) == 1023
+    a = dec.step(int(toks[1023]), 1023)
+    b = dec.step(int(toks[1023]), 1023)  # same position again: idempotent cache write, same logits
+    assert np.array_equal(a, b) and np.isfinite(a).all() and dec.kv_len() == 1024
+    ks, vs = zip(*[dec.read_kv_cache(l) for l in range(24)])
+    dec_ng = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, debug=True)
+    dec_ng.copy_kv_cache_from_tensors(list(ks), list(vs), 1023)
+    c = dec_ng.step(int(toks[1023]), 1023)
+    assert max_rel_err(c, a) < 1e-6

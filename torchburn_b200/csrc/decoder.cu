@@ -1,0 +1,689 @@
+// The decoder handle: RustQwenDecoder / WgpuQwenDecoder (src/llm/decoder.rs:111-171,
+// src/wgpu/decode.rs:297-334) on one B200, or on one rank of a tensor-parallel group.
+//
+// One step = embedding gather, then per layer five kernels
+//   [RMSNorm + QKV GEMV] -> [RoPE + KV append + split-K attention + merge]
+//   -> [O GEMV + residual] -> [RMSNorm + gate/up GEMV + SwiGLU] -> [down GEMV + residual]
+// and [RMSNorm + lm_head GEMV]; the same order as step_internal
+// (src/llm/decoder.rs:1051-1374).  The kernels are chained with programmatic
+// dependent launch, so each kernel's weight stream starts while its predecessor
+// drains, and the whole step is replayed from a CUDA graph (the reference's wgpu
+// path records one command stream per token for the same reason,
+// src/wgpu/decode.rs:6-7).  Token ids and offsets live in device memory, so one
+// graph serves every position.
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "tb_common.cuh"
+#include "tp.cuh"
+
+using namespace tb;
+
+namespace {
+
+struct LayerDev {
+  float* input_norm_w = nullptr;
+  uint8_t* qkv_w = nullptr;
+  float* qkv_s = nullptr;
+  uint8_t* o_w = nullptr;
+  float* o_s = nullptr;
+  float* post_norm_w = nullptr;
+  uint8_t* gate_w = nullptr;
+  float* gate_s = nullptr;
+  uint8_t* up_w = nullptr;
+  float* up_s = nullptr;
+  uint8_t* down_w = nullptr;
+  float* down_s = nullptr;
+  float* qkv_b = nullptr;
+};
+
+constexpr int kMaxBatch = 64;
+
+}  // namespace
+
+struct tb_decoder {
+  tb_model_config cfg;
+  // full and per-rank dimensions
+  int64_t V = 0, H = 0, I = 0, S = 0;
+  int L = 0, nh = 0, nkv = 0, hd = 0, G = 0, B = 1;
+  int tp = 1, rank = 0;
+  int nh_l = 0, nkv_l = 0;
+  int64_t I_l = 0, V_l = 0, q_dim_l = 0, tq_l = 0;
+  int device = 0;
+
+  float* embed = nullptr;
+  std::vector<LayerDev> layers;
+  float* final_norm_w = nullptr;
+  uint8_t* lm_w = nullptr;
+  float* lm_s = nullptr;
+  float *cos_t = nullptr, *sin_t = nullptr;
+  float *k_cache = nullptr, *v_cache = nullptr;  // [L][B][Hkv_l][S][d]
+  float *x = nullptr, *qkv = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr;
+  float* partial = nullptr;  // tensor parallel: this rank's partial sums [B, H]
+  float* logits_l = nullptr; // tensor parallel: this rank's logit slice [B, V_l]
+  int32_t *d_tokens = nullptr, *d_offsets = nullptr, *d_eff = nullptr;
+  int32_t *d_hist = nullptr, *d_hist_pos = nullptr;
+  int64_t hist_cap = 0;
+  int32_t* h_io = nullptr;  // pinned: tokens | offsets
+  int32_t* h_feed = nullptr; // pinned: per-step (token, offset) pairs for prefill
+  int64_t feed_cap = 0;
+  void* attn_scratch = nullptr;
+  // layer-0 stage snapshots (TB_DECODER_NO_GRAPH only)
+  float *dbg_embed = nullptr, *dbg_normed = nullptr, *dbg_qkv = nullptr, *dbg_attn = nullptr,
+        *dbg_x_attn = nullptr, *dbg_h = nullptr, *dbg_x_out = nullptr;
+
+  cudaStream_t stream = nullptr;
+  cudaGraphExec_t graphs[kMaxBatch + 1] = {};
+  cudaGraphExec_t graphs_greedy[kMaxBatch + 1] = {};
+  bool use_graph = true;
+  bool pdl = true;
+  int64_t kv_used = 0;
+  int last_batch = 1;
+  bool device_lost = false;
+  int launches_per_step = 0;
+  TpState* tpst = nullptr;
+};
+
+namespace {
+
+#define DEC_CUDA(dec, expr)                                                                     \
+  do {                                                                                          \
+    cudaError_t _e = (expr);                                                                    \
+    if (_e != cudaSuccess) {                                                                    \
+      if (_e != cudaErrorMemoryAllocation && _e != cudaErrorInvalidValue) (dec)->device_lost = true; \
+      return fail(_e == cudaErrorMemoryAllocation ? TB_ERR_OOM : TB_ERR_CUDA, "%s failed: %s",  \
+                  #expr, cudaGetErrorString(_e));                                               \
+    }                                                                                           \
+  } while (0)
+
+tb_status check_alive(const tb_decoder* d, const char* what) {
+  if (!d) return fail(TB_ERR_ARG, "%s: null decoder", what);
+  if (d->device_lost) return fail(TB_ERR_DEVICE_LOST, "%s: device lost; create a new decoder", what);
+  return TB_OK;
+}
+
+template <typename T>
+tb_status dalloc(T** p, size_t count) {
+  *p = nullptr;
+  if (count == 0) return TB_OK;
+  cudaError_t e = cudaMalloc((void**)p, count * sizeof(T));
+  if (e != cudaSuccess) return fail(TB_ERR_OOM, "Out of memory allocating %zu MB on the device (%s)",
+                                    count * sizeof(T) / (1024 * 1024), cudaGetErrorString(e));
+  return TB_OK;
+}
+
+size_t kv_layer_stride(const tb_decoder* d) { return (size_t)d->B * d->nkv_l * d->S * d->hd; }
+
+// Enqueues one step for `b` sequences on d->stream (direct launches; also what
+// a graph capture records).  debug: copy layer-0 intermediates.
+tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_head = nullptr) {
+  cudaStream_t st = d->stream;
+  const bool pdl = d->pdl;
+  int launches = 0;
+  TB_TRY(launch_embed_gather(d->embed, d->d_tokens, d->d_offsets, d->x, d->d_eff, b, d->V, d->H, d->S,
+                             false, st));
+  ++launches;
+  auto snap = [&](float* dst, const float* src, size_t n) -> tb_status {
+    if (!debug) return TB_OK;
+    TB_CUDA_TRY(cudaMemcpyAsync(dst, src, n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return TB_OK;
+  };
+  TB_TRY(snap(d->dbg_embed, d->x, d->H));
+  for (int l = 0; l < d->L; ++l) {
+    const LayerDev& W = d->layers[l];
+    const bool dbg = debug && l == 0;
+    {  // A + B: RMSNorm fused into the QKV projection
+      GemvArgs a;
+      a.x = d->x; a.w = W.qkv_w; a.scales = W.qkv_s; a.bias = W.qkv_b; a.out = d->qkv;
+      a.norm_w = W.input_norm_w; a.eps = d->cfg.rms_norm_eps;
+      a.x_normed_out = dbg ? d->dbg_normed : nullptr;
+      a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug;
+      TB_TRY(launch_w4_gemv(a, st));
+      ++launches;
+    }
+    {  // C + D + E
+      AttnArgs a;
+      a.qkv = d->qkv;
+      a.k_cache = d->k_cache + (size_t)l * kv_layer_stride(d);
+      a.v_cache = d->v_cache + (size_t)l * kv_layer_stride(d);
+      a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.offsets = d->d_eff; a.out = d->attn;
+      a.scratch = d->attn_scratch; a.q_rot_out = dbg ? d->dbg_qkv : nullptr;
+      a.batch = b; a.num_heads = d->nh_l; a.num_kv_heads = d->nkv_l; a.head_dim = d->hd;
+      a.max_seq_len = d->S; a.pdl = pdl && !debug;
+      // The kernel strides sequences by [Hkv, S, d]; with batch > 1 that is the layout of
+      // one layer's block [B][Hkv][S][d].
+      TB_TRY(launch_attention_decode(a, st));
+      ++launches;
+    }
+    if (dbg) TB_TRY(snap(d->dbg_attn, d->attn, d->q_dim_l));
+    {  // F + G
+      GemvArgs a;
+      a.x = d->attn; a.w = W.o_w; a.scales = W.o_s; a.m = b; a.n = d->H; a.k = d->q_dim_l; a.g = d->G;
+      a.pdl = pdl && !debug;
+      if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
+      else { a.out = d->partial; }
+      TB_TRY(launch_w4_gemv(a, st));
+      ++launches;
+      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, d->partial, d->x, b, d->H, st, &launches)); }
+    }
+    if (dbg) TB_TRY(snap(d->dbg_x_attn, d->x, d->H));
+    {  // H + I: RMSNorm fused into the gate/up projection with the SwiGLU epilogue
+      GemvArgs a;
+      a.x = d->x; a.w = W.gate_w; a.scales = W.gate_s; a.w2 = W.up_w; a.scales2 = W.up_s; a.out = d->h;
+      a.norm_w = W.post_norm_w; a.eps = d->cfg.rms_norm_eps;
+      a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug;
+      TB_TRY(launch_w4_gemv(a, st));
+      ++launches;
+    }
+    if (dbg) TB_TRY(snap(d->dbg_h, d->h, d->I_l));
+    {  // I' + J
+      GemvArgs a;
+      a.x = d->h; a.w = W.down_w; a.scales = W.down_s; a.m = b; a.n = d->H; a.k = d->I_l; a.g = d->G;
+      a.pdl = pdl && !debug;
+      if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
+      else { a.out = d->partial; }
+      TB_TRY(launch_w4_gemv(a, st));
+      ++launches;
+      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, d->partial, d->x, b, d->H, st, &launches)); }
+    }
+    if (dbg) TB_TRY(snap(d->dbg_x_out, d->x, d->H));
+  }
+  if (before_lm_head) TB_CUDA_TRY(cudaEventRecord(before_lm_head, st));
+  {  // 3 + 4: final RMSNorm fused into lm_head
+    GemvArgs a;
+    a.x = d->x; a.w = d->lm_w; a.scales = d->lm_s;
+    a.norm_w = d->final_norm_w; a.eps = d->cfg.rms_norm_eps;
+    a.m = b; a.n = d->V_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug;
+    a.out = d->tp == 1 ? d->logits : d->logits_l;
+    TB_TRY(launch_w4_gemv(a, st));
+    ++launches;
+    if (d->tp > 1) { TB_TRY(tp_allgather_logits(d->tpst, d->logits_l, d->logits, b, d->V_l, st, &launches)); }
+  }
+  d->launches_per_step = launches;
+  return TB_OK;
+}
+
+tb_status build_graph(tb_decoder* d, int b, bool greedy, cudaGraphExec_t* out) {
+  *out = nullptr;
+  cudaGraph_t graph = nullptr;
+  DEC_CUDA(d, cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+  tb_status s = enqueue_step(d, b, false);
+  if (s == TB_OK && greedy) s = launch_argmax(d->logits, d->V, b, d->d_tokens, d->d_offsets, d->d_hist, d->d_hist_pos, d->stream);
+  cudaError_t e = cudaStreamEndCapture(d->stream, &graph);
+  if (s != TB_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return s;
+  }
+  if (e != cudaSuccess) return fail(TB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(out, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    *out = nullptr;
+    return fail(TB_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+  }
+  return TB_OK;
+}
+
+// Runs one step for b sequences whose tokens/offsets are already in d_tokens/d_offsets.
+tb_status run_step(tb_decoder* d, int b, bool greedy) {
+  if (d->use_graph) {
+    cudaGraphExec_t* slot = greedy ? &d->graphs_greedy[b] : &d->graphs[b];
+    if (!*slot) {
+      tb_status s = build_graph(d, b, greedy, slot);
+      if (s != TB_OK) {
+        // A capture problem is not a device problem: fall back to direct launches.
+        cudaGetLastError();
+        d->use_graph = false;
+      }
+    }
+    if (*slot) {
+      DEC_CUDA(d, cudaGraphLaunch(*slot, d->stream));
+      return TB_OK;
+    }
+  }
+  TB_TRY(enqueue_step(d, b, !d->use_graph && (d->cfg.flags & TB_DECODER_NO_GRAPH)));
+  if (greedy) TB_TRY(launch_argmax(d->logits, d->V, b, d->d_tokens, d->d_offsets, d->d_hist, d->d_hist_pos, d->stream));
+  return TB_OK;
+}
+
+void note_kv(tb_decoder* d, int64_t token, int64_t offset) {
+  if (token >= 0 && token < d->V && offset >= 0 && offset < d->S && offset + 1 > d->kv_used)
+    d->kv_used = offset + 1;  // src/llm/decoder.rs:1092
+}
+
+int32_t clamp_i32(int64_t v) { return v < -1 ? -1 : (v > 0x7ffffff0 ? 0x7ffffff0 : (int32_t)v); }
+
+tb_status feed_and_step(tb_decoder* d, const int64_t* tokens, const int64_t* offsets, int b) {
+  for (int i = 0; i < b; ++i) {
+    d->h_io[i] = clamp_i32(tokens[i]);
+    d->h_io[kMaxBatch + i] = clamp_i32(offsets[i]);
+    note_kv(d, tokens[i], offsets[i]);
+  }
+  DEC_CUDA(d, cudaMemcpyAsync(d->d_tokens, d->h_io, sizeof(int32_t) * b, cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(d, cudaMemcpyAsync(d->d_offsets, d->h_io + kMaxBatch, sizeof(int32_t) * b, cudaMemcpyHostToDevice, d->stream));
+  d->last_batch = b;
+  return run_step(d, b, false);
+}
+
+}  // namespace
+
+extern "C" {
+
+tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
+                            const float* embed_tokens, const tb_layer_weights* layers,
+                            const float* final_norm_w, const uint8_t* lm_head_w,
+                            const float* lm_head_s, tb_space ws) {
+  if (!out) return fail(TB_ERR_ARG, "tb_decoder_create: null out");
+  *out = nullptr;
+  if (!cfg || !embed_tokens || !layers || !final_norm_w || !lm_head_w || !lm_head_s)
+    return fail(TB_ERR_ARG, "tb_decoder_create: null argument");
+  const tb_model_config& c = *cfg;
+  // src/llm/decoder.rs:214-233
+  if (c.hidden_size <= 0 || c.hidden_size % 4 != 0)
+    return fail(TB_ERR_ARG, "hidden_size (%lld) must be divisible by 4 (SIMD alignment)", (long long)c.hidden_size);
+  if (c.group_size != 32 && c.group_size != 64 && c.group_size != 128)
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: group_size %d (supported: 32, 64, 128)", c.group_size);
+  if (c.hidden_size % c.group_size != 0)
+    return fail(TB_ERR_ARG, "hidden_size (%lld) must be divisible by group_size (%d)", (long long)c.hidden_size, c.group_size);
+  if (c.head_dim <= 0 || c.head_dim % 2 != 0)
+    return fail(TB_ERR_ARG, "head_dim (%d) must be even for RoPE half_dim computation", c.head_dim);
+  if (c.num_kv_heads <= 0 || c.num_heads <= 0 || c.num_heads % c.num_kv_heads != 0)
+    return fail(TB_ERR_ARG, "num_heads (%d) must be divisible by num_kv_heads (%d) for GQA", c.num_heads, c.num_kv_heads);
+  if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128)
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: head_dim %d (supported: 32, 64, 128)", c.head_dim);
+  if (c.num_heads / c.num_kv_heads > 8)
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: more than 8 q heads per kv head");
+  if (c.vocab_size <= 0 || c.intermediate_size <= 0 || c.num_layers <= 0 || c.max_seq_len <= 0)
+    return fail(TB_ERR_ARG, "tb_decoder_create: non-positive dimension");
+  if (c.max_seq_len > 32768)
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: max_seq_len %lld (attention covers at most 32768 positions)", (long long)c.max_seq_len);
+  const int B = c.max_batch <= 0 ? 1 : c.max_batch;
+  if (B > kMaxBatch) return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: max_batch %d (max %d)", B, kMaxBatch);
+  const int tp = c.tp_size <= 0 ? 1 : c.tp_size;
+  if (c.tp_rank < 0 || c.tp_rank >= tp) return fail(TB_ERR_ARG, "tp_rank %d outside [0, %d)", c.tp_rank, tp);
+  const int64_t q_dim = (int64_t)c.num_heads * c.head_dim;
+  if (tp > 1) {
+    if (c.num_kv_heads % tp || c.num_heads % tp || c.intermediate_size % ((int64_t)tp * c.group_size) ||
+        q_dim % ((int64_t)tp * c.group_size) || c.vocab_size % tp)
+      return fail(TB_ERR_ARG, "tensor parallel size %d does not divide the heads / intermediate / vocab into whole groups", tp);
+  }
+  if (q_dim % c.group_size != 0 || c.intermediate_size % c.group_size != 0)
+    return fail(TB_ERR_ARG, "num_heads*head_dim and intermediate_size must be divisible by group_size (%d)", c.group_size);
+
+  tb_decoder* d = new (std::nothrow) tb_decoder();
+  if (!d) return fail(TB_ERR_OOM, "tb_decoder_create: host allocation failed");
+  d->cfg = c;
+  d->V = c.vocab_size; d->H = c.hidden_size; d->I = c.intermediate_size; d->S = c.max_seq_len;
+  d->L = c.num_layers; d->nh = c.num_heads; d->nkv = c.num_kv_heads; d->hd = c.head_dim; d->G = c.group_size;
+  d->B = B; d->tp = tp; d->rank = c.tp_rank;
+  d->nh_l = d->nh / tp; d->nkv_l = d->nkv / tp; d->I_l = d->I / tp; d->V_l = d->V / tp;
+  d->q_dim_l = (int64_t)d->nh_l * d->hd;
+  d->tq_l = d->q_dim_l + 2ll * d->nkv_l * d->hd;
+  d->use_graph = !(c.flags & TB_DECODER_NO_GRAPH);
+  cudaGetDevice(&d->device);
+
+  tb_status s = TB_OK;
+  auto fin = [&](tb_status st) -> tb_status {
+    tb_decoder_destroy(d);
+    return st;
+  };
+#define CR(expr) do { s = (expr); if (s != TB_OK) return fin(s); } while (0)
+#define CRC(expr) do { cudaError_t _e = (expr); if (_e != cudaSuccess) return fin(fail(_e == cudaErrorMemoryAllocation ? TB_ERR_OOM : TB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e))); } while (0)
+
+  CRC(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  const int64_t H = d->H, G = d->G;
+  CR(upload((void**)&d->embed, embed_tokens, sizeof(float) * d->V * H, ws));
+  CR(upload((void**)&d->final_norm_w, final_norm_w, sizeof(float) * H, ws));
+  CR(upload((void**)&d->lm_w, lm_head_w, (size_t)d->V_l * (H / 2), ws));
+  CR(upload((void**)&d->lm_s, lm_head_s, sizeof(float) * d->V_l * (H / G), ws));
+  d->layers.resize(d->L);
+  for (int l = 0; l < d->L; ++l) {
+    const tb_layer_weights& w = layers[l];
+    LayerDev& o = d->layers[l];
+    if (!w.input_norm_w || !w.qkv_w || !w.qkv_s || !w.o_w || !w.o_s || !w.post_norm_w || !w.gate_w ||
+        !w.gate_s || !w.up_w || !w.up_s || !w.down_w || !w.down_s)
+      return fin(fail(TB_ERR_ARG, "Each layer requires 12 tensors: input_norm, qkv_w, qkv_s, o_w, o_s, post_norm, gate_w, gate_s, up_w, up_s, down_w, down_s (layer %d)", l));
+    CR(upload((void**)&o.input_norm_w, w.input_norm_w, sizeof(float) * H, ws));
+    CR(upload((void**)&o.qkv_w, w.qkv_w, (size_t)d->tq_l * (H / 2), ws));
+    CR(upload((void**)&o.qkv_s, w.qkv_s, sizeof(float) * d->tq_l * (H / G), ws));
+    CR(upload((void**)&o.o_w, w.o_w, (size_t)H * (d->q_dim_l / 2), ws));
+    CR(upload((void**)&o.o_s, w.o_s, sizeof(float) * H * (d->q_dim_l / G), ws));
+    CR(upload((void**)&o.post_norm_w, w.post_norm_w, sizeof(float) * H, ws));
+    CR(upload((void**)&o.gate_w, w.gate_w, (size_t)d->I_l * (H / 2), ws));
+    CR(upload((void**)&o.gate_s, w.gate_s, sizeof(float) * d->I_l * (H / G), ws));
+    CR(upload((void**)&o.up_w, w.up_w, (size_t)d->I_l * (H / 2), ws));
+    CR(upload((void**)&o.up_s, w.up_s, sizeof(float) * d->I_l * (H / G), ws));
+    CR(upload((void**)&o.down_w, w.down_w, (size_t)H * (d->I_l / 2), ws));
+    CR(upload((void**)&o.down_s, w.down_s, sizeof(float) * H * (d->I_l / G), ws));
+    if (w.qkv_b) CR(upload((void**)&o.qkv_b, w.qkv_b, sizeof(float) * d->tq_l, ws));
+  }
+  {  // RoPE tables in float64, src/llm/decoder.rs:336-350
+    const int hd = d->hd, half = hd / 2;
+    std::vector<float> ct((size_t)d->S * hd), sn((size_t)d->S * hd);
+    std::vector<double> freq(half);
+    for (int i = 0; i < half; ++i) freq[i] = 1.0 / std::pow(c.rope_theta, (2.0 * (double)i) / (double)hd);
+    for (int64_t pos = 0; pos < d->S; ++pos)
+      for (int i = 0; i < half; ++i) {
+        const double val = (double)pos * freq[i];
+        const float cv = (float)std::cos(val), sv = (float)std::sin(val);
+        ct[pos * hd + i] = cv; ct[pos * hd + i + half] = cv;
+        sn[pos * hd + i] = sv; sn[pos * hd + i + half] = sv;
+      }
+    CR(upload((void**)&d->cos_t, ct.data(), sizeof(float) * ct.size(), TB_HOST));
+    CR(upload((void**)&d->sin_t, sn.data(), sizeof(float) * sn.size(), TB_HOST));
+  }
+  const size_t kv_elems = (size_t)d->L * kv_layer_stride(d);
+  CR(dalloc(&d->k_cache, kv_elems));
+  CR(dalloc(&d->v_cache, kv_elems));
+  CRC(cudaMemset(d->k_cache, 0, kv_elems * sizeof(float)));
+  CRC(cudaMemset(d->v_cache, 0, kv_elems * sizeof(float)));
+  CR(dalloc(&d->x, (size_t)B * H));
+  CR(dalloc(&d->qkv, (size_t)B * d->tq_l));
+  CR(dalloc(&d->attn, (size_t)B * d->q_dim_l));
+  CR(dalloc(&d->h, (size_t)B * d->I_l));
+  CR(dalloc(&d->logits, (size_t)B * d->V));
+  CRC(cudaMemset(d->logits, 0, (size_t)B * d->V * sizeof(float)));
+  if (tp > 1) {
+    CR(dalloc(&d->partial, (size_t)B * H));
+    CR(dalloc(&d->logits_l, (size_t)B * d->V_l));
+  }
+  CR(dalloc(&d->d_tokens, (size_t)kMaxBatch));
+  CR(dalloc(&d->d_offsets, (size_t)kMaxBatch));
+  CR(dalloc(&d->d_eff, (size_t)kMaxBatch));
+  CR(dalloc(&d->d_hist_pos, (size_t)1));
+  CRC(cudaMemset(d->d_hist_pos, 0, sizeof(int32_t)));
+  CRC(cudaMallocHost((void**)&d->h_io, sizeof(int32_t) * 2 * kMaxBatch));
+  const size_t sb = attention_scratch_bytes(B, d->nh_l, d->nkv_l, d->hd, d->S);
+  CRC(cudaMalloc(&d->attn_scratch, sb));
+  CRC(cudaMemset(d->attn_scratch, 0, sb));
+  if (c.flags & TB_DECODER_NO_GRAPH) {
+    CR(dalloc(&d->dbg_embed, (size_t)H)); CR(dalloc(&d->dbg_normed, (size_t)B * H));
+    CR(dalloc(&d->dbg_qkv, (size_t)B * d->tq_l)); CR(dalloc(&d->dbg_attn, (size_t)d->q_dim_l));
+    CR(dalloc(&d->dbg_x_attn, (size_t)H)); CR(dalloc(&d->dbg_h, (size_t)d->I_l));
+    CR(dalloc(&d->dbg_x_out, (size_t)H));
+  }
+  // Warm-up with an out-of-range token: every kernel runs once (function attributes get
+  // set outside of any graph capture), nothing is written to the KV cache, logits stay 0.
+  if (tp == 1) {
+    int64_t tok = -1, off = 0;
+    const bool g = d->use_graph;
+    d->use_graph = false;
+    const int flags = d->cfg.flags;
+    d->cfg.flags &= ~TB_DECODER_NO_GRAPH;
+    s = feed_and_step(d, &tok, &off, 1);
+    d->cfg.flags = flags;
+    d->use_graph = g;
+    if (s != TB_OK) return fin(s);
+    CRC(cudaStreamSynchronize(d->stream));
+  }
+#undef CR
+#undef CRC
+  *out = d;
+  return TB_OK;
+}
+
+void tb_decoder_destroy(tb_decoder* d) {
+  if (!d) return;
+  if (d->stream) cudaStreamSynchronize(d->stream);
+  for (int i = 0; i <= kMaxBatch; ++i) {
+    if (d->graphs[i]) cudaGraphExecDestroy(d->graphs[i]);
+    if (d->graphs_greedy[i]) cudaGraphExecDestroy(d->graphs_greedy[i]);
+  }
+  if (d->tpst) tp_destroy(d->tpst);
+  cudaFree(d->embed); cudaFree(d->final_norm_w); cudaFree(d->lm_w); cudaFree(d->lm_s);
+  for (LayerDev& o : d->layers) {
+    cudaFree(o.input_norm_w); cudaFree(o.qkv_w); cudaFree(o.qkv_s); cudaFree(o.o_w); cudaFree(o.o_s);
+    cudaFree(o.post_norm_w); cudaFree(o.gate_w); cudaFree(o.gate_s); cudaFree(o.up_w); cudaFree(o.up_s);
+    cudaFree(o.down_w); cudaFree(o.down_s); cudaFree(o.qkv_b);
+  }
+  cudaFree(d->cos_t); cudaFree(d->sin_t); cudaFree(d->k_cache); cudaFree(d->v_cache);
+  cudaFree(d->x); cudaFree(d->qkv); cudaFree(d->attn); cudaFree(d->h); cudaFree(d->logits);
+  cudaFree(d->partial); cudaFree(d->logits_l);
+  cudaFree(d->d_tokens); cudaFree(d->d_offsets); cudaFree(d->d_eff); cudaFree(d->d_hist); cudaFree(d->d_hist_pos);
+  cudaFreeHost(d->h_io); cudaFreeHost(d->h_feed);
+  cudaFree(d->attn_scratch);
+  cudaFree(d->dbg_embed); cudaFree(d->dbg_normed); cudaFree(d->dbg_qkv); cudaFree(d->dbg_attn);
+  cudaFree(d->dbg_x_attn); cudaFree(d->dbg_h); cudaFree(d->dbg_x_out);
+  if (d->stream) cudaStreamDestroy(d->stream);
+  delete d;
+}
+
+tb_status tb_decoder_step_batch(tb_decoder* d, const int64_t* token_ids, const int64_t* offsets,
+                                int32_t batch, float* logits_host) {
+  TB_TRY(check_alive(d, "tb_decoder_step_batch"));
+  if (!token_ids || !offsets) return fail(TB_ERR_ARG, "tb_decoder_step_batch: null tokens/offsets");
+  if (batch < 1 || batch > d->B) return fail(TB_ERR_ARG, "tb_decoder_step_batch: batch %d outside [1, max_batch=%d]", batch, d->B);
+  TB_TRY(feed_and_step(d, token_ids, offsets, batch));
+  if (logits_host)
+    DEC_CUDA(d, cudaMemcpyAsync(logits_host, d->logits, sizeof(float) * batch * d->V, cudaMemcpyDeviceToHost, d->stream));
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  return TB_OK;
+}
+
+tb_status tb_decoder_step(tb_decoder* d, int64_t token_id, int64_t offset, float* logits_host) {
+  return tb_decoder_step_batch(d, &token_id, &offset, 1, logits_host);
+}
+
+tb_status tb_decoder_prefill_tokens(tb_decoder* d, const int64_t* tokens, int64_t n,
+                                    int64_t start_offset, int64_t* end_offset) {
+  TB_TRY(check_alive(d, "tb_decoder_prefill_tokens"));
+  if (n == 0) {  // src/llm/decoder.rs:432-434
+    if (end_offset) *end_offset = start_offset;
+    return TB_OK;
+  }
+  if (!tokens || n < 0 || start_offset < 0) return fail(TB_ERR_ARG, "tb_decoder_prefill_tokens: bad arguments");
+  if (start_offset + n > d->S)
+    return fail(TB_ERR_ARG, "prefill %lld tokens at offset %lld exceeds max_seq_len %lld", (long long)n, (long long)start_offset, (long long)d->S);
+  if (n > d->feed_cap) {
+    cudaFreeHost(d->h_feed);
+    d->h_feed = nullptr;
+    d->feed_cap = 0;
+    DEC_CUDA(d, cudaMallocHost((void**)&d->h_feed, sizeof(int32_t) * 2 * n));
+    d->feed_cap = n;
+  }
+  for (int64_t i = 0; i < n; ++i) {
+    d->h_feed[2 * i] = clamp_i32(tokens[i]);
+    d->h_feed[2 * i + 1] = clamp_i32(start_offset + i);
+    note_kv(d, tokens[i], start_offset + i);
+  }
+  d->last_batch = 1;
+  for (int64_t i = 0; i < n; ++i) {
+    DEC_CUDA(d, cudaMemcpyAsync(d->d_tokens, d->h_feed + 2 * i, sizeof(int32_t), cudaMemcpyHostToDevice, d->stream));
+    DEC_CUDA(d, cudaMemcpyAsync(d->d_offsets, d->h_feed + 2 * i + 1, sizeof(int32_t), cudaMemcpyHostToDevice, d->stream));
+    TB_TRY(run_step(d, 1, false));
+  }
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  if (end_offset) *end_offset = start_offset + n;
+  return TB_OK;
+}
+
+tb_status tb_decoder_prefill(tb_decoder* d, const int64_t* tokens, int64_t n, float* logits_host) {
+  TB_TRY(check_alive(d, "tb_decoder_prefill"));
+  if (n <= 0 || !tokens) return fail(TB_ERR_ARG, "empty prefill");
+  if (n > d->S) return fail(TB_ERR_ARG, "prefill exceeds max_seq_len");
+  TB_TRY(tb_decoder_prefill_tokens(d, tokens, n, 0, nullptr));
+  if (logits_host) return tb_decoder_get_logits(d, logits_host);
+  return TB_OK;
+}
+
+tb_status tb_decoder_verify_tokens(tb_decoder* d, int64_t start_offset, const int64_t* tokens,
+                                   int64_t n, float* logits_host) {
+  TB_TRY(check_alive(d, "tb_decoder_verify_tokens"));
+  if (n == 0) return TB_OK;
+  if (!tokens || !logits_host || n < 0 || start_offset < 0) return fail(TB_ERR_ARG, "tb_decoder_verify_tokens: bad arguments");
+  if (start_offset + n > d->S) return fail(TB_ERR_ARG, "verify exceeds max_seq_len");
+  for (int64_t i = 0; i < n; ++i) {
+    const int64_t off = start_offset + i;
+    TB_TRY(feed_and_step(d, tokens + i, &off, 1));
+    DEC_CUDA(d, cudaMemcpyAsync(logits_host + i * d->V, d->logits, sizeof(float) * d->V, cudaMemcpyDeviceToHost, d->stream));
+  }
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  return TB_OK;
+}
+
+tb_status tb_decoder_reset_kv_cache(tb_decoder* d) {
+  TB_TRY(check_alive(d, "tb_decoder_reset_kv_cache"));
+  const int64_t used = d->kv_used < d->S ? d->kv_used : d->S;
+  if (used == 0) return TB_OK;  // src/llm/decoder.rs:452-455
+  const size_t pitch = (size_t)d->S * d->hd * sizeof(float);
+  const size_t width = (size_t)used * d->hd * sizeof(float);
+  const size_t rows = (size_t)d->L * d->B * d->nkv_l;
+  DEC_CUDA(d, cudaMemset2DAsync(d->k_cache, pitch, 0, width, rows, d->stream));
+  DEC_CUDA(d, cudaMemset2DAsync(d->v_cache, pitch, 0, width, rows, d->stream));
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  d->kv_used = 0;
+  return TB_OK;
+}
+
+tb_status tb_decoder_copy_kv_cache_from(tb_decoder* d, const float* const* k, const float* const* v,
+                                        int32_t num_given, int64_t seq_len, int64_t src_max_len,
+                                        int32_t seq, tb_space space) {
+  TB_TRY(check_alive(d, "tb_decoder_copy_kv_cache_from"));
+  if (!k || !v || num_given < 0 || seq < 0 || seq >= d->B) return fail(TB_ERR_ARG, "tb_decoder_copy_kv_cache_from: bad arguments");
+  if (seq_len < 0 || seq_len > d->S || seq_len > src_max_len) return fail(TB_ERR_ARG, "KV cache copy out of bounds");
+  const int nl = num_given < d->L ? num_given : d->L;  // src/llm/decoder.rs:486
+  const size_t spitch = (size_t)src_max_len * d->hd * sizeof(float);
+  const size_t dpitch = (size_t)d->S * d->hd * sizeof(float);
+  const size_t width = (size_t)seq_len * d->hd * sizeof(float);
+  const cudaMemcpyKind kind = space == TB_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+  if (seq_len > 0)
+    for (int l = 0; l < nl; ++l) {
+      if (!k[l] || !v[l]) return fail(TB_ERR_ARG, "tb_decoder_copy_kv_cache_from: null layer tensor");
+      const size_t base = (size_t)l * kv_layer_stride(d) + (size_t)seq * d->nkv_l * d->S * d->hd;
+      DEC_CUDA(d, cudaMemcpy2DAsync(d->k_cache + base, dpitch, k[l], spitch, width, d->nkv_l, kind, d->stream));
+      DEC_CUDA(d, cudaMemcpy2DAsync(d->v_cache + base, dpitch, v[l], spitch, width, d->nkv_l, kind, d->stream));
+    }
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  if (seq_len > d->kv_used) d->kv_used = seq_len;  // src/llm/decoder.rs:521
+  return TB_OK;
+}
+
+tb_status tb_decoder_read_kv_cache(tb_decoder* d, int32_t layer, int32_t seq, float* k_host, float* v_host) {
+  TB_TRY(check_alive(d, "tb_decoder_read_kv_cache"));
+  if (layer < 0 || layer >= d->L || seq < 0 || seq >= d->B || !k_host || !v_host) return fail(TB_ERR_ARG, "tb_decoder_read_kv_cache: bad arguments");
+  const size_t n = (size_t)d->nkv_l * d->S * d->hd;
+  const size_t base = (size_t)layer * kv_layer_stride(d) + (size_t)seq * n;
+  DEC_CUDA(d, cudaMemcpyAsync(k_host, d->k_cache + base, n * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
+  DEC_CUDA(d, cudaMemcpyAsync(v_host, d->v_cache + base, n * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  return TB_OK;
+}
+
+int64_t tb_decoder_kv_len(const tb_decoder* d) { return d ? d->kv_used : 0; }
+
+tb_status tb_decoder_get_logits(tb_decoder* d, float* logits_host) {
+  TB_TRY(check_alive(d, "tb_decoder_get_logits"));
+  if (!logits_host) return fail(TB_ERR_ARG, "tb_decoder_get_logits: null buffer");
+  DEC_CUDA(d, cudaMemcpyAsync(logits_host, d->logits, sizeof(float) * d->last_batch * d->V, cudaMemcpyDeviceToHost, d->stream));
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  return TB_OK;
+}
+
+const float* tb_decoder_logits_device(const tb_decoder* d) { return d ? d->logits : nullptr; }
+
+tb_status tb_decoder_generate_greedy(tb_decoder* d, int64_t first_token, int64_t start_offset,
+                                     int64_t n_new, int64_t* out_tokens) {
+  TB_TRY(check_alive(d, "tb_decoder_generate_greedy"));
+  if (n_new == 0) return TB_OK;
+  if (!out_tokens || n_new < 0 || start_offset < 0) return fail(TB_ERR_ARG, "tb_decoder_generate_greedy: bad arguments");
+  if (start_offset + n_new > d->S) return fail(TB_ERR_ARG, "generate exceeds max_seq_len");
+  if (n_new > d->hist_cap) {
+    cudaFree(d->d_hist);
+    d->d_hist = nullptr;
+    d->hist_cap = 0;
+    TB_TRY(dalloc(&d->d_hist, (size_t)n_new));
+    d->hist_cap = n_new;
+    // the graph holds the history pointer: rebuild
+    for (int i = 0; i <= kMaxBatch; ++i)
+      if (d->graphs_greedy[i]) { cudaGraphExecDestroy(d->graphs_greedy[i]); d->graphs_greedy[i] = nullptr; }
+  }
+  d->h_io[0] = clamp_i32(first_token);
+  d->h_io[kMaxBatch] = clamp_i32(start_offset);
+  DEC_CUDA(d, cudaMemcpyAsync(d->d_tokens, d->h_io, sizeof(int32_t), cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(d, cudaMemcpyAsync(d->d_offsets, d->h_io + kMaxBatch, sizeof(int32_t), cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(d, cudaMemsetAsync(d->d_hist_pos, 0, sizeof(int32_t), d->stream));
+  d->last_batch = 1;
+  for (int64_t i = 0; i < n_new; ++i) TB_TRY(run_step(d, 1, true));
+  std::vector<int32_t> hist((size_t)n_new);
+  DEC_CUDA(d, cudaMemcpyAsync(hist.data(), d->d_hist, sizeof(int32_t) * n_new, cudaMemcpyDeviceToHost, d->stream));
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  int64_t tok = first_token;
+  for (int64_t i = 0; i < n_new; ++i) {
+    note_kv(d, tok, start_offset + i);
+    out_tokens[i] = hist[i];
+    tok = hist[i];
+  }
+  return TB_OK;
+}
+
+tb_status tb_decoder_decode_greedy(tb_decoder* d, int64_t token_id, int64_t offset, int64_t* next_token) {
+  if (!next_token) return fail(TB_ERR_ARG, "tb_decoder_decode_greedy: null out");
+  if (d && (offset < 0 || offset >= d->S || token_id < 0 || token_id >= d->V)) {
+    // zero logits -> argmax 0 (src/llm/decoder.rs:1066-1078, 895-906)
+    TB_TRY(tb_decoder_step(d, token_id, offset, nullptr));
+    *next_token = 0;
+    return TB_OK;
+  }
+  return tb_decoder_generate_greedy(d, token_id, offset, 1, next_token);
+}
+
+tb_status tb_decoder_debug_stage(tb_decoder* d, const char* name, float* out_host, int64_t cap, int64_t* n) {
+  TB_TRY(check_alive(d, "tb_decoder_debug_stage"));
+  if (!name || !n) return fail(TB_ERR_ARG, "tb_decoder_debug_stage: null argument");
+  if (!(d->cfg.flags & TB_DECODER_NO_GRAPH))
+    return fail(TB_ERR_UNSUPPORTED, "debug stages are recorded only by a decoder created with TB_DECODER_NO_GRAPH");
+  const float* src = nullptr;
+  int64_t cnt = 0;
+  if (!strcmp(name, "embed")) { src = d->dbg_embed; cnt = d->H; }
+  else if (!strcmp(name, "normed")) { src = d->dbg_normed; cnt = d->H; }
+  else if (!strcmp(name, "qkv")) { src = d->dbg_qkv; cnt = d->tq_l; }
+  else if (!strcmp(name, "attn")) { src = d->dbg_attn; cnt = d->q_dim_l; }
+  else if (!strcmp(name, "x_attn")) { src = d->dbg_x_attn; cnt = d->H; }
+  else if (!strcmp(name, "h")) { src = d->dbg_h; cnt = d->I_l; }
+  else if (!strcmp(name, "x_out")) { src = d->dbg_x_out; cnt = d->H; }
+  else return fail(TB_ERR_ARG, "unknown stage '%s'", name);
+  *n = cnt;
+  if (out_host && cap > 0) {
+    const int64_t m = cap < cnt ? cap : cnt;
+    DEC_CUDA(d, cudaMemcpyAsync(out_host, src, sizeof(float) * m, cudaMemcpyDeviceToHost, d->stream));
+    DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  }
+  return TB_OK;
+}
+
+tb_status tb_decoder_step_timed(tb_decoder* d, int64_t token_id, int64_t offset, float* logits_host, float ms_out[3]) {
+  TB_TRY(check_alive(d, "tb_decoder_step_timed"));
+  if (!ms_out) return fail(TB_ERR_ARG, "tb_decoder_step_timed: null ms_out");
+  cudaEvent_t ev[4];
+  for (auto& e : ev) DEC_CUDA(d, cudaEventCreate(&e));
+  d->h_io[0] = clamp_i32(token_id);
+  d->h_io[kMaxBatch] = clamp_i32(offset);
+  note_kv(d, token_id, offset);
+  d->last_batch = 1;
+  DEC_CUDA(d, cudaMemcpyAsync(d->d_tokens, d->h_io, sizeof(int32_t), cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(d, cudaMemcpyAsync(d->d_offsets, d->h_io + kMaxBatch, sizeof(int32_t), cudaMemcpyHostToDevice, d->stream));
+  DEC_CUDA(d, cudaEventRecord(ev[0], d->stream));
+  // direct launches (no graph) so that an event can sit in front of lm_head
+  tb_status s = enqueue_step(d, 1, false, ev[1]);
+  if (s == TB_OK) {
+    DEC_CUDA(d, cudaEventRecord(ev[2], d->stream));
+    if (logits_host)
+      DEC_CUDA(d, cudaMemcpyAsync(logits_host, d->logits, sizeof(float) * d->V, cudaMemcpyDeviceToHost, d->stream));
+    DEC_CUDA(d, cudaEventRecord(ev[3], d->stream));
+    DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+    cudaEventElapsedTime(&ms_out[0], ev[0], ev[1]);
+    cudaEventElapsedTime(&ms_out[1], ev[1], ev[2]);
+    cudaEventElapsedTime(&ms_out[2], ev[2], ev[3]);
+  }
+  for (auto& e : ev) cudaEventDestroy(e);
+  return s;
+}
+
+int32_t tb_decoder_is_device_lost(const tb_decoder* d) { return d && d->device_lost ? 1 : 0; }
+void tb_decoder_mark_device_lost(tb_decoder* d) { if (d) d->device_lost = true; }
+int32_t tb_decoder_launches_per_step(const tb_decoder* d) { return d ? d->launches_per_step : 0; }
+void* tb_decoder_stream(const tb_decoder* d) { return d ? (void*)d->stream : nullptr; }
+
+}  // extern "C"

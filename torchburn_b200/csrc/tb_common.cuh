@@ -1,0 +1,106 @@
+// Shared host/device helpers of the torchburn_b200 library.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/torchburn_b200.h"
+
+namespace tb {
+
+// Thread-local last-error message behind tb_last_error_string().
+void set_error(const char* fmt, ...);
+tb_status fail(tb_status code, const char* fmt, ...);
+
+#define TB_CUDA_TRY(expr)                                                                  \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess) {                                                               \
+      return ::tb::fail(_e == cudaErrorMemoryAllocation ? TB_ERR_OOM : TB_ERR_CUDA,        \
+                        "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__,  \
+                        __LINE__);                                                         \
+    }                                                                                      \
+  } while (0)
+
+#define TB_TRY(expr)                   \
+  do {                                 \
+    tb_status _s = (expr);             \
+    if (_s != TB_OK) return _s;        \
+  } while (0)
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+// Copies `bytes` from host or device memory into a fresh device allocation.
+tb_status upload(void** dst, const void* src, size_t bytes, tb_space space);
+
+// ---- argument blocks of the kernel launchers (all pointers DEVICE) ----------
+
+// One grouped-INT4 projection y = W x (+ epilogue).  See w4_gemv.cu.
+struct GemvArgs {
+  const float* x = nullptr;        // [m, k]
+  const uint8_t* w = nullptr;      // [n, k/2]
+  const float* scales = nullptr;   // [n, k/g]
+  const float* bias = nullptr;     // [n] or null
+  const uint8_t* w2 = nullptr;     // SwiGLU: the "up" matrix (w is "gate")
+  const float* scales2 = nullptr;
+  const float* bias2 = nullptr;
+  const float* norm_w = nullptr;   // fused RMSNorm of x before the product: [k] or null
+  float eps = 0.f;
+  const float* resid = nullptr;    // out = resid + y when not null: [m, n]
+  float* out = nullptr;            // [m, n]
+  float* x_normed_out = nullptr;   // optional copy of the normalised x (debug): [m, k]
+  int m = 1;
+  int64_t n = 0, k = 0;
+  int g = 32;
+  bool pdl = false;                // launch with programmatic stream serialization
+};
+
+tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream);
+
+struct AttnArgs {
+  const float* qkv = nullptr;   // [b, (Hq+2Hkv)*d], before RoPE
+  float* k_cache = nullptr;     // [b, Hkv, max_seq, d]
+  float* v_cache = nullptr;
+  const float* cos_t = nullptr; // [max_seq, d] (or [b, d] when per_call_tables)
+  const float* sin_t = nullptr;
+  const int32_t* offsets = nullptr;  // [b]
+  float* out = nullptr;         // [b, Hq*d]
+  void* scratch = nullptr;
+  float* q_rot_out = nullptr;   // optional: rotated q|k|v copy (debug) [b, (Hq+2Hkv)*d]
+  int batch = 1, num_heads = 0, num_kv_heads = 0, head_dim = 0;
+  int64_t max_seq_len = 0;
+  bool per_call_tables = false; // cos/sin hold one row per sequence instead of a table
+  bool pdl = false;
+};
+size_t attention_scratch_bytes(int batch, int num_heads, int num_kv_heads, int head_dim,
+                               int64_t max_seq_len);
+// Byte offset of the ticket counters inside the scratch block (they must be zero before the
+// first launch).
+size_t attention_counters_offset(int batch, int num_heads, int num_kv_heads, int head_dim,
+                                 int64_t max_seq_len, size_t* counter_bytes);
+// Tuning hook: force the positions per attention CTA (0 = automatic).
+void set_attention_chunk_override(int tc);
+tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream);
+
+tb_status launch_rms_norm(const float* x, const float* w, float* out, int64_t m, int64_t n,
+                          float eps, cudaStream_t stream);
+// x[b] = table[tokens[b]] and eff_offsets[b] = offsets[b] when token and offset are in range,
+// else x[b] = 0 and eff_offsets[b] = -1 (src/llm/decoder.rs:1066-1092).
+tb_status launch_embed_gather(const float* table, const int32_t* tokens, const int32_t* offsets,
+                              float* x, int32_t* eff_offsets, int batch, int64_t vocab,
+                              int64_t hidden, int64_t max_seq_len, bool pdl, cudaStream_t stream);
+tb_status launch_quantize_int4(const float* w, int64_t n, int64_t k, int g, uint8_t* packed,
+                               float* scales, cudaStream_t stream);
+// out_tokens[b] = first index of the maximum of logits[b] (src/llm/decoder.rs:895-906); when
+// next_offsets is not null, next_offsets[b] += 1 (feeds the next step of a generate loop).
+// When hist is not null, sequence 0's token is appended at hist[(*hist_pos)++].
+tb_status launch_argmax(const float* logits, int64_t vocab, int batch, int32_t* out_tokens,
+                        int32_t* next_offsets, int32_t* hist, int32_t* hist_pos,
+                        cudaStream_t stream);
+
+}  // namespace tb
