@@ -129,6 +129,22 @@ tb_status tb_attention_decode(const float* qkv, float* k_cache, float* v_cache,
  * of two in [32, 256]; 0 = choose from the shape).  Process-wide; plays the role
  * of TORCHBURN_ROWS_PER_WG, src/wgpu/backend.rs:428-437. */
 void tb_set_attention_chunk(int32_t positions);
+/* Tuning hook for the M = 1 GEMV kernels.  product_mode 1 (default): activations are
+ * rounded per 32-element block to 24-bit fixed point and multiplied with integer dot
+ * products; 0: fp32 products.  rows_per_warp in {0,1,2,4} and warps in {0,4,8} force
+ * the launch shape (0 = choose from the matrix size).  Process-wide. */
+void tb_set_gemv_tuning(int32_t product_mode, int32_t rows_per_warp, int32_t warps);
+/* Tuning hook for the persistent M = 1 kernel (one long-lived CTA per SM fed by a ring of
+ * bulk asynchronous copies): enabled 0 routes every product to the per-row-tile kernels;
+ * ctas_per_sm in {1, 2, ...}; ring_kb = shared-memory ring size per CTA (0 = default);
+ * elements_per_lane in {0, 16, 32} and groups in {0..4} force the split of K over lanes and
+ * the number of tiles a CTA works on at once (0 = choose from the shape). */
+void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb,
+                          int32_t elements_per_lane, int32_t groups);
+/* 1 after a bounded device-side wait ran out in any kernel of this library on the current
+ * device (the results of that launch are invalid), 0 otherwise, -1 if the flag could not
+ * be read.  Device-side waits never spin without a limit. */
+int32_t tb_device_fault_flag(void);
 
 /* ------------------------------------------------------------------------
  * QuantizedLinear (python/torchburn/quantization.py:756-869) as a handle.

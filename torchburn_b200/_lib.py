@@ -56,6 +56,9 @@ SIGNATURES = {
     "tb_attention_scratch_bytes": (_sz, [_i32, _i32, _i32, _i32, _i64]),
     "tb_attention_decode": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i64, _p]),
     "tb_set_attention_chunk": (None, [_i32]),
+    "tb_set_gemv_tuning": (None, [_i32, _i32, _i32]),
+    "tb_set_stream_tuning": (None, [_i32, _i32, _i32, _i32, _i32]),
+    "tb_device_fault_flag": (_i32, []),
     "tb_linear_create": (_i32, [_PP, _p, _p, _p, _i64, _i64, _i32, _i32]),
     "tb_linear_destroy": (None, [_p]),
     "tb_linear_forward": (_i32, [_p, _p, _i64, _p, _i32, _p]),

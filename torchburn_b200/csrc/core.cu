@@ -181,6 +181,14 @@ tb_status tb_attention_decode(const float* qkv, float* k_cache, float* v_cache,
 
 void tb_set_attention_chunk(int32_t tc) { set_attention_chunk_override(tc); }
 
+void tb_set_gemv_tuning(int32_t xmode, int32_t rows_per_warp, int32_t warps) { set_gemv_tuning(xmode, rows_per_warp, warps); }
+
+void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb, int32_t epl, int32_t groups) {
+  set_stream_tuning(enabled, ctas_per_sm, ring_kb, epl, groups);
+}
+
+int32_t tb_device_fault_flag(void) { return stream_fault_flag(); }
+
 /* ------------------------------------------------------------ QuantizedLinear */
 
 tb_status tb_linear_create(tb_linear** out, const uint8_t* qweight, const float* scales,

@@ -61,6 +61,15 @@ struct GemvArgs {
 };
 
 tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream);
+// Tuning hook: xmode 0 = fp32 products (M = 1 only), 1 = integer products; rows_per_warp /
+// warps force the launch shape of the M = 1 kernels (0 = automatic).
+void set_gemv_tuning(int xmode, int rows_per_warp, int warps);
+
+// Persistent TMA-ring kernel for M = 1 (w4_stream.cu).
+bool w4_stream_supported(const GemvArgs& a);
+tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream);
+void set_stream_tuning(int enabled, int ctas_per_sm, int ring_kb, int epl, int groups);
+int stream_fault_flag();
 
 struct AttnArgs {
   const float* qkv = nullptr;   // [b, (Hq+2Hkv)*d], before RoPE

@@ -22,6 +22,7 @@
 // these scalings are by powers of two, so every product is the bit-exact
 // fp32 product x * (code4 - 8) the reference computes.
 #include "tb_common.cuh"
+#include "w4_math.cuh"
 
 namespace tb {
 
@@ -111,11 +112,14 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // EPI: 0 = plain (+bias, +resid), 1 = SwiGLU of two matrices sharing x.
-// M activations rows, R weight rows per warp, WARPS warps per CTA.
-template <int M, int R, int WARPS, int EPI, bool NORM>
+// M activation rows, R weight rows per warp, WARPS warps per CTA,
+// XMODE: 0 = fp32 products, 1 = integer products (see above).
+template <int M, int R, int WARPS, int EPI, bool NORM, int XMODE>
 __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p) {
   constexpr int NW = (EPI == 1) ? 2 : 1;
-  extern __shared__ float4 xs4[];  // [M][kc / 4], XOR-swizzled per 32-element block
+  constexpr int XV = XMODE == 1 ? 7 : 8;  // 16-byte vectors of staged x per block
+  extern __shared__ uint4 xs[];  // XMODE 0: [M][kc/4] float4, XOR-swizzled per block
+                                 // XMODE 1: [M][7][kc/32] (vector-major, block-minor)
   __shared__ float s_red[kMaxM][WARPS];
 
   const int lane = threadIdx.x & 31;
@@ -124,6 +128,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
   const int64_t bpr = (int64_t)p.k >> 1;
   const int iters = (p.nb32 + 31) >> 5;
   const int iters_per_chunk = p.kc >> 10;
+  const int cb = p.kc >> 5;  // blocks per chunk
 
   // Row pointers; rows past the end are clamped for the loads and masked at the store.
   const uint8_t* wrow[NW][R];
@@ -194,31 +199,67 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
   const int kc4 = p.kc >> 2;
   for (int it = 0; it < iters; ++it) {
     if (it % iters_per_chunk == 0) {
-      // Stage the next chunk of activations: normalise, pre-scale by 16^-p, swizzle.
+      // Stage the next chunk of activations.
       if (it != 0) __syncthreads();
       const int k0 = it << 10;
-      const int kn4 = min(p.kc, p.k - k0) >> 2;
+      if (XMODE == 0) {
+        // normalise, pre-scale by 16^-p, swizzle
+        float4* xs4 = reinterpret_cast<float4*>(xs);
+        const int kn4 = min(p.kc, p.k - k0) >> 2;
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        const float4* xg = reinterpret_cast<const float4*>(p.x + (int64_t)m * p.k + k0);
-        for (int i = threadIdx.x; i < kn4; i += WARPS * 32) {
-          float4 v = xg[i];
-          if (NORM) {
-            const float4 nw = reinterpret_cast<const float4*>(p.norm_w + k0)[i];
-            v.x = (v.x * inv_rms[m]) * nw.x;
-            v.y = (v.y * inv_rms[m]) * nw.y;
-            v.z = (v.z * inv_rms[m]) * nw.z;
-            v.w = (v.w * inv_rms[m]) * nw.w;
-            if (p.x_normed_out != nullptr && blockIdx.x == 0)
-              reinterpret_cast<float4*>(p.x_normed_out + (int64_t)m * p.k + k0)[i] = v;
+        for (int m = 0; m < M; ++m) {
+          const float4* xg = reinterpret_cast<const float4*>(p.x + (int64_t)m * p.k + k0);
+          for (int i = threadIdx.x; i < kn4; i += WARPS * 32) {
+            float4 v = xg[i];
+            if (NORM) {
+              const float4 nw = reinterpret_cast<const float4*>(p.norm_w + k0)[i];
+              v.x = (v.x * inv_rms[m]) * nw.x;
+              v.y = (v.y * inv_rms[m]) * nw.y;
+              v.z = (v.z * inv_rms[m]) * nw.z;
+              v.w = (v.w * inv_rms[m]) * nw.w;
+              if (p.x_normed_out != nullptr && blockIdx.x == 0)
+                reinterpret_cast<float4*>(p.x_normed_out + (int64_t)m * p.k + k0)[i] = v;
+            }
+            const int e0 = (i & 1) * 4;  // position of v.x inside its 8-element word
+            v.x *= prescale_of(e0 + 0);
+            v.y *= prescale_of(e0 + 1);
+            v.z *= prescale_of(e0 + 2);
+            v.w *= prescale_of(e0 + 3);
+            const int blk = i >> 3, j = i & 7;
+            xs4[m * kc4 + blk * 8 + (j ^ (blk & 7))] = v;
           }
-          const int e0 = (i & 1) * 4;  // position of v.x inside its 8-element word
-          v.x *= prescale_of(e0 + 0);
-          v.y *= prescale_of(e0 + 1);
-          v.z *= prescale_of(e0 + 2);
-          v.w *= prescale_of(e0 + 3);
-          const int blk = i >> 3, j = i & 7;
-          xs4[m * kc4 + blk * 8 + (j ^ (blk & 7))] = v;
+        }
+      } else {
+        // normalise, then one thread per block: 24-bit fixed point digits
+        const int nblk = min(p.kc, p.k - k0) >> 5;
+#pragma unroll 1
+        for (int m = 0; m < M; ++m) {
+          for (int blk = threadIdx.x; blk < nblk; blk += WARPS * 32) {
+            const float4* xg = reinterpret_cast<const float4*>(p.x + (int64_t)m * p.k + k0) + blk * 8;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 t = xg[j];
+              if (NORM) {
+                const float4 nw = reinterpret_cast<const float4*>(p.norm_w + k0)[blk * 8 + j];
+                t.x = (t.x * inv_rms[m]) * nw.x;
+                t.y = (t.y * inv_rms[m]) * nw.y;
+                t.z = (t.z * inv_rms[m]) * nw.z;
+                t.w = (t.w * inv_rms[m]) * nw.w;
+                if (p.x_normed_out != nullptr && blockIdx.x == 0)
+                  reinterpret_cast<float4*>(p.x_normed_out + (int64_t)m * p.k + k0)[blk * 8 + j] = t;
+              }
+              v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+            }
+            uint32_t dig[24];
+            float sx, corr;
+            quantize_block(v, dig, sx, corr);
+            uint4* dst = xs + (size_t)m * 7 * cb + blk;
+#pragma unroll
+            for (int j = 0; j < 6; ++j)
+              dst[j * cb] = make_uint4(dig[4 * j], dig[4 * j + 1], dig[4 * j + 2], dig[4 * j + 3]);
+            dst[6 * cb] = make_uint4(__float_as_uint(sx), __float_as_uint(corr), 0u, 0u);
+          }
         }
       }
       __syncthreads();
@@ -229,16 +270,8 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
 
     const int bl = (it % iters_per_chunk) * 32 + lane;  // block index inside the chunk
     if (it * 32 + lane < p.nb32) {
-      if (M == 1) {
-        float4 xr[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) xr[j] = xs4[bl * 8 + (j ^ (bl & 7))];
-#pragma unroll
-        for (int q = 0; q < NW; ++q)
-#pragma unroll
-          for (int r = 0; r < R; ++r)
-            acc[q][0][r] = fmaf(dot32(wv[q][r], xr), sc[q][r], acc[q][0][r]);
-      } else {
+      if (XMODE == 0) {
+        const float4* xs4 = reinterpret_cast<const float4*>(xs);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
           float4 xr[8];
@@ -249,6 +282,26 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
 #pragma unroll
             for (int r = 0; r < R; ++r)
               acc[q][m][r] = fmaf(dot32(wv[q][r], xr), sc[q][r], acc[q][m][r]);
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          uint32_t xq[24];
+          const uint4* src = xs + (size_t)m * 7 * cb + bl;
+#pragma unroll
+          for (int j = 0; j < 6; ++j) {
+            const uint4 t = src[j * cb];
+            xq[4 * j] = t.x; xq[4 * j + 1] = t.y; xq[4 * j + 2] = t.z; xq[4 * j + 3] = t.w;
+          }
+          const uint4 tail = src[6 * cb];
+          const float sx = __uint_as_float(tail.x), corr = __uint_as_float(tail.y);
+#pragma unroll
+          for (int q = 0; q < NW; ++q)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const float d = fmaf(sx, idot32(wv[q][r], xq), corr);
+              acc[q][m][r] = fmaf(d, sc[q][r], acc[q][m][r]);
+            }
         }
       }
     }
@@ -292,14 +345,19 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
   }
 }
 
-template <int M, int R, int WARPS, int EPI, bool NORM>
+// Tuning state (process-wide): product mode and an optional forced launch shape.
+int g_xmode = 1;
+int g_force_r = 0, g_force_warps = 0;
+
+template <int M, int R, int WARPS, int EPI, bool NORM, int XMODE>
 tb_status launch_cfg(const GemvParams& p, bool pdl, cudaStream_t stream) {
-  auto kern = w4_gemv_kernel<M, R, WARPS, EPI, NORM>;
-  const size_t smem = (size_t)M * p.kc * sizeof(float);
+  auto kern = w4_gemv_kernel<M, R, WARPS, EPI, NORM, XMODE>;
+  const size_t smem = XMODE == 1 ? (size_t)M * 7 * (p.kc >> 5) * sizeof(uint4) : (size_t)M * p.kc * sizeof(float);
   static thread_local size_t configured[64] = {0};
   int dev = 0;
   TB_CUDA_TRY(cudaGetDevice(&dev));
-  if (smem > 48 * 1024 && (dev >= 64 || configured[dev] < smem)) {
+  // static + dynamic shared memory above 48 KB needs the opt-in, so opt in from 32 KB up
+  if (smem > 32 * 1024 && (dev >= 64 || configured[dev] < smem)) {
     TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 64) configured[dev] = smem;
   }
@@ -318,42 +376,68 @@ tb_status launch_cfg(const GemvParams& p, bool pdl, cudaStream_t stream) {
   return TB_OK;
 }
 
-template <int M, int EPI, bool NORM>
+template <int M, int EPI, bool NORM, int XMODE>
 tb_status launch_m(const GemvParams& p, bool pdl, cudaStream_t stream) {
-  // Rows per warp: more rows amortise the activation reads from shared memory;
-  // fewer rows give more warps when the matrix is small.
+  // Rows per warp: more rows amortise the activation reads from shared memory and keep
+  // more loads in flight; fewer rows give more warps when the matrix is small.
   const int sms = sm_count();
   if constexpr (M == 1) {
-    if constexpr (EPI == 1) {
-      if ((int64_t)p.n >= (int64_t)sms * 64) return launch_cfg<M, 2, 8, EPI, NORM>(p, pdl, stream);
-      return launch_cfg<M, 1, 8, EPI, NORM>(p, pdl, stream);
+    int r = 0, w = 8;
+    if (g_force_r > 0) {
+      r = g_force_r;
+      w = g_force_warps > 0 ? g_force_warps : 8;
+    } else if (EPI == 1) {
+      r = ((int64_t)p.n >= (int64_t)sms * 64) ? 2 : 1;
+    } else {
+      r = ((int64_t)p.n >= (int64_t)sms * 128) ? 4 : ((int64_t)p.n >= (int64_t)sms * 32 ? 2 : 1);
+      if (r == 1) w = 4;
     }
-    if ((int64_t)p.n >= (int64_t)sms * 128) return launch_cfg<M, 4, 8, EPI, NORM>(p, pdl, stream);
-    if ((int64_t)p.n >= (int64_t)sms * 32) return launch_cfg<M, 2, 8, EPI, NORM>(p, pdl, stream);
-    return launch_cfg<M, 1, 4, EPI, NORM>(p, pdl, stream);
+    if (EPI == 1 && r == 4) r = 2;
+    if (w == 4) {
+      if (r == 1) return launch_cfg<M, 1, 4, EPI, NORM, XMODE>(p, pdl, stream);
+      if (r == 2) return launch_cfg<M, 2, 4, EPI, NORM, XMODE>(p, pdl, stream);
+      if constexpr (EPI == 0) return launch_cfg<M, 4, 4, EPI, NORM, XMODE>(p, pdl, stream);
+    }
+    if (r == 1) return launch_cfg<M, 1, 8, EPI, NORM, XMODE>(p, pdl, stream);
+    if (r == 2) return launch_cfg<M, 2, 8, EPI, NORM, XMODE>(p, pdl, stream);
+    if constexpr (EPI == 0) return launch_cfg<M, 4, 8, EPI, NORM, XMODE>(p, pdl, stream);
+    return launch_cfg<M, 2, 8, EPI, NORM, XMODE>(p, pdl, stream);
   } else if constexpr (EPI == 1) {
-    return launch_cfg<M, 1, 8, EPI, NORM>(p, pdl, stream);
+    return launch_cfg<M, 1, 8, EPI, NORM, XMODE>(p, pdl, stream);
   } else {
-    return launch_cfg<M, 2, 8, EPI, NORM>(p, pdl, stream);
+    return launch_cfg<M, 2, 8, EPI, NORM, XMODE>(p, pdl, stream);
   }
 }
 
-template <int EPI, bool NORM>
-tb_status launch_epi(int m, const GemvParams& p, bool pdl, cudaStream_t stream) {
+template <int EPI, bool NORM, int XMODE>
+tb_status launch_x(int m, const GemvParams& p, bool pdl, cudaStream_t stream) {
   switch (m) {
-    case 1: return launch_m<1, EPI, NORM>(p, pdl, stream);
-    case 2: return launch_m<2, EPI, NORM>(p, pdl, stream);
-    case 3: return launch_m<3, EPI, NORM>(p, pdl, stream);
-    case 4: return launch_m<4, EPI, NORM>(p, pdl, stream);
-    case 5: return launch_m<5, EPI, NORM>(p, pdl, stream);
-    case 6: return launch_m<6, EPI, NORM>(p, pdl, stream);
-    case 7: return launch_m<7, EPI, NORM>(p, pdl, stream);
-    case 8: return launch_m<8, EPI, NORM>(p, pdl, stream);
+    case 1: return launch_m<1, EPI, NORM, XMODE>(p, pdl, stream);
+    case 2: return launch_m<2, EPI, NORM, XMODE>(p, pdl, stream);
+    case 3: return launch_m<3, EPI, NORM, XMODE>(p, pdl, stream);
+    case 4: return launch_m<4, EPI, NORM, XMODE>(p, pdl, stream);
+    case 5: return launch_m<5, EPI, NORM, XMODE>(p, pdl, stream);
+    case 6: return launch_m<6, EPI, NORM, XMODE>(p, pdl, stream);
+    case 7: return launch_m<7, EPI, NORM, XMODE>(p, pdl, stream);
+    case 8: return launch_m<8, EPI, NORM, XMODE>(p, pdl, stream);
   }
   return fail(TB_ERR_SHAPE, "w4 gemv: m=%d outside 1..8", m);
 }
 
+template <int EPI, bool NORM>
+tb_status launch_epi(int m, const GemvParams& p, bool pdl, cudaStream_t stream) {
+  // The fp32 product path is kept for M = 1 (A/B measurements, exact-fp32 option).
+  if (g_xmode == 0 && m == 1) return launch_m<1, EPI, NORM, 0>(p, pdl, stream);
+  return launch_x<EPI, NORM, 1>(m, p, pdl, stream);
+}
+
 }  // namespace
+
+void set_gemv_tuning(int xmode, int rows_per_warp, int warps) {
+  g_xmode = xmode != 0 ? 1 : 0;
+  g_force_r = rows_per_warp;
+  g_force_warps = warps;
+}
 
 // Rows of x beyond 8 are processed in slices of up to 8 (the weights are
 // streamed once per slice).
@@ -383,6 +467,8 @@ tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
   p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
   p.ng = (int)(a.k / a.g);
   const int k_pad = (int)((a.k + 1023) / 1024 * 1024);
+
+  if (w4_stream_supported(a)) return launch_w4_stream(a, stream);
 
   for (int m0 = 0; m0 < a.m; m0 += kMaxM) {
     const int mc = a.m - m0 < kMaxM ? a.m - m0 : kMaxM;
