@@ -443,6 +443,8 @@ def run_gpu(args):
     if rank != 0:
         if tp > 1:
             dist.barrier()
+            dec.close()
+            dist.destroy_process_group()
         return
     # ---- rank 0: roofline of the dominant kernel, config-1 GEMV, CPU baseline ----
     peak, peak_kind = measured_peak()
@@ -476,9 +478,11 @@ def run_gpu(args):
     }
     if args.cpu_baseline:
         line["cpu_baseline"] = {k: v for k, v in cpu_decode_sample(c, CONTEXT).items() if k != "ms_per_step"}
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
     if tp > 1:
         dist.barrier()
+        dec.close()
+        dist.destroy_process_group()
 
 
 def lib_stream(tb, dec):

@@ -1,0 +1,87 @@
+"""Tensor-parallel decoder on 2 GPUs (skipped on a single-GPU box): one process per GPU
+over NCCL; the fused peer-memory all-reduce and the plain-NCCL path must both reproduce
+the single-GPU decoder and the oracle."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _rank_main(rank, world, port, q, nccl_only):
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.dirname(HERE))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import torchburn_b200 as tb
+        from helpers import max_rel_err, synth_model
+        from oracle import oracle as o
+        from torchburn_b200.tp import init_tensor_parallel
+        from tp_helpers import shard_model
+
+        cfg = dict(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_layers=3, num_heads=8,
+                   num_kv_heads=4, head_dim=64, group_size=32, max_seq_len=64, rms_norm_eps=1e-6, rope_theta=5e5)
+        embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 3, o.quantize_int4_grouped, qkv_bias=True)
+        layers_r, lw_r, ls_r = shard_model(tb, cfg, layers, lm_w, lm_s, rank, world)
+        order = ["input_norm_w", "qkv_w", "qkv_s", "o_w", "o_s", "post_norm_w", "gate_w", "gate_s", "up_w", "up_s",
+                 "down_w", "down_s", "qkv_b"]
+        B = 3
+        dec = tb.B200QwenDecoder(embed, [[lw[k] for k in order] for lw in layers_r], fnorm, lw_r, ls_r,
+                                 cfg["num_layers"], cfg["hidden_size"], cfg["intermediate_size"], cfg["num_heads"],
+                                 cfg["num_kv_heads"], cfg["head_dim"], cfg["group_size"], cfg["rms_norm_eps"],
+                                 cfg["max_seq_len"], cfg["rope_theta"], max_batch=B, tp_size=world, tp_rank=rank,
+                                 vocab_size=cfg["vocab_size"], nccl_only=nccl_only)
+        init_tensor_parallel(dec, dist, torch.device("cuda", rank), fused=not nccl_only)
+        ref = o.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+        worst = 0.0
+        toks = [3, 500, 17, 17, 255, 9, 1000, 1]
+        for off, tok in enumerate(toks):
+            worst = max(worst, max_rel_err(dec.step(tok, off), ref.step(tok, off)))
+        # batched step: three sequences at once against three oracles
+        refs = [o.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s) for _ in range(B)]
+        dec.reset_kv_cache()
+        for off in range(4):
+            tk = [(7 * off + 11 * b + 1) % cfg["vocab_size"] for b in range(B)]
+            got = dec.step_batch(tk, [off] * B)
+            for b in range(B):
+                worst = max(worst, max_rel_err(got[b], refs[b].step(tk[b], off)))
+        fault = tb.lib().tb_device_fault_flag()
+        q.put((rank, worst, fault))
+        dec.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("nccl_only", [False, True])
+def test_tp2_decoder_matches_oracle(nccl_only):
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("no CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + (os.getpid() % 90) + (50 if nccl_only else 0)
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, nccl_only)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, worst, fault in results:
+        assert worst < 1e-3, (rank, worst)
+        assert fault == 0

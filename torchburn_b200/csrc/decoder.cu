@@ -163,10 +163,10 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x = d->attn; a.w = W.o_w; a.scales = W.o_s; a.m = b; a.n = d->H; a.k = d->q_dim_l; a.g = d->G;
       a.pdl = pdl && !debug;
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
-      else { a.out = d->partial; }
+      else { a.out = tp_partial_buffer(d->tpst, d->partial); }
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
-      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, d->partial, d->x, b, d->H, st, &launches)); }
+      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches)); }
     }
     if (dbg) TB_TRY(snap(d->dbg_x_attn, d->x, d->H));
     {  // H + I: RMSNorm fused into the gate/up projection with the SwiGLU epilogue
@@ -183,10 +183,10 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x = d->h; a.w = W.down_w; a.scales = W.down_s; a.m = b; a.n = d->H; a.k = d->I_l; a.g = d->G;
       a.pdl = pdl && !debug;
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
-      else { a.out = d->partial; }
+      else { a.out = tp_partial_buffer(d->tpst, d->partial); }
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
-      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, d->partial, d->x, b, d->H, st, &launches)); }
+      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches)); }
     }
     if (dbg) TB_TRY(snap(d->dbg_x_out, d->x, d->H));
   }
@@ -679,6 +679,24 @@ tb_status tb_decoder_step_timed(tb_decoder* d, int64_t token_id, int64_t offset,
   }
   for (auto& e : ev) cudaEventDestroy(e);
   return s;
+}
+
+tb_status tb_decoder_tp_init(tb_decoder* d, const uint8_t id[128], tb_allgather_fn allgather, void* user) {
+  TB_TRY(check_alive(d, "tb_decoder_tp_init"));
+  if (!id) return fail(TB_ERR_ARG, "tb_decoder_tp_init: null id");
+  if (d->tp < 2) return fail(TB_ERR_ARG, "tb_decoder_tp_init: the decoder was created with tp_size 1");
+  if (d->tpst) return fail(TB_ERR_ARG, "tb_decoder_tp_init: already initialised");
+  TB_TRY(tp_create(&d->tpst, d->rank, d->tp, id, (size_t)d->B * d->H, allgather, user,
+                   (d->cfg.flags & TB_DECODER_NCCL_ONLY) != 0));
+  // warm-up with an out-of-range token (collective: every rank runs it)
+  int64_t tok = -1, off = 0;
+  const bool g = d->use_graph;
+  d->use_graph = false;
+  tb_status s = feed_and_step(d, &tok, &off, 1);
+  d->use_graph = g;
+  if (s != TB_OK) return s;
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  return TB_OK;
 }
 
 int32_t tb_decoder_is_device_lost(const tb_decoder* d) { return d && d->device_lost ? 1 : 0; }

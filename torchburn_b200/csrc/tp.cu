@@ -1,25 +1,322 @@
-// Tensor-parallel exchange (placeholder until the communicator is wired in).
+// Tensor-parallel exchange steps of the decoder.  The reference has no multi-device
+// code; this follows the Megatron layout: after each row-parallel projection (o_proj,
+// down) the ranks' partial sums [batch, hidden] are added up and added to the residual
+// stream, and the vocabulary-sharded logits are gathered.
+//
+// Two implementations of the sum:
+//  * ncclAllReduce (the baseline; NCCL is loaded at run time with dlopen so that a process
+//    that already carries an NCCL - e.g. through torch - shares it), followed by the
+//    residual add;
+//  * a one-shot kernel over peer memory: the projection writes its partial straight into a
+//    buffer that every rank has mapped (cudaIpc), a flag per rank announces it, and each
+//    rank reads all partials over NVLink with plain loads, adds them in rank order (so every
+//    rank holds bit-identical sums) and applies the residual - one launch, no extra
+//    pass over the data.  Every wait on a peer's flag is bounded; when it runs out the
+//    kernel raises an error word and returns.
+#include <dlfcn.h>
+
+#include <cstring>
+#include <vector>
+
 #include "tp.cuh"
 
 namespace tb {
 
-struct TpState { int dummy; };
+namespace {
 
-tb_status tp_allreduce_residual(TpState* st, const float*, float*, int, int64_t, cudaStream_t, int*) {
-  (void)st;
-  return fail(TB_ERR_NCCL, "tensor-parallel decoder used before tb_decoder_tp_init");
+struct NcclId { char internal[128]; };
+typedef void* nccl_comm_t;
+typedef int (*fn_get_unique_id)(NcclId*);
+typedef int (*fn_comm_init_rank)(nccl_comm_t*, int, NcclId, int);
+typedef int (*fn_comm_destroy)(nccl_comm_t);
+typedef int (*fn_all_reduce)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t);
+typedef int (*fn_all_gather)(const void*, void*, size_t, int, nccl_comm_t, cudaStream_t);
+typedef int (*fn_group)(void);
+typedef const char* (*fn_err_string)(int);
+
+struct NcclApi {
+  void* lib = nullptr;
+  fn_get_unique_id get_unique_id = nullptr;
+  fn_comm_init_rank comm_init_rank = nullptr;
+  fn_comm_destroy comm_destroy = nullptr;
+  fn_all_reduce all_reduce = nullptr;
+  fn_all_gather all_gather = nullptr;
+  fn_group group_start = nullptr, group_end = nullptr;
+  fn_err_string err_string = nullptr;
+};
+
+constexpr int kNcclFloat32 = 7, kNcclSum = 0;
+
+NcclApi* nccl() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api.lib ? &api : nullptr;
+  tried = true;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    api.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (api.lib) break;
+  }
+  if (!api.lib) return nullptr;
+  api.get_unique_id = (fn_get_unique_id)dlsym(api.lib, "ncclGetUniqueId");
+  api.comm_init_rank = (fn_comm_init_rank)dlsym(api.lib, "ncclCommInitRank");
+  api.comm_destroy = (fn_comm_destroy)dlsym(api.lib, "ncclCommDestroy");
+  api.all_reduce = (fn_all_reduce)dlsym(api.lib, "ncclAllReduce");
+  api.all_gather = (fn_all_gather)dlsym(api.lib, "ncclAllGather");
+  api.group_start = (fn_group)dlsym(api.lib, "ncclGroupStart");
+  api.group_end = (fn_group)dlsym(api.lib, "ncclGroupEnd");
+  api.err_string = (fn_err_string)dlsym(api.lib, "ncclGetErrorString");
+  if (!api.get_unique_id || !api.comm_init_rank || !api.comm_destroy || !api.all_reduce || !api.all_gather ||
+      !api.group_start || !api.group_end) {
+    dlclose(api.lib);
+    api.lib = nullptr;
+    return nullptr;
+  }
+  return &api;
 }
-tb_status tp_allgather_logits(TpState* st, const float*, float*, int, int64_t, cudaStream_t, int*) {
-  (void)st;
-  return fail(TB_ERR_NCCL, "tensor-parallel decoder used before tb_decoder_tp_init");
+
+#define TB_NCCL_TRY(api, expr)                                                          \
+  do {                                                                                  \
+    int _r = (expr);                                                                    \
+    if (_r != 0)                                                                        \
+      return fail(TB_ERR_NCCL, "%s failed: %s", #expr,                                  \
+                  (api)->err_string ? (api)->err_string(_r) : "nccl error");            \
+  } while (0)
+
+constexpr int kMaxRanks = 8;
+constexpr long long kPeerWaitCycles = 20000000000ll;  // ~10 s: ranks may be apart by a graph instantiation
+
+struct PeerArgs {
+  const float* bufs[kMaxRanks];  // every rank's partial for this call, [count] floats
+  uint32_t* my_flags;            // flags[src]: written by rank src (over NVLink)
+  uint32_t* peer_flags[kMaxRanks];
+  uint32_t* epoch;               // device word: number of completed exchanges
+  int* done_ctas;                // ticket for the epoch increment
+  int* err;
+  float* x;                      // residual stream, updated in place
+  int rank, size;
+  int count4;                    // float4 elements
+};
+
+__device__ __forceinline__ float4 ld_volatile_f4(const float4* p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
 }
-void tp_destroy(TpState* st) { delete st; }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// x += sum over ranks of partial_r, partial_r read from rank r's memory.
+__global__ void __launch_bounds__(1024) peer_allreduce_residual_kernel(const PeerArgs a) {
+  __shared__ int s_ok;
+  const uint32_t want = *a.epoch + 1;
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    if (blockIdx.x == 0) {
+      // My partial was written by the previous kernel on this stream: publish it.
+      __threadfence_system();
+      for (int r = 0; r < a.size; ++r) st_release_sys(a.peer_flags[r] + a.rank, want);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < a.size) {
+    const long long t0 = clock64();
+    while (ld_acquire_sys(a.my_flags + threadIdx.x) < want) {
+      if (clock64() - t0 > kPeerWaitCycles) {  // a peer never arrived: give up, flag the error
+        s_ok = 0;
+        atomicExch(a.err, 1);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < a.count4; i += gridDim.x * blockDim.x) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < a.size; ++r) {
+        const float4 v = ld_volatile_f4(reinterpret_cast<const float4*>(a.bufs[r]) + i);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+      float4 xv = reinterpret_cast<float4*>(a.x)[i];
+      xv.x += s.x; xv.y += s.y; xv.z += s.z; xv.w += s.w;
+      reinterpret_cast<float4*>(a.x)[i] = xv;
+    }
+  }
+  // the last CTA closes the exchange
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(a.done_ctas, 1) == (int)gridDim.x - 1) {
+      *a.done_ctas = 0;
+      *a.epoch = want;
+    }
+  }
+}
+
+__global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ y, int n4) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n4) {
+    float4 a = reinterpret_cast<float4*>(x)[i];
+    const float4 b = reinterpret_cast<const float4*>(y)[i];
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    reinterpret_cast<float4*>(x)[i] = a;
+  }
+}
+
+}  // namespace
+
+struct TpState {
+  int rank = 0, size = 1;
+  nccl_comm_t comm = nullptr;
+  bool fused = false;
+  size_t max_count = 0;       // floats per partial
+  // fused path
+  char* block = nullptr;      // my shared block: [2][max_count] floats | flags | epoch | ticket | err
+  char* peer_block[kMaxRanks] = {};
+  size_t flags_off = 0;
+  int calls = 0;              // host-side call parity selects the buffer a projection writes to
+  float* reduced = nullptr;   // NCCL path: the summed partial
+};
+
+float* tp_partial_buffer(TpState* st, float* fallback) {
+  if (!st || !st->fused) return fallback;
+  return reinterpret_cast<float*>(st->block) + (size_t)(st->calls & 1) * st->max_count;
+}
+
+tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int batch, int64_t hidden,
+                                cudaStream_t stream, int* launches) {
+  if (!st || !st->comm) return fail(TB_ERR_NCCL, "tensor-parallel decoder used before tb_decoder_tp_init");
+  const size_t count = (size_t)batch * hidden;
+  if (count > st->max_count || (count & 3)) return fail(TB_ERR_SHAPE, "tp all-reduce: %zu elements", count);
+  if (st->fused) {
+    const int slot = st->calls & 1;
+    st->calls++;
+    PeerArgs a;
+    for (int r = 0; r < st->size; ++r) {
+      a.bufs[r] = reinterpret_cast<const float*>(st->peer_block[r]) + (size_t)slot * st->max_count;
+      a.peer_flags[r] = reinterpret_cast<uint32_t*>(st->peer_block[r] + st->flags_off);
+    }
+    if (partial != a.bufs[st->rank]) return fail(TB_ERR_ARG, "tp all-reduce: the partial must be written to tp_partial_buffer()");
+    uint32_t* words = reinterpret_cast<uint32_t*>(st->block + st->flags_off);
+    a.my_flags = words;
+    a.epoch = words + 16;
+    a.done_ctas = reinterpret_cast<int*>(words + 17);
+    a.err = reinterpret_cast<int*>(words + 18);
+    a.x = x;
+    a.rank = st->rank; a.size = st->size;
+    a.count4 = (int)(count / 4);
+    int grid = (a.count4 + 1023) / 1024;
+    if (grid > 16) grid = 16;
+    peer_allreduce_residual_kernel<<<grid, 1024, 0, stream>>>(a);
+    TB_CUDA_TRY(cudaGetLastError());
+    if (launches) ++*launches;
+    return TB_OK;
+  }
+  NcclApi* api = nccl();
+  TB_NCCL_TRY(api, api->all_reduce(partial, st->reduced, count, kNcclFloat32, kNcclSum, st->comm, stream));
+  const int n4 = (int)(count / 4);
+  add_inplace_kernel<<<(n4 + 255) / 256, 256, 0, stream>>>(x, st->reduced, n4);
+  TB_CUDA_TRY(cudaGetLastError());
+  if (launches) *launches += 2;
+  return TB_OK;
+}
+
+tb_status tp_allgather_logits(TpState* st, const float* logits_l, float* logits, int batch,
+                              int64_t v_local, cudaStream_t stream, int* launches) {
+  if (!st || !st->comm) return fail(TB_ERR_NCCL, "tensor-parallel decoder used before tb_decoder_tp_init");
+  NcclApi* api = nccl();
+  const int64_t v = v_local * st->size;
+  if (batch > 1) TB_NCCL_TRY(api, api->group_start());
+  for (int b = 0; b < batch; ++b)
+    TB_NCCL_TRY(api, api->all_gather(logits_l + (size_t)b * v_local, logits + (size_t)b * v, (size_t)v_local,
+                                     kNcclFloat32, st->comm, stream));
+  if (batch > 1) TB_NCCL_TRY(api, api->group_end());
+  if (launches) ++*launches;
+  return TB_OK;
+}
+
+int tp_error_flag(TpState* st) {
+  if (!st || !st->fused) return 0;
+  int v = 0;
+  if (cudaMemcpy(&v, st->block + st->flags_off + 18 * sizeof(uint32_t), sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return v;
+}
+
+void tp_destroy(TpState* st) {
+  if (!st) return;
+  for (int r = 0; r < st->size; ++r)
+    if (r != st->rank && st->peer_block[r]) cudaIpcCloseMemHandle(st->peer_block[r]);
+  cudaFree(st->block);
+  cudaFree(st->reduced);
+  if (st->comm) {
+    NcclApi* api = nccl();
+    if (api) api->comm_destroy(st->comm);
+  }
+  delete st;
+}
+
+tb_status tp_create(TpState** out, int rank, int size, const uint8_t id[128], size_t max_count,
+                    tb_allgather_fn allgather, void* user, bool nccl_only) {
+  *out = nullptr;
+  if (size < 2 || size > kMaxRanks || rank < 0 || rank >= size) return fail(TB_ERR_ARG, "tensor parallel size %d / rank %d (supported: 2..%d ranks)", size, rank, kMaxRanks);
+  NcclApi* api = nccl();
+  if (!api) return fail(TB_ERR_NCCL, "libnccl.so.2 could not be loaded: %s", dlerror());
+  TpState* st = new TpState();
+  st->rank = rank; st->size = size; st->max_count = (max_count + 3) & ~(size_t)3;
+  NcclId nid;
+  memcpy(nid.internal, id, 128);
+  int r = api->comm_init_rank(&st->comm, size, nid, rank);
+  if (r != 0) {
+    delete st;
+    return fail(TB_ERR_NCCL, "ncclCommInitRank failed: %s", api->err_string ? api->err_string(r) : "?");
+  }
+  auto bail = [&](tb_status s) { tp_destroy(st); return s; };
+  cudaError_t e = cudaMalloc(&st->reduced, st->max_count * sizeof(float));
+  if (e != cudaSuccess) return bail(fail(TB_ERR_OOM, "tp: %s", cudaGetErrorString(e)));
+  if (allgather && !nccl_only) {
+    st->flags_off = 2 * st->max_count * sizeof(float);
+    const size_t bytes = st->flags_off + 256;
+    e = cudaMalloc(&st->block, bytes);
+    if (e != cudaSuccess) return bail(fail(TB_ERR_OOM, "tp: %s", cudaGetErrorString(e)));
+    cudaMemset(st->block, 0, bytes);
+    cudaDeviceSynchronize();
+    cudaIpcMemHandle_t mine;
+    e = cudaIpcGetMemHandle(&mine, st->block);
+    if (e != cudaSuccess) return bail(fail(TB_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e)));
+    std::vector<cudaIpcMemHandle_t> all(size);
+    if (allgather(user, &mine, all.data(), sizeof(mine)) != 0) return bail(fail(TB_ERR_NCCL, "tp: the caller's all-gather failed"));
+    for (int p = 0; p < size; ++p) {
+      if (p == rank) { st->peer_block[p] = st->block; continue; }
+      void* ptr = nullptr;
+      e = cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) return bail(fail(TB_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", p, cudaGetErrorString(e)));
+      st->peer_block[p] = static_cast<char*>(ptr);
+    }
+    // nobody may start an exchange before every rank has mapped every block
+    int token = 1;
+    std::vector<int> tokens(size);
+    if (allgather(user, &token, tokens.data(), sizeof(int)) != 0) return bail(fail(TB_ERR_NCCL, "tp: the caller's all-gather failed"));
+    st->fused = true;
+  }
+  *out = st;
+  return TB_OK;
+}
 
 }  // namespace tb
 
-extern "C" {
-tb_status tb_tp_unique_id(uint8_t id[128]) { (void)id; return tb::fail(TB_ERR_UNSUPPORTED, "tensor parallelism not built yet"); }
-tb_status tb_decoder_tp_init(tb_decoder*, const uint8_t*, tb_allgather_fn, void*) {
-  return tb::fail(TB_ERR_UNSUPPORTED, "tensor parallelism not built yet");
-}
+extern "C" tb_status tb_tp_unique_id(uint8_t id[128]) {
+  if (!id) return tb::fail(TB_ERR_ARG, "tb_tp_unique_id: null buffer");
+  tb::NcclApi* api = tb::nccl();
+  if (!api) return tb::fail(TB_ERR_NCCL, "libnccl.so.2 could not be loaded: %s", dlerror());
+  tb::NcclId nid;
+  int r = api->get_unique_id(&nid);
+  if (r != 0) return tb::fail(TB_ERR_NCCL, "ncclGetUniqueId failed: %s", api->err_string ? api->err_string(r) : "?");
+  memcpy(id, nid.internal, 128);
+  return TB_OK;
 }

@@ -13,5 +13,14 @@ tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int
 tb_status tp_allgather_logits(TpState* st, const float* logits_l, float* logits, int batch,
                               int64_t v_local, cudaStream_t stream, int* launches);
 void tp_destroy(TpState* st);
+// Communicator (NCCL) and, when `allgather` is given and nccl_only is false, the peer-memory
+// exchange buffers.  Collective: every rank calls it.  max_count = floats per partial.
+tb_status tp_create(TpState** out, int rank, int size, const uint8_t id[128], size_t max_count,
+                    tb_allgather_fn allgather, void* user, bool nccl_only);
+// Where the row-parallel projection of the NEXT tp_allreduce_residual call must write its
+// partial (the peer-visible buffer on the fused path, `fallback` otherwise).
+float* tp_partial_buffer(TpState* st, float* fallback);
+// 1 after a bounded wait on a peer ran out.
+int tp_error_flag(TpState* st);
 
 }  // namespace tb
