@@ -369,7 +369,7 @@ def run_gpu(args):
     dec = tb.B200QwenDecoder(embed, layers, fnorm, lm_p, lm_s, c["num_layers"], c["hidden_size"],
                              c["intermediate_size"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["group_size"],
                              c["rms_norm_eps"], max_seq, c["rope_theta"], max_batch=B, tp_size=tp, tp_rank=rank,
-                             vocab_size=c["vocab_size"], nccl_only=args.nccl_only)
+                             vocab_size=c["vocab_size"], nccl_only=args.nccl_only, pdl=not args.no_pdl, debug=args.no_graph)
     if tp > 1:
         from torchburn_b200.tp import init_tensor_parallel
 
@@ -446,6 +446,13 @@ def run_gpu(args):
             dec.close()
             dist.destroy_process_group()
         return
+    if args.quick:
+        print(json.dumps({"value": value, "ms_per_step": ms_per_step, "e2e": e2e_value, "n_gpus": tp}), flush=True)
+        if tp > 1:
+            dist.barrier()
+            dec.close()
+            dist.destroy_process_group()
+        return
     # ---- rank 0: roofline of the dominant kernel, config-1 GEMV, CPU baseline ----
     peak, peak_kind = measured_peak()
     alg, sec, _ = time_dominant_kernel(torch, tb, c, layers, device, tp)
@@ -498,6 +505,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: plain ncclAllReduce instead of the fused kernel")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-pdl", action="store_true", help="plain stream order between kernels (A/B of programmatic dependent launch)")
+    ap.add_argument("--no-graph", action="store_true", help="direct launches instead of CUDA-graph replay")
+    ap.add_argument("--quick", action="store_true", help="skip the kernel-alone and CPU measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

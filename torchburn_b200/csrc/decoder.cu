@@ -12,6 +12,7 @@
 // src/wgpu/decode.rs:6-7).  Token ids and offsets live in device memory, so one
 // graph serves every position.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -79,6 +80,11 @@ struct tb_decoder {
   cudaGraphExec_t graphs_greedy[kMaxBatch + 1] = {};
   bool use_graph = true;
   bool pdl = true;
+  // Kernels launched with programmatic dependent launch (bit 0 qkv, 1 attention, 2 o_proj,
+  // 3 gate/up, 4 down, 5 lm_head).  Measured on B200: the attention kernel gains from starting
+  // its K/V tile copies early; the persistent GEMV kernels run slower when they are made
+  // resident before their predecessor has finished, so they keep plain stream order.
+  int pdl_mask = 2;
   int64_t kv_used = 0;
   int last_batch = 1;
   bool device_lost = false;
@@ -121,6 +127,7 @@ size_t kv_layer_stride(const tb_decoder* d) { return (size_t)d->B * d->nkv_l * d
 tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_head = nullptr) {
   cudaStream_t st = d->stream;
   const bool pdl = d->pdl;
+  const int pm = d->pdl_mask;
   int launches = 0;
   TB_TRY(launch_embed_gather(d->embed, d->d_tokens, d->d_offsets, d->x, d->d_eff, b, d->V, d->H, d->S,
                              false, st));
@@ -139,7 +146,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x = d->x; a.w = W.qkv_w; a.scales = W.qkv_s; a.bias = W.qkv_b; a.out = d->qkv;
       a.norm_w = W.input_norm_w; a.eps = d->cfg.rms_norm_eps;
       a.x_normed_out = dbg ? d->dbg_normed : nullptr;
-      a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug;
+      a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 1);
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
     }
@@ -151,7 +158,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.offsets = d->d_eff; a.out = d->attn;
       a.scratch = d->attn_scratch; a.q_rot_out = dbg ? d->dbg_qkv : nullptr;
       a.batch = b; a.num_heads = d->nh_l; a.num_kv_heads = d->nkv_l; a.head_dim = d->hd;
-      a.max_seq_len = d->S; a.pdl = pdl && !debug;
+      a.max_seq_len = d->S; a.pdl = pdl && !debug && (pm & 2);
       // The kernel strides sequences by [Hkv, S, d]; with batch > 1 that is the layout of
       // one layer's block [B][Hkv][S][d].
       TB_TRY(launch_attention_decode(a, st));
@@ -161,7 +168,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     {  // F + G
       GemvArgs a;
       a.x = d->attn; a.w = W.o_w; a.scales = W.o_s; a.m = b; a.n = d->H; a.k = d->q_dim_l; a.g = d->G;
-      a.pdl = pdl && !debug;
+      a.pdl = pdl && !debug && (pm & 4);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
       TB_TRY(launch_w4_gemv(a, st));
@@ -173,7 +180,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       GemvArgs a;
       a.x = d->x; a.w = W.gate_w; a.scales = W.gate_s; a.w2 = W.up_w; a.scales2 = W.up_s; a.out = d->h;
       a.norm_w = W.post_norm_w; a.eps = d->cfg.rms_norm_eps;
-      a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug;
+      a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 8);
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
     }
@@ -181,7 +188,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     {  // I' + J
       GemvArgs a;
       a.x = d->h; a.w = W.down_w; a.scales = W.down_s; a.m = b; a.n = d->H; a.k = d->I_l; a.g = d->G;
-      a.pdl = pdl && !debug;
+      a.pdl = pdl && !debug && (pm & 16);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
       TB_TRY(launch_w4_gemv(a, st));
@@ -195,7 +202,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     GemvArgs a;
     a.x = d->x; a.w = d->lm_w; a.scales = d->lm_s;
     a.norm_w = d->final_norm_w; a.eps = d->cfg.rms_norm_eps;
-    a.m = b; a.n = d->V_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug;
+    a.m = b; a.n = d->V_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 32);
     a.out = d->tp == 1 ? d->logits : d->logits_l;
     TB_TRY(launch_w4_gemv(a, st));
     ++launches;
@@ -322,6 +329,8 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   d->q_dim_l = (int64_t)d->nh_l * d->hd;
   d->tq_l = d->q_dim_l + 2ll * d->nkv_l * d->hd;
   d->use_graph = !(c.flags & TB_DECODER_NO_GRAPH);
+  d->pdl = !(c.flags & TB_DECODER_NO_PDL);
+  if (const char* pmv = getenv("TB_PDL_MASK")) d->pdl_mask = atoi(pmv);
   cudaGetDevice(&d->device);
 
   tb_status s = TB_OK;

@@ -42,10 +42,10 @@ struct StreamParams {
   float eps;
   int n, k, nb32, gshift, ng;
   int nwarps;        // consumer warps per group = ceil(k / EPL / 32)
-  int groups;        // consumer groups (each takes every groups-th tile)
+  int groups;        // always 1 (see the kernel comment)
   int stages;        // ring depth
   int stage_bytes;   // bytes of one stage
-  int tiles;         // ceil(n / 32)
+  int rounds;        // ceil(n / 8): the unit of work distribution (8 rows)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -106,16 +106,38 @@ __device__ __forceinline__ float transpose_reduce(float (&p)[32], int lane) {
   return p[0];
 }
 
-// RS rows per stage (32 % RS == 0); EPI 0 plain / 1 SwiGLU; NORM fused RMSNorm of x;
+// Same idea for 8 values: three transposing steps leave one row per lane (row = lane >> 2),
+// two plain steps finish the sum over the four lanes that share it (9 shuffles for 8 rows).
+__device__ __forceinline__ float transpose_reduce8(float (&p)[8], int lane) {
+#pragma unroll
+  for (int step = 0; step < 3; ++step) {
+    const int off = 16 >> step, half = 4 >> step;
+    const bool hi = (lane & off) != 0;
+#pragma unroll
+    for (int j = 0; j < half; ++j) {
+      const float send = hi ? p[j] : p[j + half];
+      const float keep = hi ? p[j + half] : p[j];
+      p[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+  float v = p[0];
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v;
+}
+
+// RS rows per stage (8 % RS == 0); EPI 0 plain / 1 SwiGLU; NORM fused RMSNorm of x;
 // EPL elements of K owned by one lane (32 = a whole block, 16 = half a block).
 //
-// Consumer warps form `groups` groups of `nwarps` warps.  A group covers all of K (lane l of
-// group warp w owns elements [(w*32+l)*EPL, +EPL)) and takes every groups-th 32-row tile of
-// the CTA, so several tiles are in progress at once and the schedulers have warps to pick from.
+// The consumer warps of a CTA together cover all of K (lane l of warp w owns elements
+// [(w*32+l)*EPL, +EPL)) and observe every stage of the ring in order, which keeps the mbarrier
+// phase parities unambiguous (p.groups is always 1).  Work is handed out in rounds of 8 rows:
+// every CTA gets a contiguous, balanced share, so no CTA waits for a straggler tile.
 template <int RS, int EPI, bool NORM, int EPL>
 __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   constexpr int NW = EPI == 1 ? 2 : 1;
-  constexpr int SPT = 32 / RS;     // stages per 32-row tile
+  constexpr int TR = 8;            // rows per round
+  constexpr int SPR = TR / RS;     // stages per round
   constexpr int NWD = EPL / 8;     // 32-bit weight words per lane and row
   extern __shared__ __align__(128) unsigned char ring[];
   __shared__ uint64_t full[kMaxStages], empty[kMaxStages];
@@ -127,8 +149,11 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   const int nwarps = p.nwarps, groups = p.groups;
   const bool is_producer = warp == nwarps * groups;
   const int row_bytes = p.k >> 1, srow_bytes = p.ng * 4;
-  const int my_tiles = (p.tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int total_stages = my_tiles * SPT;
+  // Contiguous, balanced share of the 8-row rounds: the first `rem` CTAs take one more.
+  const int base_rounds = p.rounds / (int)gridDim.x, rem_rounds = p.rounds % (int)gridDim.x;
+  const int my_rounds = base_rounds + ((int)blockIdx.x < rem_rounds ? 1 : 0);
+  const int round0 = (int)blockIdx.x * base_rounds + min((int)blockIdx.x, rem_rounds);
+  const int total_stages = my_rounds * SPR;
 
   if (tid == 0) {
     s_abort = 0;
@@ -149,8 +174,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
       for (int i = 0; i < total_stages; ++i) {
         const int s = i % p.stages, round = i / p.stages;
         if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
-        const int tile = (int)blockIdx.x + (i / SPT) * (int)gridDim.x;
-        const int row0 = tile * 32 + (i % SPT) * RS;
+        const int row0 = (round0 + i / SPR) * TR + (i % SPR) * RS;
         const int cnt = max(0, min(RS, p.n - row0));
         unsigned char* dst = ring + (size_t)s * p.stage_bytes;
         if (cnt == 0) {  // nothing to fetch for this stage: complete the phase by hand
@@ -229,12 +253,13 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   }
 
   const int sidx = blk >> p.gshift;
-  int n_done = 0;
-  for (int t = grp; t < my_tiles; t += groups, ++n_done) {
-    float pa[NW][32];
+  int buf = 0;
+#pragma unroll 1
+  for (int rd = 0; rd < my_rounds; ++rd) {
+    float pa[NW][TR];
 #pragma unroll
-    for (int sub = 0; sub < SPT; ++sub) {
-      const int it = t * SPT + sub;
+    for (int ss = 0; ss < SPR; ++ss) {
+      const int it = rd * SPR + ss;
       const int s = it % p.stages;
       const bool ok = mbar_wait(&full[s], (uint32_t)(it / p.stages) & 1u, &s_abort);
       const unsigned char* st = ring + (size_t)s * p.stage_bytes;
@@ -257,19 +282,24 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
             const float sc = *reinterpret_cast<const float*>(base + (size_t)RS * row_bytes + (size_t)r * srow_bytes + sidx * 4);
             val = sc * fmaf(sx, idot_words<NWD>(wv, dig), corr);
           }
-          pa[q][sub * RS + r] = val;
+          pa[q][ss * RS + r] = val;
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
     }
-    // ---- 32 rows done for this lane's slice of K: sum over the group's lanes ----
-    const int buf = n_done & 1;
+    // ---- 8 rows done for this lane's slice of K: sum over the warp's lanes ----
+    const int slot = rd & 3;
 #pragma unroll
-    for (int q = 0; q < NW; ++q) s_part[buf][q][warp][lane] = transpose_reduce(pa[q], lane);
+    for (int q = 0; q < NW; ++q) {
+      const float v = transpose_reduce8(pa[q], lane);
+      if ((lane & 3) == 0) s_part[buf][q][warp][slot * TR + (lane >> 2)] = v;
+    }
+    if (slot != 3 && rd != my_rounds - 1) continue;
+    // ---- up to 32 rows gathered: sum over the warps, epilogue, one coalesced store ----
     asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(group_threads) : "memory");
-    if (gw == 0) {
-      const int row = ((int)blockIdx.x + t * (int)gridDim.x) * 32 + lane;
+    if (gw == 0 && lane < (slot + 1) * TR) {
+      const int row = (round0 + (rd & ~3)) * TR + lane;
       float acc[NW];
 #pragma unroll
       for (int q = 0; q < NW; ++q) {
@@ -290,6 +320,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
         p.out[row] = v;
       }
     }
+    buf ^= 1;
   }
   if (s_abort && tid == 0) atomicExch(&g_stream_fault, 1);
 }
@@ -331,8 +362,6 @@ tb_status launch_en(int rs, const StreamParams& p, int grid, size_t smem, bool p
     case 2: return launch_rs<2, EPI, NORM, EPL>(p, grid, smem, pdl, stream);
     case 4: return launch_rs<4, EPI, NORM, EPL>(p, grid, smem, pdl, stream);
     case 8: return launch_rs<8, EPI, NORM, EPL>(p, grid, smem, pdl, stream);
-    case 16: return launch_rs<16, EPI, NORM, EPL>(p, grid, smem, pdl, stream);
-    case 32: return launch_rs<32, EPI, NORM, EPL>(p, grid, smem, pdl, stream);
   }
   return fail(TB_ERR_ARG, "w4 stream: rows per stage %d", rs);
 }
@@ -386,15 +415,15 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   p.n = (int)a.n; p.k = (int)a.k; p.nb32 = (int)(a.k / 32);
   p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
   p.ng = (int)(a.k / a.g);
-  p.tiles = (p.n + 31) / 32;
+  p.rounds = (p.n + 7) / 8;
   // K split: half a block per lane in the latency regime (few tiles per CTA: more lanes work
   // on each row), a whole block per lane in the throughput regime (fewer instructions per
   // element); wide K runs one CTA per SM with twice the ring.
-  int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (p.k >= 8192 ? 1 : 2);
+  int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (p.k >= 8192 ? 1 : 3);
   int grid = sm_count() * cps;
-  if (grid > p.tiles) grid = p.tiles;
-  const int tiles_per_cta = (p.tiles + grid - 1) / grid;
-  int epl = (tiles_per_cta == 1 && p.nb32 * 2 <= 14 * 32) ? 16 : 32;
+  if (grid > p.rounds) grid = p.rounds;
+  const int rounds_per_cta = (p.rounds + grid - 1) / grid;
+  int epl = (rounds_per_cta <= 4 && p.nb32 * 2 <= 14 * 32) ? 16 : 32;
   if (g_force_epl == 16 || g_force_epl == 32) epl = g_force_epl;
   p.nwarps = (p.k / epl + 31) / 32;
   if (p.nwarps > 15) { epl = 32; p.nwarps = (p.nb32 + 31) / 32; }
@@ -404,8 +433,8 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   const int nw = a.w2 ? 2 : 1;
   const int per_row = nw * (p.k / 2 + p.ng * 4);
   // Stage: at most ~20 KB; ring: as many stages as fit the budget (2..8).
-  const int ring_budget = g_ring_kb > 0 ? g_ring_kb * 1024 : kRingBytesMax / cps;
-  int rs = 32;
+  const int ring_budget = g_ring_kb > 0 ? g_ring_kb * 1024 : (cps >= 3 ? 40 * 1024 : kRingBytesMax / cps);
+  int rs = 8;
   while (rs > 1 && (rs * per_row > 20 * 1024 || rs * per_row * 3 > ring_budget)) rs >>= 1;
   p.stage_bytes = rs * per_row;
   p.stages = ring_budget / p.stage_bytes;

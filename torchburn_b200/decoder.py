@@ -64,7 +64,7 @@ class B200QwenDecoder:
                  num_kv_heads: int, head_dim: int, group_size: int = 64, rms_norm_eps: float = 1e-6,
                  max_seq_len: int = 2048, rope_theta: float = 1000000.0, max_batch: int = 1,
                  tp_size: int = 1, tp_rank: int = 0, debug: bool = False, vocab_size: Optional[int] = None,
-                 nccl_only: bool = False):
+                 nccl_only: bool = False, pdl: bool = True):
         self._h = None
         ops = _Operands()
         emb_p = ops.ptr(embed_tokens, np.float32)
@@ -84,7 +84,8 @@ class B200QwenDecoder:
         fn_p = ops.ptr(final_norm_w, np.float32)
         lw_p = ops.ptr(lm_head_w, np.uint8)
         ls_p = ops.ptr(lm_head_s, np.float32)
-        flags = (_lib.TB_DECODER_NO_GRAPH if debug else 0) | (_lib.TB_DECODER_NCCL_ONLY if nccl_only else 0)
+        flags = ((_lib.TB_DECODER_NO_GRAPH if debug else 0) | (_lib.TB_DECODER_NCCL_ONLY if nccl_only else 0)
+                 | (0 if pdl else _lib.TB_DECODER_NO_PDL))
         cfg = ModelConfig(vocab_size=self.vocab_size, hidden_size=hidden_size, intermediate_size=intermediate_size,
                           num_layers=num_layers, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                           group_size=group_size, rms_norm_eps=rms_norm_eps, max_seq_len=max_seq_len,
