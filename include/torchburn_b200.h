@@ -125,6 +125,32 @@ tb_status tb_attention_decode(const float* qkv, float* k_cache, float* v_cache,
                               int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
                               int64_t max_seq_len, void* stream);
 
+/* tb_attention_decode for callers that cannot allocate device memory.  (No counterpart in
+ * the reference: its attention runs on the host and needs no scratch.)
+ *
+ * Who needs it: a server that hands out all of its device memory at start-up and has nothing
+ * left to cudaMalloc from; code that may run while some thread of the process is capturing a
+ * CUDA graph, where an allocation would invalidate the capture; a latency-critical loop that
+ * cannot afford the device-wide stall of an allocation.  For them the split-K partials and
+ * ticket counters live in a block of tb_attention_static_scratch_bytes() (8 MiB) that is part
+ * of the library's device image - every GPU that loads the library carries it until the
+ * process exits.  The caller still passes all inputs and outputs; arguments and results are
+ * those of tb_attention_decode.
+ *
+ * Limit: shapes with tb_attention_scratch_bytes(...) above that size fail with
+ * TB_ERR_UNSUPPORTED (use tb_attention_decode with your own scratch).  The call allocates
+ * nothing: no cudaMalloc / cudaFree, only a memset of its counters and the kernel launch.
+ * The first call on each device looks up the block's device address; make that first call
+ * before any stream capture begins.  All calls on a device share the one block, which keeps
+ * the previous call's contents: the entry point clears what must start at zero itself, but
+ * two calls that overlap on the GPU (different streams) race on it - serialise them. */
+size_t tb_attention_static_scratch_bytes(void);
+tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_cache,
+                                     const float* cos_table, const float* sin_table,
+                                     const int32_t* offsets, float* out, int32_t batch,
+                                     int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                     int64_t max_seq_len, void* stream);
+
 /* Tuning hook: positions of the KV sequence handled per attention CTA (a power
  * of two in [32, 256]; 0 = choose from the shape).  Process-wide; plays the role
  * of TORCHBURN_ROWS_PER_WG, src/wgpu/backend.rs:428-437. */

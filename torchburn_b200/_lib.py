@@ -55,6 +55,8 @@ SIGNATURES = {
     "tb_quantize_weight_int4_grouped": (_i32, [_p, _i64, _i64, _i32, _p, _p, _p]),
     "tb_attention_scratch_bytes": (_sz, [_i32, _i32, _i32, _i32, _i64]),
     "tb_attention_decode": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i64, _p]),
+    "tb_attention_static_scratch_bytes": (_sz, []),
+    "tb_attention_decode_static": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i64, _p]),
     "tb_set_attention_chunk": (None, [_i32]),
     "tb_set_gemv_tuning": (None, [_i32, _i32, _i32]),
     "tb_set_stream_tuning": (None, [_i32, _i32, _i32, _i32, _i32]),

@@ -462,4 +462,37 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   return TB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Attention without any allocation.  The partials and ticket counters of the kernel above
+// normally live in scratch memory that the caller allocates.  Some callers cannot allocate:
+// a serving process whose device memory was carved up completely at start-up, code that runs
+// while another thread is capturing a CUDA graph (an allocation there breaks the capture), or a
+// latency-critical loop in which a cudaMalloc would stall every stream of the device.  For
+// them the same kernel runs on a fixed block of device memory that is part of this library's
+// image: every GPU that loads the library holds these 8 MiB until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
+
+size_t static_attention_scratch_capacity() { return kStaticScratchBytes; }
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel
+// could use; the device address is looked up once per device, with that device current.
+tb_status static_attention_scratch(void** ptr) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  TB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev]) {
+    *ptr = cached[dev];
+    return TB_OK;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_static_attn_scratch);
+  if (e != cudaSuccess || p == nullptr)
+    return fail(TB_ERR_CUDA, "cudaGetSymbolAddress(static attention scratch) failed: %s", cudaGetErrorString(e));
+  if (dev >= 0 && dev < 64) cached[dev] = p;
+  *ptr = p;
+  return TB_OK;
+}
+
 }  // namespace tb

@@ -179,6 +179,35 @@ tb_status tb_attention_decode(const float* qkv, float* k_cache, float* v_cache,
   return launch_attention_decode(a, as_stream(stream));
 }
 
+size_t tb_attention_static_scratch_bytes(void) { return static_attention_scratch_capacity(); }
+
+tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_cache,
+                                     const float* cos_table, const float* sin_table,
+                                     const int32_t* offsets, float* out, int32_t batch,
+                                     int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                     int64_t max_seq_len, void* stream) {
+  if (batch < 1 || num_heads < 1 || num_kv_heads < 1 || head_dim < 1 || max_seq_len < 1)
+    return fail(TB_ERR_SHAPE, "tb_attention_decode_static: empty shape");
+  const size_t need = attention_scratch_bytes(batch, num_heads, num_kv_heads, head_dim, max_seq_len);
+  if (need > static_attention_scratch_capacity())
+    return fail(TB_ERR_UNSUPPORTED,
+                "tb_attention_decode_static: this shape needs %zu bytes of scratch, the built-in block holds %zu; "
+                "use tb_attention_decode with caller-provided scratch",
+                need, static_attention_scratch_capacity());
+  void* scratch = nullptr;
+  TB_TRY(static_attention_scratch(&scratch));
+  // The block keeps whatever the previous call (possibly of another shape) left behind:
+  // the ticket counters and the error word of this shape must start at zero.
+  size_t cbytes = 0;
+  const size_t coff = attention_counters_offset(batch, num_heads, num_kv_heads, head_dim, max_seq_len, &cbytes);
+  TB_CUDA_TRY(cudaMemsetAsync(static_cast<char*>(scratch) + coff, 0, cbytes, as_stream(stream)));
+  AttnArgs a;
+  a.qkv = qkv; a.k_cache = k_cache; a.v_cache = v_cache; a.cos_t = cos_table; a.sin_t = sin_table;
+  a.offsets = offsets; a.out = out; a.scratch = scratch; a.batch = batch; a.num_heads = num_heads;
+  a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.max_seq_len = max_seq_len;
+  return launch_attention_decode(a, as_stream(stream));
+}
+
 void tb_set_attention_chunk(int32_t tc) { set_attention_chunk_override(tc); }
 
 void tb_set_gemv_tuning(int32_t xmode, int32_t rows_per_warp, int32_t warps) { set_gemv_tuning(xmode, rows_per_warp, warps); }

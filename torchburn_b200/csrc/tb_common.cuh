@@ -95,6 +95,9 @@ size_t attention_counters_offset(int batch, int num_heads, int num_kv_heads, int
 // Tuning hook: force the positions per attention CTA (0 = automatic).
 void set_attention_chunk_override(int tc);
 tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream);
+// The library's built-in scratch block for tb_attention_decode_static (attention.cu).
+size_t static_attention_scratch_capacity();
+tb_status static_attention_scratch(void** ptr);
 
 tb_status launch_rms_norm(const float* x, const float* w, float* out, int64_t m, int64_t n,
                           float eps, cudaStream_t stream);
