@@ -152,7 +152,7 @@ tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_
                                      int64_t max_seq_len, void* stream);
 
 /* Tuning hook: positions of the KV sequence handled per attention CTA (a power
- * of two in [32, 256]; 0 = choose from the shape).  Process-wide; plays the role
+ * of two in [64, 512]; 0 = choose from the shape).  Process-wide; plays the role
  * of TORCHBURN_ROWS_PER_WG, src/wgpu/backend.rs:428-437. */
 void tb_set_attention_chunk(int32_t positions);
 /* Tuning hook for the M = 1 GEMV kernels.  product_mode 1 (default): activations are

@@ -6,7 +6,7 @@
 //
 // The reference walks the sequence serially per q head with a two-pass softmax.
 // Here the sequence of every (sequence, kv head) is cut into chunks of `tc`
-// positions, one CTA per chunk; the CTA serves all q heads that share the kv
+// positions, one CTA per chunk (each warp streaming its own rows straight into registers); the CTA serves all q heads that share the kv
 // head, so each K/V row is read from HBM once per step.  Every CTA writes an
 // un-normalised partial (max, sum, weighted V) to scratch; the last CTA of a
 // (sequence, kv head) to finish - found with a ticket counter - rescales and
@@ -90,38 +90,55 @@ __device__ __forceinline__ float rope_elem(const float* x, const float* c, const
   return __fadd_rn(__fmul_rn(x[i], c[i]), __fmul_rn(x[i - half], s[i]));
 }
 
-// Shared memory (floats): K tile [tc][D] | V tile [tc][D] | q_s [gq][D] | sc [gq][tc] |
-// red [1024 * gq] | ml [2 * gq].  The merge reuses the K|V tiles for its weights [gq][nc].
-__host__ __device__ inline size_t attn_smem_floats(int D, int tc, int gq) {
-  return (size_t)2 * tc * D + (size_t)gq * D + (size_t)gq * tc + (size_t)1024 * gq + 2 * gq;
+// Shared memory (floats): q_s [gq][D] | kv_new [2][D] | w_acc [8][gq][D] | w_ml [8][gq][2] |
+// wts [gq][nc] | red [1024*gq] | ml [2*gq]   (the last three are used by the merge).  Every
+// region starts on a 16-byte boundary (float4 accesses).
+__host__ __device__ inline size_t attn_smem_floats(int D, int nc, int gq) {
+  return (size_t)gq * D + 2 * D + (size_t)kAttnWarps * gq * D + (size_t)((kAttnWarps * gq * 2 + 3) & ~3) +
+         (size_t)((gq * nc + 3) & ~3) + (size_t)1024 * gq + 2 * gq;
 }
 
+__device__ __forceinline__ float4 ldg_stream_f4(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// One CTA = one chunk of tc positions of one (sequence, kv head).  Inside the CTA every warp is
+// on its own: in each pass it takes 8 rows of the chunk, loads their K and V rows straight into
+// registers (all 16 KB requested before anything is consumed), scores them for the gq query
+// heads (8 lanes per row, shuffle reduction), keeps an online softmax (running max / sum) and
+// accumulates the weighted V with one float4 column per lane.  No block-wide barrier sits in
+// that loop; the warps meet once to combine their (max, sum, acc) triples.
 template <int D>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnParams p) {
-  constexpr int F4 = D / 32;        // float4 per lane in the score phase (8 lanes per row)
+__global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const AttnParams p) {
+  constexpr int F4 = D / 32;        // float4 per lane and row in the score phase (8 lanes per row)
   constexpr int CPR = D / 4;        // float4 columns per row
-  constexpr int RPL = 32 / CPR;     // rows per warp load in the V phase
+  constexpr int RPL = 32 / CPR;     // rows per warp-wide load in the V phase
+  constexpr int VL = 8 / RPL;       // V loads per lane and pass
   constexpr int SL = kAttnThreads / CPR;  // chunk slices in the merge
   static_assert(D == 32 || D == 64 || D == 128, "head_dim");
-  static_assert(kAttnWarps * RPL == SL, "the V-phase and merge reductions share one buffer");
 
   extern __shared__ __align__(128) float smem[];
   const int gq = p.gq, tc = p.tc;
-  float* k_s = smem;
-  float* v_s = k_s + (size_t)tc * D;
-  float* q_s = v_s + (size_t)tc * D;
-  float* sc = q_s + gq * D;
-  float* red = sc + gq * tc;
+  float* q_s = smem;
+  float* kv_new = q_s + gq * D;
+  float* w_acc = kv_new + 2 * D;
+  float* w_ml = w_acc + (size_t)kAttnWarps * gq * D;
+  float* wts = w_ml + ((kAttnWarps * gq * 2 + 3) & ~3);
+  float* red = wts + (((size_t)gq * p.nc + 3) & ~(size_t)3);
   float* ml = red + 1024 * gq;
-  __shared__ uint64_t bar[2];
   __shared__ int s_last;
 
   const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qkv_dim = (p.num_heads + 2 * p.num_kv_heads) * D;
 
-  // The offsets were produced before the previous kernel could start, so the K/V tiles
-  // (written by earlier steps) can be requested while that kernel is still draining.
+  pdl_wait();
+  pdl_launch_dependents();
+
   const int off = p.offsets[b];
   const bool seq_ok = off >= 0 && (int64_t)off < p.max_seq_len;
   const int t_end = seq_ok ? min(off + 1, kSeqCap) : 0;  // attend to [0, t_end)
@@ -132,22 +149,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
   float* kc = p.k_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
   float* vc = p.v_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
   const float* qkv_b = p.qkv + (int64_t)b * qkv_dim;
-  bool loads_ok = true;
-
-  if (active) {
-    if (tid == 0) {
-      mbar_init(&bar[0], 1);
-      mbar_init(&bar[1], 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      const uint32_t bytes = (uint32_t)rows * D * sizeof(float);
-      mbar_expect_tx(&bar[0], bytes);
-      bulk_g2s(k_s, kc + (int64_t)t0 * D, bytes, &bar[0]);
-      mbar_expect_tx(&bar[1], bytes);
-      bulk_g2s(v_s, vc + (int64_t)t0 * D, bytes, &bar[1]);
-    }
-  }
-  pdl_wait();
-  pdl_launch_dependents();
 
   if (active) {
     const float* cs = p.cos_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
@@ -161,13 +162,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
       if (p.qkv_rot_out && chunk == 0)
         p.qkv_rot_out[(int64_t)b * qkv_dim + (int64_t)(kvh * gq + g) * D + e] = v;
     }
-    __syncthreads();  // q_s ready; mbarrier inits visible to every thread
-    loads_ok = mbar_wait(&bar[0], 0);
-    // The chunk that holds position `off` appends the new k (rotated) and v: to the cache in
-    // global memory and over whatever the bulk copy fetched for that row.
-    const bool has_new = off >= t0 && off < t0 + tc;
-    if (has_new) {
-      loads_ok = mbar_wait(&bar[1], 0) && loads_ok;
+    // The chunk that holds position `off` appends the new k (rotated) and v to the cache and
+    // keeps a copy: its rows are read below while that store may still be in flight.
+    const int new_row = off - t0;  // in [0, tc) only for that chunk
+    if (new_row >= 0 && new_row < tc) {
       const float* kx = qkv_b + (int64_t)p.num_heads * D + (int64_t)kvh * D;
       const float* vx = kx + (int64_t)p.num_kv_heads * D;
       for (int e = tid; e < D; e += kAttnThreads) {
@@ -175,105 +173,152 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
         const float vr = vx[e];
         kc[(int64_t)off * D + e] = kr;
         vc[(int64_t)off * D + e] = vr;
-        k_s[(off - t0) * D + e] = kr;
-        v_s[(off - t0) * D + e] = vr;
+        kv_new[e] = kr;
+        kv_new[D + e] = vr;
         if (p.qkv_rot_out) {
           float* o = p.qkv_rot_out + (int64_t)b * qkv_dim + (int64_t)p.num_heads * D + (int64_t)kvh * D;
           o[e] = kr;
           o[(int64_t)p.num_kv_heads * D + e] = vr;
         }
       }
-      __syncthreads();
     }
+    __syncthreads();
 
-    // ---- scores: 8 lanes per row, each lane F4 float4 (columns l8 + 8*i) ----
-    {
-      const int l8 = lane & 7, rsub = lane >> 3;
-      for (int r = warp * 4 + rsub; r < tc; r += kAttnWarps * 4) {
-        const bool rv = r < rows;
-        float4 kv4[F4];
-        const float4* krow = reinterpret_cast<const float4*>(k_s + (size_t)(rv ? r : 0) * D);
+    const int l8 = lane & 7, rsub = lane >> 3;   // score phase: 8 lanes per row, 4 rows per group
+    const int vc4 = lane % CPR, vrs = lane / CPR; // V phase: one float4 column per lane
+    float m_run[kMaxGq], l_run[kMaxGq];
+    float4 acc[kMaxGq];
 #pragma unroll
-        for (int i = 0; i < F4; ++i) kv4[i] = krow[l8 + 8 * i];
-        for (int g = 0; g < gq; ++g) {
-          const float4* q4 = reinterpret_cast<const float4*>(q_s + g * D);
-          float a = 0.f;
+    for (int g = 0; g < kMaxGq; ++g) {
+      m_run[g] = -INFINITY;
+      l_run[g] = 0.f;
+      acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int base = warp * 8; base < rows; base += kAttnWarps * 8) {
+      // ---- request the 8 K rows and 8 V rows of this pass ----
+      float4 kreg[2][F4];
+      float4 vreg[VL];
 #pragma unroll
-          for (int i = 0; i < F4; ++i) {
-            const float4 qv = q4[l8 + 8 * i];
-            a = fmaf(qv.x, kv4[i].x, a);
-            a = fmaf(qv.y, kv4[i].y, a);
-            a = fmaf(qv.z, kv4[i].z, a);
-            a = fmaf(qv.w, kv4[i].w, a);
+      for (int rg = 0; rg < 2; ++rg) {
+        const int r = base + rg * 4 + rsub;
+        const float4* krow = reinterpret_cast<const float4*>(kc + (int64_t)(t0 + (r < rows ? r : 0)) * D);
+#pragma unroll
+        for (int i = 0; i < F4; ++i) kreg[rg][i] = ldg_stream_f4(krow + l8 + 8 * i);
+      }
+#pragma unroll
+      for (int j = 0; j < VL; ++j) {
+        const int r = base + j * RPL + vrs;
+        vreg[j] = ldg_stream_f4(reinterpret_cast<const float4*>(vc + (int64_t)(t0 + (r < rows ? r : 0)) * D) + vc4);
+      }
+      // the freshly appended row comes from shared memory
+      if (new_row >= base && new_row < base + 8) {
+#pragma unroll
+        for (int rg = 0; rg < 2; ++rg)
+          if (base + rg * 4 + rsub == new_row) {
+#pragma unroll
+            for (int i = 0; i < F4; ++i) kreg[rg][i] = reinterpret_cast<const float4*>(kv_new)[l8 + 8 * i];
           }
-          a += __shfl_xor_sync(0xffffffffu, a, 1);
-          a += __shfl_xor_sync(0xffffffffu, a, 2);
-          a += __shfl_xor_sync(0xffffffffu, a, 4);
-          if (l8 == 0) sc[g * tc + r] = rv ? a * p.scale : -INFINITY;
-        }
-      }
-    }
-    __syncthreads();
-    // ---- chunk-local softmax numerators: warp g owns q head g ----
-    if (warp < gq) {
-      float mx = -INFINITY;
-      for (int t = lane; t < tc; t += 32) mx = fmaxf(mx, sc[warp * tc + t]);
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      float sum = 0.f;
-      for (int t = lane; t < tc; t += 32) {
-        const float e = expf(sc[warp * tc + t] - mx);  // exp(-inf) = 0 for masked rows
-        sc[warp * tc + t] = e;
-        sum += e;
+        for (int j = 0; j < VL; ++j)
+          if (base + j * RPL + vrs == new_row) vreg[j] = reinterpret_cast<const float4*>(kv_new + D)[vc4];
       }
+      // ---- scores: sg[rg][g] = (q_g . k_row) * scale, identical in the row's 8 lanes ----
+      float sg[2][kMaxGq];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      if (lane == 0) {
-        ml[warp * 2 + 0] = mx;
-        ml[warp * 2 + 1] = sum;
-      }
-    }
-    if (!has_new) loads_ok = mbar_wait(&bar[1], 0) && loads_ok;
-    __syncthreads();
-    // ---- weighted V: lane owns float4 column c of row (step*RPL + rs) ----
-    {
-      const int c = lane % CPR, rs = lane / CPR;
-      float4 acc[kMaxGq];
-#pragma unroll
-      for (int g = 0; g < kMaxGq; ++g) acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = warp * RPL + rs; r < rows; r += kAttnWarps * RPL) {
-        const float4 v4 = reinterpret_cast<const float4*>(v_s + (size_t)r * D)[c];
+      for (int rg = 0; rg < 2; ++rg) {
+        const bool rv = base + rg * 4 + rsub < rows;
 #pragma unroll
         for (int g = 0; g < kMaxGq; ++g) {
+          float a = 0.f;
           if (g < gq) {
-            const float w = sc[g * tc + r];
-            acc[g].x = fmaf(w, v4.x, acc[g].x);
-            acc[g].y = fmaf(w, v4.y, acc[g].y);
-            acc[g].z = fmaf(w, v4.z, acc[g].z);
-            acc[g].w = fmaf(w, v4.w, acc[g].w);
+            const float4* q4 = reinterpret_cast<const float4*>(q_s + g * D);
+#pragma unroll
+            for (int i = 0; i < F4; ++i) {
+              const float4 qv = q4[l8 + 8 * i];
+              a = fmaf(qv.x, kreg[rg][i].x, a);
+              a = fmaf(qv.y, kreg[rg][i].y, a);
+              a = fmaf(qv.z, kreg[rg][i].z, a);
+              a = fmaf(qv.w, kreg[rg][i].w, a);
+            }
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            a += __shfl_xor_sync(0xffffffffu, a, 4);
+          }
+          sg[rg][g] = rv ? a * p.scale : -INFINITY;
+        }
+      }
+      // ---- online softmax over the pass's 8 rows, then the weighted V ----
+#pragma unroll
+      for (int g = 0; g < kMaxGq; ++g) {
+        if (g < gq) {
+          float mx = fmaxf(sg[0][g], sg[1][g]);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m_run[g], mx);  // finite: the pass has at least one valid row
+          const float resc = expf(m_run[g] - m_new); // exp(-inf) = 0 on the first pass
+          const float e0 = expf(sg[0][g] - m_new), e1 = expf(sg[1][g] - m_new);
+          float ps = (l8 == 0) ? e0 + e1 : 0.f;      // each row counted once
+          ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+          ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+          ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+          ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+          ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+          l_run[g] = l_run[g] * resc + ps;
+          m_run[g] = m_new;
+          acc[g].x *= resc; acc[g].y *= resc; acc[g].z *= resc; acc[g].w *= resc;
+#pragma unroll
+          for (int j = 0; j < VL; ++j) {
+            const int r8 = j * RPL + vrs;                 // row of this lane's V load within the pass
+            const float pw = __shfl_sync(0xffffffffu, (j * RPL) / 4 == 0 ? e0 : e1, (r8 & 3) * 8);
+            acc[g].x = fmaf(pw, vreg[j].x, acc[g].x);
+            acc[g].y = fmaf(pw, vreg[j].y, acc[g].y);
+            acc[g].z = fmaf(pw, vreg[j].z, acc[g].z);
+            acc[g].w = fmaf(pw, vreg[j].w, acc[g].w);
           }
         }
       }
+    }
+    // lanes that share a column (head_dim < 128) add up their rows
 #pragma unroll
-      for (int g = 0; g < kMaxGq; ++g)
-        if (g < gq) reinterpret_cast<float4*>(red + ((size_t)(warp * RPL + rs) * gq + g) * D)[c] = acc[g];
+    for (int g = 0; g < kMaxGq; ++g) {
+      if (g < gq) {
+#pragma unroll
+        for (int o = CPR; o < 32; o <<= 1) {
+          acc[g].x += __shfl_xor_sync(0xffffffffu, acc[g].x, o);
+          acc[g].y += __shfl_xor_sync(0xffffffffu, acc[g].y, o);
+          acc[g].z += __shfl_xor_sync(0xffffffffu, acc[g].z, o);
+          acc[g].w += __shfl_xor_sync(0xffffffffu, acc[g].w, o);
+        }
+        if (lane < CPR) reinterpret_cast<float4*>(w_acc + ((size_t)warp * gq + g) * D)[lane] = acc[g];
+        if (lane == 0) {
+          w_ml[(warp * gq + g) * 2 + 0] = m_run[g];
+          w_ml[(warp * gq + g) * 2 + 1] = l_run[g];
+        }
+      }
     }
     __syncthreads();
+    // ---- combine the 8 warps: the chunk's partial (max, sum, weighted V) ----
     for (int i = tid; i < gq * D; i += kAttnThreads) {
       const int g = i / D, e = i - g * D;
-      float s = 0.f;
+      float mx = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < SL; ++w) s += red[((size_t)w * gq + g) * D + e];
+      for (int w = 0; w < kAttnWarps; ++w) mx = fmaxf(mx, w_ml[(w * gq + g) * 2]);
+      float o = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) {
+        const float mw = w_ml[(w * gq + g) * 2];
+        const float f = mw == -INFINITY ? 0.f : expf(mw - mx);  // warps without rows contribute nothing
+        o = fmaf(w_acc[((size_t)w * gq + g) * D + e], f, o);
+        l = fmaf(w_ml[(w * gq + g) * 2 + 1], f, l);
+      }
       const int h = kvh * gq + g;
-      p.part_o[(((int64_t)b * p.num_heads + h) * p.nc + chunk) * D + e] = s;
+      p.part_o[(((int64_t)b * p.num_heads + h) * p.nc + chunk) * D + e] = o;
+      if (e == 0) {
+        float* dst = p.part_ml + (((int64_t)b * p.num_heads + h) * p.nc + chunk) * 2;
+        dst[0] = mx;
+        dst[1] = l;
+      }
     }
-    if (tid < gq) {
-      const int h = kvh * gq + tid;
-      float* dst = p.part_ml + (((int64_t)b * p.num_heads + h) * p.nc + chunk) * 2;
-      dst[0] = ml[tid * 2 + 0];
-      dst[1] = ml[tid * 2 + 1];
-    }
-    if (!loads_ok && tid == 0) atomicExch(p.err, 1);  // a tile never arrived: results are invalid
   }
 
   // ---- ticket: the last CTA of this (sequence, kv head) merges the partials ----
@@ -293,8 +338,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
     for (int i = tid; i < gq * D; i += kAttnThreads) p.out[((int64_t)b * p.num_heads + h0) * D + i] = 0.f;
     return;
   }
-  // weights of every chunk: warp g owns q head g.  wts [gq][nc] lives in the K|V tile area.
-  float* wts = smem;
+  // weights of every chunk: warp g owns q head g
   if (warp < gq) {
     const float* pml = p.part_ml + ((int64_t)b * p.num_heads + h0 + warp) * p.nc * 2;
     float mx = -INFINITY;
@@ -346,14 +390,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
 }
 
 int pick_chunk(int batch, int num_kv_heads, int gq, int head_dim, int64_t max_seq_len) {
-  // About 3.5 CTAs per SM over the whole grid; the chunk is a power of two in [32, 128] and
-  // large enough for the merge weights [gq][nc] to fit in the K|V tile area.
+  // The smallest chunk (a multiple of the 64 rows one pass of a CTA covers) for which the
+  // whole grid is resident at once (two CTAs per SM), so that no CTA waits for a second wave.
+  (void)gq; (void)head_dim;
   const int64_t cols = (int64_t)batch * num_kv_heads;
-  const int64_t want_nc = (7ll * sm_count() / 2 + cols - 1) / cols;
-  int tc = 128;
-  while (tc > 32 && (max_seq_len + tc - 1) / tc < want_nc) tc >>= 1;
   const int64_t cap = max_seq_len < kSeqCap ? max_seq_len : kSeqCap;
-  while (tc < 256 && (int64_t)gq * ((cap + tc - 1) / tc) > (int64_t)2 * tc * head_dim) tc <<= 1;
+  int tc = 64;
+  while (tc < 512 && cols * ((cap + tc - 1) / tc) > (int64_t)2 * sm_count()) tc <<= 1;
   return tc;
 }
 
@@ -431,9 +474,9 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.scale = 1.0f / sqrtf((float)a.head_dim);
 
   const int D = a.head_dim;
-  if (L.tc < 32 || L.tc > 256 || (L.tc & (L.tc - 1)) || (int64_t)gq * L.nc > (int64_t)2 * L.tc * D)
-    return fail(TB_ERR_ARG, "attention: chunk %d is not a power of two in [32, 256] or too small for %d chunks", L.tc, L.nc);
-  const size_t smem = sizeof(float) * attn_smem_floats(D, L.tc, gq);
+  if (L.tc < 64 || L.tc > 512 || (L.tc & (L.tc - 1)))
+    return fail(TB_ERR_ARG, "attention: chunk %d is not a power of two in [64, 512]", L.tc);
+  const size_t smem = sizeof(float) * attn_smem_floats(D, L.nc, gq);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)L.nc, (unsigned)a.num_kv_heads, (unsigned)a.batch);
   cfg.blockDim = dim3(kAttnThreads);

@@ -71,6 +71,7 @@ struct tb_decoder {
   int32_t* h_feed = nullptr; // pinned: per-step (token, offset) pairs for prefill
   int64_t feed_cap = 0;
   void* attn_scratch = nullptr;
+  void* argmax_scratch = nullptr;
   // layer-0 stage snapshots (TB_DECODER_NO_GRAPH only)
   float *dbg_embed = nullptr, *dbg_normed = nullptr, *dbg_qkv = nullptr, *dbg_attn = nullptr,
         *dbg_x_attn = nullptr, *dbg_h = nullptr, *dbg_x_out = nullptr;
@@ -217,7 +218,7 @@ tb_status build_graph(tb_decoder* d, int b, bool greedy, cudaGraphExec_t* out) {
   cudaGraph_t graph = nullptr;
   DEC_CUDA(d, cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
   tb_status s = enqueue_step(d, b, false);
-  if (s == TB_OK && greedy) s = launch_argmax(d->logits, d->V, b, d->d_tokens, d->d_offsets, d->d_hist, d->d_hist_pos, d->stream);
+  if (s == TB_OK && greedy) s = launch_argmax(d->logits, d->V, b, d->d_tokens, d->d_offsets, d->d_hist, d->d_hist_pos, d->argmax_scratch, d->stream);
   cudaError_t e = cudaStreamEndCapture(d->stream, &graph);
   if (s != TB_OK) {
     if (graph) cudaGraphDestroy(graph);
@@ -251,7 +252,7 @@ tb_status run_step(tb_decoder* d, int b, bool greedy) {
     }
   }
   TB_TRY(enqueue_step(d, b, !d->use_graph && (d->cfg.flags & TB_DECODER_NO_GRAPH)));
-  if (greedy) TB_TRY(launch_argmax(d->logits, d->V, b, d->d_tokens, d->d_offsets, d->d_hist, d->d_hist_pos, d->stream));
+  if (greedy) TB_TRY(launch_argmax(d->logits, d->V, b, d->d_tokens, d->d_offsets, d->d_hist, d->d_hist_pos, d->argmax_scratch, d->stream));
   return TB_OK;
 }
 
@@ -407,6 +408,8 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   const size_t sb = attention_scratch_bytes(B, d->nh_l, d->nkv_l, d->hd, d->S);
   CRC(cudaMalloc(&d->attn_scratch, sb));
   CRC(cudaMemset(d->attn_scratch, 0, sb));
+  CRC(cudaMalloc(&d->argmax_scratch, 16 * kMaxBatch));
+  CRC(cudaMemset(d->argmax_scratch, 0, 16 * kMaxBatch));
   if (c.flags & TB_DECODER_NO_GRAPH) {
     CR(dalloc(&d->dbg_embed, (size_t)H)); CR(dalloc(&d->dbg_normed, (size_t)B * H));
     CR(dalloc(&d->dbg_qkv, (size_t)B * d->tq_l)); CR(dalloc(&d->dbg_attn, (size_t)d->q_dim_l));
@@ -453,6 +456,7 @@ void tb_decoder_destroy(tb_decoder* d) {
   cudaFree(d->d_tokens); cudaFree(d->d_offsets); cudaFree(d->d_eff); cudaFree(d->d_hist); cudaFree(d->d_hist_pos);
   cudaFreeHost(d->h_io); cudaFreeHost(d->h_feed);
   cudaFree(d->attn_scratch);
+  cudaFree(d->argmax_scratch);
   cudaFree(d->dbg_embed); cudaFree(d->dbg_normed); cudaFree(d->dbg_qkv); cudaFree(d->dbg_attn);
   cudaFree(d->dbg_x_attn); cudaFree(d->dbg_h); cudaFree(d->dbg_x_out);
   if (d->stream) cudaStreamDestroy(d->stream);

@@ -58,43 +58,52 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(const float* __restri
 }
 
 // Greedy branch of sample_logits, src/llm/decoder.rs:895-906: the first maximum wins.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t vocab,
-                                                      int32_t* __restrict__ out_tokens,
-                                                      int32_t* __restrict__ next_offsets,
-                                                      int32_t* __restrict__ hist,
-                                                      int32_t* __restrict__ hist_pos) {
-  __shared__ float s_v[32];
-  __shared__ int s_i[32];
-  const float* row = logits + (int64_t)blockIdx.x * vocab;
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+// Several CTAs per row: each folds its slice into a 64-bit key (order-preserving image of the
+// float in the high word, ~index in the low word, so the maximum key is the largest value at
+// the smallest index) with atomicMax; the last CTA of the row publishes the token and resets
+// the row's key and ticket for the next launch.
+__device__ __forceinline__ unsigned int orderable(float v) {
+  const unsigned int u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int64_t vocab,
+                                                     int32_t* __restrict__ out_tokens,
+                                                     int32_t* __restrict__ next_offsets,
+                                                     int32_t* __restrict__ hist,
+                                                     int32_t* __restrict__ hist_pos,
+                                                     unsigned long long* __restrict__ keys,
+                                                     int* __restrict__ tickets) {
+  __shared__ unsigned long long s_key[8];
+  const int b = blockIdx.y;
+  const float* row = logits + (int64_t)b * vocab;
+  unsigned long long best = 0ull;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += (int64_t)gridDim.x * blockDim.x) {
     const float v = row[i];
-    if (v > bv) { bv = v; bi = (int)i; }
+    if (v == v) {  // NaN never wins (the reference compares with >)
+      const unsigned long long k = ((unsigned long long)orderable(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)i);
+      best = k > best ? k : best;
+    }
   }
-  auto better = [](float v, int i, float ov, int oi) { return ov > v || (ov == v && oi < i); };
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (better(bv, bi, ov, oi)) { bv = ov; bi = oi; }
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
   }
-  if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = bv; s_i[threadIdx.x >> 5] = bi; }
+  if ((threadIdx.x & 31) == 0) s_key[threadIdx.x >> 5] = best;
   __syncthreads();
-  if (threadIdx.x < 32) {
-    bv = s_v[threadIdx.x];
-    bi = s_i[threadIdx.x];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (better(bv, bi, ov, oi)) { bv = ov; bi = oi; }
-    }
-    if (threadIdx.x == 0) {
-      const int tok = bi == 0x7fffffff ? 0 : bi;
-      out_tokens[blockIdx.x] = tok;
-      if (next_offsets) next_offsets[blockIdx.x] += 1;
-      if (hist && blockIdx.x == 0) hist[(*hist_pos)++] = tok;
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) best = s_key[w] > best ? s_key[w] : best;
+    atomicMax(&keys[b], best);
+    __threadfence();
+    if (atomicAdd(&tickets[b], 1) == (int)gridDim.x - 1) {
+      __threadfence();
+      const unsigned long long k = atomicExch(&keys[b], 0ull);
+      tickets[b] = 0;
+      const int tok = k == 0ull ? 0 : (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull));
+      out_tokens[b] = tok;
+      if (next_offsets) next_offsets[b] += 1;
+      if (hist && b == 0) hist[(*hist_pos)++] = tok;
     }
   }
 }
@@ -164,9 +173,13 @@ tb_status launch_embed_gather(const float* table, const int32_t* tokens, const i
 }
 
 tb_status launch_argmax(const float* logits, int64_t vocab, int batch, int32_t* out_tokens,
-                        int32_t* next_offsets, int32_t* hist, int32_t* hist_pos,
+                        int32_t* next_offsets, int32_t* hist, int32_t* hist_pos, void* scratch,
                         cudaStream_t stream) {
-  argmax_kernel<<<(unsigned)batch, 1024, 0, stream>>>(logits, vocab, out_tokens, next_offsets, hist, hist_pos);
+  unsigned long long* keys = static_cast<unsigned long long*>(scratch);
+  int* tickets = reinterpret_cast<int*>(keys + batch);
+  int ctas = (int)((vocab + 4095) / 4096);
+  if (ctas > 64) ctas = 64;
+  argmax_kernel<<<dim3((unsigned)ctas, (unsigned)batch), 256, 0, stream>>>(logits, vocab, out_tokens, next_offsets, hist, hist_pos, keys, tickets);
   TB_CUDA_TRY(cudaGetLastError());
   return TB_OK;
 }

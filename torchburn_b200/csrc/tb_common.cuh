@@ -112,7 +112,8 @@ tb_status launch_quantize_int4(const float* w, int64_t n, int64_t k, int g, uint
 // next_offsets is not null, next_offsets[b] += 1 (feeds the next step of a generate loop).
 // When hist is not null, sequence 0's token is appended at hist[(*hist_pos)++].
 tb_status launch_argmax(const float* logits, int64_t vocab, int batch, int32_t* out_tokens,
-                        int32_t* next_offsets, int32_t* hist, int32_t* hist_pos,
+                        int32_t* next_offsets, int32_t* hist, int32_t* hist_pos, void* scratch,
                         cudaStream_t stream);
+// `scratch`: batch * 12 bytes (8-byte aligned), zero before the first launch; left zero.
 
 }  // namespace tb
