@@ -46,7 +46,7 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu capture summarised under profiles/ (None until a capture exists for this kernel).
-DOMINANT_KERNEL_DRAM_TRAFFIC = None
+DOMINANT_KERNEL_DRAM_TRAFFIC = 73_467_392 + 1_368_576  # profiles/w4_stream_kernel_gateup_swiglu_14336x4096.md
 
 
 def measured_peak():
@@ -457,10 +457,13 @@ def run_gpu(args):
     peak, peak_kind = measured_peak()
     alg, sec, _ = time_dominant_kernel(torch, tb, c, layers, device, tp)
     achieved = alg / sec / 1e9
-    roofline = {"bound": "hbm", "kernel": "w4_gemv_kernel<M=1, SwiGLU> (gate/up GEMV + SwiGLU)", "achieved": achieved,
+    roofline = {"bound": "hbm", "kernel": "w4_stream_kernel<EPI=SwiGLU> (gate/up GEMV + SwiGLU, 2 x [14336 x 4096] INT4 g32)", "achieved": achieved,
                 "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": DOMINANT_KERNEL_DRAM_TRAFFIC,
-                "algorithmic_bytes_per_launch": alg, "us_per_launch": sec * 1e6}
+                "algorithmic_bytes_per_launch": alg, "us_per_launch": sec * 1e6,
+                "traffic_note": "dram bytes read+written per launch from the ncu capture of the same kernel and shape (tp=1)"}
+    if tp > 1:
+        roofline["traffic"] = None
     c1_alg, c1_sec = time_c1_gemv(torch, tb, device)
     wb = step_weight_bytes(c) / tp
     kvb = kv_bytes_per_seq(c, CONTEXT) / tp

@@ -43,6 +43,7 @@ struct AttnParams {
   int64_t max_seq_len;
   int per_call_tables;
   float scale;
+  PrefetchList prefetch;
 };
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -136,6 +137,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qkv_dim = (p.num_heads + 2 * p.num_kv_heads) * D;
 
+  if (tid == 32)
+    prefetch_l2_slice(p.prefetch, (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),
+                      (int)(gridDim.x * gridDim.y * gridDim.z));
   pdl_wait();
   pdl_launch_dependents();
 
@@ -472,6 +476,7 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.max_seq_len = a.max_seq_len;
   p.per_call_tables = a.per_call_tables ? 1 : 0;
   p.scale = 1.0f / sqrtf((float)a.head_dim);
+  p.prefetch = a.prefetch;
 
   const int D = a.head_dim;
   if (L.tc < 64 || L.tc > 512 || (L.tc & (L.tc - 1)))

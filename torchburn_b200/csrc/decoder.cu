@@ -86,6 +86,9 @@ struct tb_decoder {
   // its K/V tile copies early; the persistent GEMV kernels run slower when they are made
   // resident before their predecessor has finished, so they keep plain stream order.
   int pdl_mask = 2;
+  // L2 prefetch chain (PrefetchList): measured on B200 it does not pay - the kernels are bound by
+  // their own latency chains, not by HBM - so it is off unless TB_L2_PREFETCH=1.
+  bool prefetch_chain = false;
   int64_t kv_used = 0;
   int last_batch = 1;
   bool device_lost = false;
@@ -139,6 +142,21 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     return TB_OK;
   };
   TB_TRY(snap(d->dbg_embed, d->x, d->H));
+  // L2 prefetch chain (see PrefetchList): each kernel requests what the kernels after it read.
+  const bool pfc = d->prefetch_chain && !debug;
+  const size_t wq = (size_t)(d->H / 2), sq = sizeof(float) * (size_t)(d->H / d->G);
+  auto add_mat = [&](PrefetchList& pf, const uint8_t* w, const float* sc, int64_t n, int64_t k) {
+    if (!pfc) return;
+    pf.add(w, (size_t)n * (k / 2));
+    pf.add(sc, sizeof(float) * (size_t)n * (k / d->G));
+  };
+  auto add_kv = [&](PrefetchList& pf, int layer) {
+    if (!pfc || layer >= d->L) return;
+    const size_t bytes = sizeof(float) * (size_t)b * d->nkv_l * d->S * d->hd;
+    pf.add(d->k_cache + (size_t)layer * kv_layer_stride(d), bytes);
+    pf.add(d->v_cache + (size_t)layer * kv_layer_stride(d), bytes);
+  };
+  (void)wq; (void)sq;
   for (int l = 0; l < d->L; ++l) {
     const LayerDev& W = d->layers[l];
     const bool dbg = debug && l == 0;
@@ -148,6 +166,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.norm_w = W.input_norm_w; a.eps = d->cfg.rms_norm_eps;
       a.x_normed_out = dbg ? d->dbg_normed : nullptr;
       a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 1);
+      if (l == 0) add_kv(a.prefetch, 0);  // later layers: requested by the previous layer's gate/up
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
     }
@@ -160,6 +179,9 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.scratch = d->attn_scratch; a.q_rot_out = dbg ? d->dbg_qkv : nullptr;
       a.batch = b; a.num_heads = d->nh_l; a.num_kv_heads = d->nkv_l; a.head_dim = d->hd;
       a.max_seq_len = d->S; a.pdl = pdl && !debug && (pm & 2);
+      add_mat(a.prefetch, W.o_w, W.o_s, d->H, d->q_dim_l);
+      add_mat(a.prefetch, W.gate_w, W.gate_s, d->I_l, d->H);
+      add_mat(a.prefetch, W.up_w, W.up_s, d->I_l, d->H);
       // The kernel strides sequences by [Hkv, S, d]; with batch > 1 that is the layout of
       // one layer's block [B][Hkv][S][d].
       TB_TRY(launch_attention_decode(a, st));
@@ -170,6 +192,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       GemvArgs a;
       a.x = d->attn; a.w = W.o_w; a.scales = W.o_s; a.m = b; a.n = d->H; a.k = d->q_dim_l; a.g = d->G;
       a.pdl = pdl && !debug && (pm & 4);
+      add_mat(a.prefetch, W.down_w, W.down_s, d->H, d->I_l);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
       TB_TRY(launch_w4_gemv(a, st));
@@ -182,6 +205,14 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x = d->x; a.w = W.gate_w; a.scales = W.gate_s; a.w2 = W.up_w; a.scales2 = W.up_s; a.out = d->h;
       a.norm_w = W.post_norm_w; a.eps = d->cfg.rms_norm_eps;
       a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 8);
+      if (l + 1 < d->L) {
+        add_mat(a.prefetch, d->layers[l + 1].qkv_w, d->layers[l + 1].qkv_s, d->tq_l, d->H);
+        add_kv(a.prefetch, l + 1);
+      } else {
+        // the head of lm_head that fits next to what is still in flight
+        const int64_t rows = d->V_l < 24576 ? d->V_l : 24576;
+        add_mat(a.prefetch, d->lm_w, d->lm_s, rows, d->H);
+      }
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
     }
@@ -332,6 +363,7 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   d->use_graph = !(c.flags & TB_DECODER_NO_GRAPH);
   d->pdl = !(c.flags & TB_DECODER_NO_PDL);
   if (const char* pmv = getenv("TB_PDL_MASK")) d->pdl_mask = atoi(pmv);
+  if (const char* pfv = getenv("TB_L2_PREFETCH")) d->prefetch_chain = atoi(pfv) != 0;
   cudaGetDevice(&d->device);
 
   tb_status s = TB_OK;

@@ -35,8 +35,9 @@ __device__ __forceinline__ uint32_t dp4a_uu(uint32_t a, uint32_t b, uint32_t c) 
 // NWORDS words as fp32 (exact integer parts, combined in fp32).
 template <int NWORDS>
 __device__ __forceinline__ float idot_words(const uint32_t (&w)[NWORDS], const uint32_t (&xq)[NWORDS * 6]) {
-  uint32_t d0 = 0, d1 = 0;
-  int d2 = 0;
+  // two independent accumulator sets (even / odd elements) keep the dp4a chains short
+  uint32_t d0 = 0, d1 = 0, e0 = 0, e1 = 0;
+  int d2 = 0, e2 = 0;
 #pragma unroll
   for (int wd = 0; wd < NWORDS; ++wd) {
     const uint32_t t = w[wd] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
@@ -44,10 +45,11 @@ __device__ __forceinline__ float idot_words(const uint32_t (&w)[NWORDS], const u
     d0 = dp4a_uu(t, xq[wd * 6 + 0], d0);
     d1 = dp4a_uu(t, xq[wd * 6 + 1], d1);
     d2 = dp4a_us(t, xq[wd * 6 + 2], d2);
-    d0 = dp4a_uu(u, xq[wd * 6 + 3], d0);
-    d1 = dp4a_uu(u, xq[wd * 6 + 4], d1);
-    d2 = dp4a_us(u, xq[wd * 6 + 5], d2);
+    e0 = dp4a_uu(u, xq[wd * 6 + 3], e0);
+    e1 = dp4a_uu(u, xq[wd * 6 + 4], e1);
+    e2 = dp4a_us(u, xq[wd * 6 + 5], e2);
   }
+  d0 += e0; d1 += e1; d2 += e2;
   const int i01 = (int)(d0 + (d1 << 8));  // < 2^25, exact
   return fmaf(65536.0f, (float)d2, (float)i01);
 }

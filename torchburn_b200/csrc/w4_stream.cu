@@ -46,6 +46,7 @@ struct StreamParams {
   int stages;        // ring depth
   int stage_bytes;   // bytes of one stage
   int rounds;        // ceil(n / 8): the unit of work distribution (8 rows)
+  PrefetchList prefetch;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -170,6 +171,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
     // The producer must not signal launch_dependents: the next kernel may only start once
     // this grid's consumers are past their griddepcontrol.wait, i.e. once everything before
     // this kernel has completed (kernels further down the chain rely on that).
+    if (lane == 1) prefetch_l2_slice(p.prefetch, (int)blockIdx.x, (int)gridDim.x);
     if (lane == 0) {
       for (int i = 0; i < total_stages; ++i) {
         const int s = i % p.stages, round = i / p.stages;
@@ -412,6 +414,7 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   p.bias[0] = a.bias; p.bias[1] = a.bias2;
   p.norm_w = a.norm_w; p.resid = a.resid; p.out = a.out; p.x_normed_out = a.x_normed_out;
   p.eps = a.eps;
+  p.prefetch = a.prefetch;
   p.n = (int)a.n; p.k = (int)a.k; p.nb32 = (int)(a.k / 32);
   p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
   p.ng = (int)(a.k / a.g);
