@@ -157,7 +157,8 @@ tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_
 void tb_set_attention_chunk(int32_t positions);
 /* Tuning hook for the M = 1 GEMV kernels.  product_mode 1 (default): activations are
  * rounded per 32-element block to 24-bit fixed point and multiplied with integer dot
- * products; 0: fp32 products.  rows_per_warp in {0,1,2,4} and warps in {0,4,8} force
+ * products (M >= 2 on the tensor cores); 0: fp32 products for M = 1; 2: integer products on
+ * CUDA cores for every M (no tensor cores).  rows_per_warp in {0,1,2,4} and warps in {0,4,8} force
  * the launch shape (0 = choose from the matrix size).  Process-wide. */
 void tb_set_gemv_tuning(int32_t product_mode, int32_t rows_per_warp, int32_t warps);
 /* Tuning hook for the persistent M = 1 kernel (one long-lived CTA per SM fed by a ring of

@@ -72,6 +72,7 @@ struct tb_decoder {
   int64_t feed_cap = 0;
   void* attn_scratch = nullptr;
   void* argmax_scratch = nullptr;
+  void* xq_scratch = nullptr;  // digit form of the activations for batch > 1
   // layer-0 stage snapshots (TB_DECODER_NO_GRAPH only)
   float *dbg_embed = nullptr, *dbg_normed = nullptr, *dbg_qkv = nullptr, *dbg_attn = nullptr,
         *dbg_x_attn = nullptr, *dbg_h = nullptr, *dbg_x_out = nullptr;
@@ -167,6 +168,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x_normed_out = dbg ? d->dbg_normed : nullptr;
       a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 1);
       if (l == 0) add_kv(a.prefetch, 0);  // later layers: requested by the previous layer's gate/up
+      a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
     }
@@ -195,6 +197,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       add_mat(a.prefetch, W.down_w, W.down_s, d->H, d->I_l);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
+      a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
       if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches)); }
@@ -213,6 +216,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
         const int64_t rows = d->V_l < 24576 ? d->V_l : 24576;
         add_mat(a.prefetch, d->lm_w, d->lm_s, rows, d->H);
       }
+      a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
     }
@@ -223,6 +227,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.pdl = pdl && !debug && (pm & 16);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
+      a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
       if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches)); }
@@ -236,10 +241,12 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     a.norm_w = d->final_norm_w; a.eps = d->cfg.rms_norm_eps;
     a.m = b; a.n = d->V_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 32);
     a.out = d->tp == 1 ? d->logits : d->logits_l;
+    a.xq_scratch = d->xq_scratch;
     TB_TRY(launch_w4_gemv(a, st));
     ++launches;
     if (d->tp > 1) { TB_TRY(tp_allgather_logits(d->tpst, d->logits_l, d->logits, b, d->V_l, st, &launches)); }
   }
+  if (b > 1) launches += 4 * d->L + 1;  // the activation-digit pass in front of every batched projection
   d->launches_per_step = launches;
   return TB_OK;
 }
@@ -440,6 +447,11 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   const size_t sb = attention_scratch_bytes(B, d->nh_l, d->nkv_l, d->hd, d->S);
   CRC(cudaMalloc(&d->attn_scratch, sb));
   CRC(cudaMemset(d->attn_scratch, 0, sb));
+  if (B > 1) {
+    int64_t kmax = d->H > d->I_l ? d->H : d->I_l;
+    if (d->q_dim_l > kmax) kmax = d->q_dim_l;
+    CRC(cudaMalloc(&d->xq_scratch, w4_mma_scratch_bytes(B, kmax)));
+  }
   CRC(cudaMalloc(&d->argmax_scratch, 16 * kMaxBatch));
   CRC(cudaMemset(d->argmax_scratch, 0, 16 * kMaxBatch));
   if (c.flags & TB_DECODER_NO_GRAPH) {
@@ -489,6 +501,7 @@ void tb_decoder_destroy(tb_decoder* d) {
   cudaFreeHost(d->h_io); cudaFreeHost(d->h_feed);
   cudaFree(d->attn_scratch);
   cudaFree(d->argmax_scratch);
+  cudaFree(d->xq_scratch);
   cudaFree(d->dbg_embed); cudaFree(d->dbg_normed); cudaFree(d->dbg_qkv); cudaFree(d->dbg_attn);
   cudaFree(d->dbg_x_attn); cudaFree(d->dbg_h); cudaFree(d->dbg_x_out);
   if (d->stream) cudaStreamDestroy(d->stream);

@@ -93,12 +93,18 @@ struct GemvArgs {
   int g = 32;
   bool pdl = false;                // launch with programmatic stream serialization
   PrefetchList prefetch;           // operands of later kernels to pull into L2 meanwhile
+  void* xq_scratch = nullptr;      // m > 1: room for the digit form of x (w4_mma_scratch_bytes);
+                                   // null = allocate on the stream for the duration of the call
 };
 
 tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream);
 // Tuning hook: xmode 0 = fp32 products (M = 1 only), 1 = integer products; rows_per_warp /
 // warps force the launch shape of the M = 1 kernels (0 = automatic).
 void set_gemv_tuning(int xmode, int rows_per_warp, int warps);
+
+// Tensor-core kernel for 2 <= M (w4_mma.cu).
+size_t w4_mma_scratch_bytes(int m, int64_t k);
+tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream);
 
 // Persistent TMA-ring kernel for M = 1 (w4_stream.cu).
 bool w4_stream_supported(const GemvArgs& a);

@@ -347,6 +347,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
 
 // Tuning state (process-wide): product mode and an optional forced launch shape.
 int g_xmode = 1;
+int g_mma_enabled = 1;
 int g_force_r = 0, g_force_warps = 0;
 
 template <int M, int R, int WARPS, int EPI, bool NORM, int XMODE>
@@ -434,6 +435,7 @@ tb_status launch_epi(int m, const GemvParams& p, bool pdl, cudaStream_t stream) 
 }  // namespace
 
 void set_gemv_tuning(int xmode, int rows_per_warp, int warps) {
+  g_mma_enabled = xmode == 2 ? 0 : 1;  // 2: integer products on CUDA cores for every M
   g_xmode = xmode != 0 ? 1 : 0;
   g_force_r = rows_per_warp;
   g_force_warps = warps;
@@ -469,6 +471,14 @@ tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
   const int k_pad = (int)((a.k + 1023) / 1024 * 1024);
 
   if (w4_stream_supported(a)) return launch_w4_stream(a, stream);
+  if (a.m >= 2 && g_mma_enabled && ((a.k / 2) % 16) == 0) {
+    if (a.xq_scratch) return launch_w4_mma(a, a.xq_scratch, stream);
+    void* tmp = nullptr;
+    TB_CUDA_TRY(cudaMallocAsync(&tmp, w4_mma_scratch_bytes(a.m < 64 ? a.m : 64, a.k), stream));
+    const tb_status s = launch_w4_mma(a, tmp, stream);
+    cudaFreeAsync(tmp, stream);
+    return s;
+  }
 
   for (int m0 = 0; m0 < a.m; m0 += kMaxM) {
     const int mc = a.m - m0 < kMaxM ? a.m - m0 : kMaxM;

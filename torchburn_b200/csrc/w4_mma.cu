@@ -1,0 +1,304 @@
+// Grouped INT4 W4A32 products for several activation rows (2 <= M <= 64 per pass) on the
+// tensor cores, with exact integer arithmetic.
+//
+// Replaces gemm_w4a32_grouped (src/quantization/gemv.rs:1690-1725: M independent GEMVs) and
+// fused_swiglu_mlp_batched (src/quantization/fused_ops.rs:1267-1319) for M > 1.
+//
+// Step 1 (quantize_x_kernel): every 32-element block of every activation row becomes three
+// byte digits of a 24-bit block-fixed-point number (see w4_math.cuh), optionally after the
+// fused RMSNorm, stored in the fragment order the MMA wants.
+// Step 2 (w4_mma_kernel): per 32-element block of K one mma.sync.m16n8k32 per digit multiplies
+// 16 weight rows (nibbles kept as unsigned bytes: two AND/shift per 32-bit word, no
+// conversion) with 8 activation rows; the three int32 results are combined and scaled by
+// scale[row, group] * sx[m, block] in fp32.  The per-group scale forces that promotion once
+// per 32 elements of K, which - not the tensor pipe - bounds the kernel for M >= 32; the
+// weights are still read from HBM exactly once per pass of up to 64 activation rows.
+#include "tb_common.cuh"
+#include "w4_math.cuh"
+
+namespace tb {
+
+namespace {
+
+constexpr int kTileWords = 208;  // per (block, 8 activation rows): 6 x 32 digit words + 8 sx + 8 corr
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------
+// x [M, K] fp32 -> xq [K/32][Mt][208] words, Mt = ceil(M/8).  Tile layout: word
+// ((d' * 4 + t) * 8 + g) holds digit word d' (0..2 even elements digit 0..2, 3..5 odd elements)
+// of 8-element word t of the block, for activation row 8*mt + g; then sx[8], corr[8].
+// One CTA per activation row (rows >= M are written as zeros).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict__ x, const float* __restrict__ norm_w,
+                                                         float eps, uint32_t* __restrict__ xq, int m_rows, int k,
+                                                         int mt_total, float* __restrict__ x_normed_out) {
+  __shared__ float s_part[8];
+  pdl_wait();
+  const int m = blockIdx.x;
+  const int nb32 = k >> 5;
+  const int mt = m >> 3, g = m & 7;
+  const bool live = m < m_rows;
+  float inv_rms = 1.f;
+  if (norm_w != nullptr && live) {
+    float ss = 0.f;
+    const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)m * k);
+    for (int i = threadIdx.x; i < (k >> 2); i += blockDim.x) {
+      const float4 v = xr[i];
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    inv_rms = 1.0f / sqrtf(tot / (float)k + eps);
+  }
+  for (int blk = threadIdx.x; blk < nb32; blk += blockDim.x) {
+    float v[32];
+    if (live) {
+      const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)m * k) + blk * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 t = xr[j];
+        if (norm_w != nullptr) {
+          const float4 nw = reinterpret_cast<const float4*>(norm_w)[blk * 8 + j];
+          t.x = (t.x * inv_rms) * nw.x; t.y = (t.y * inv_rms) * nw.y;
+          t.z = (t.z * inv_rms) * nw.z; t.w = (t.w * inv_rms) * nw.w;
+          if (x_normed_out != nullptr) reinterpret_cast<float4*>(x_normed_out + (int64_t)m * k)[blk * 8 + j] = t;
+        }
+        v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    }
+    uint32_t dig[24];
+    float sx, corr;
+    quantize_block(v, dig, sx, corr);
+    if (!live) { sx = 0.f; corr = 0.f; }
+    uint32_t* tile = xq + ((size_t)blk * mt_total + mt) * kTileWords;
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int d = 0; d < 6; ++d) tile[(d * 4 + t) * 8 + g] = dig[t * 6 + d];
+    tile[192 + g] = __float_as_uint(sx);
+    tile[200 + g] = __float_as_uint(corr);
+  }
+}
+
+__device__ __forceinline__ void mma_u8u8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+struct MmaParams {
+  const uint32_t* xq;     // [nb32][mt_total][208]
+  const uint8_t* w[2];
+  const float* scales[2];
+  const float* bias[2];
+  const float* resid;
+  float* out;
+  int m, n, k, nb32, gshift, ng, mt_total;
+};
+
+// 4 warps = WR row groups (16 weight rows each) x WM groups of MT activation tiles (8 rows
+// each).  KC blocks of K per pipeline stage, two stages (cp.async).
+template <int MT, int WM, int EPI, int KC>
+__global__ void __launch_bounds__(128) w4_mma_kernel(const MmaParams p) {
+  constexpr int NW = EPI == 1 ? 2 : 1;
+  constexpr int WR = 4 / WM;
+  constexpr int RC = 16 * WR;             // weight rows per CTA
+  constexpr int MTC = MT * WM;            // activation tiles per CTA
+  constexpr int WROW = KC * 4 + 4;        // words per staged weight row (16 bytes of padding)
+  extern __shared__ __align__(16) uint32_t sm[];
+  // stage layout: weights [NW][RC][WROW] | digits [KC][MTC][208]
+  constexpr int W_WORDS = NW * RC * WROW;
+  constexpr int X_WORDS = KC * MTC * kTileWords;
+  constexpr int STAGE = W_WORDS + X_WORDS;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int wr = warp / WM, wm = warp % WM;
+  const int row_base = blockIdx.x * RC;
+  const int mt0 = blockIdx.y * MTC;       // first activation tile of this CTA
+  const int64_t bpr = (int64_t)p.k >> 1;
+  const int nchunks = (p.nb32 + KC - 1) / KC;
+
+  auto issue = [&](int chunk, int stage) {
+    uint32_t* ws = sm + stage * STAGE;
+    uint32_t* xs = ws + W_WORDS;
+    const int b0 = chunk * KC;
+    // weights: RC rows x KC 16-byte pieces per matrix
+    for (int i = tid; i < NW * RC * KC; i += 128) {
+      const int q = i / (RC * KC), r = (i / KC) % RC, c = i % KC;
+      const int row = min(row_base + r, p.n - 1);
+      const int blk = min(b0 + c, p.nb32 - 1);
+      cp_async16(ws + (q * RC + r) * WROW + c * 4, p.w[q] + (int64_t)row * bpr + (int64_t)blk * 16);
+    }
+    // digits: KC x MTC tiles of 832 bytes
+    for (int i = tid; i < KC * MTC * (kTileWords / 4); i += 128) {
+      const int piece = i % (kTileWords / 4), tile = i / (kTileWords / 4);
+      const int c = tile / MTC, mt = tile % MTC;
+      const int blk = min(b0 + c, p.nb32 - 1);
+      const int mtg = min(mt0 + mt, p.mt_total - 1);
+      cp_async16(xs + (c * MTC + mt) * kTileWords + piece * 4,
+                 p.xq + ((size_t)blk * p.mt_total + mtg) * kTileWords + piece * 4);
+    }
+    cp_async_commit();
+  };
+
+  float acc[NW][MT][4];
+#pragma unroll
+  for (int q = 0; q < NW; ++q)
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[q][nt][i] = 0.f;
+
+  pdl_wait();
+  const int r0 = min(row_base + wr * 16 + g, p.n - 1), r1 = min(row_base + wr * 16 + g + 8, p.n - 1);
+  issue(0, 0);
+  for (int ch = 0; ch < nchunks; ++ch) {
+    if (ch + 1 < nchunks) {
+      issue(ch + 1, (ch + 1) & 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t* ws = sm + (ch & 1) * STAGE;
+    const uint32_t* xs = ws + W_WORDS;
+#pragma unroll
+    for (int c = 0; c < KC; ++c) {
+      const int blk = ch * KC + c;
+      if (blk < p.nb32) {
+        const int sidx = blk >> p.gshift;
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          const uint32_t w0 = ws[(q * RC + wr * 16 + g) * WROW + c * 4 + t];
+          const uint32_t w1 = ws[(q * RC + wr * 16 + g + 8) * WROW + c * 4 + t];
+          const uint32_t a[4] = {w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu};
+          const float s0 = __ldg(p.scales[q] + (int64_t)r0 * p.ng + sidx);
+          const float s1 = __ldg(p.scales[q] + (int64_t)r1 * p.ng + sidx);
+#pragma unroll
+          for (int nt = 0; nt < MT; ++nt) {
+            const uint32_t* tile = xs + (c * MTC + wm * MT + nt) * kTileWords;
+            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+            mma_u8u8(c0, a, tile[(0 * 4 + t) * 8 + g], tile[(3 * 4 + t) * 8 + g]);
+            mma_u8u8(c1, a, tile[(1 * 4 + t) * 8 + g], tile[(4 * 4 + t) * 8 + g]);
+            mma_u8s8(c2, a, tile[(2 * 4 + t) * 8 + g], tile[(5 * 4 + t) * 8 + g]);
+            const float2 sx = *reinterpret_cast<const float2*>(tile + 192 + 2 * t);
+            const float2 cr = *reinterpret_cast<const float2*>(tile + 200 + 2 * t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float f = fmaf(65536.0f, (float)c2[i], (float)(c0[i] + (c1[i] << 8)));
+              const float d = fmaf((i & 1) ? sx.y : sx.x, f, (i & 1) ? cr.y : cr.x);
+              acc[q][nt][i] = fmaf(d, (i & 2) ? s1 : s0, acc[q][nt][i]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // accumulator i: row (g + 8 * (i >> 1)), activation row (tile * 8 + 2 * t + (i & 1))
+#pragma unroll
+  for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row_base + wr * 16 + g + 8 * (i >> 1);
+      const int m = (mt0 + wm * MT + nt) * 8 + 2 * t + (i & 1);
+      if (row >= p.n || m >= p.m) continue;
+      float v;
+      if (EPI == 1) {
+        const float gg = acc[0][nt][i] + (p.bias[0] ? p.bias[0][row] : 0.f);
+        const float uu = acc[NW - 1][nt][i] + (p.bias[1] ? p.bias[1][row] : 0.f);
+        v = (gg / (1.0f + expf(-gg))) * uu;  // src/quantization/fused_ops.rs:1305-1311
+      } else {
+        v = acc[0][nt][i] + (p.bias[0] ? p.bias[0][row] : 0.f);
+        if (p.resid) v = p.resid[(int64_t)m * p.n + row] + v;
+      }
+      p.out[(int64_t)m * p.n + row] = v;
+    }
+}
+
+template <int MT, int WM, int EPI, int KC>
+tb_status launch_mma_cfg(const MmaParams& p, cudaStream_t stream) {
+  constexpr int NW = EPI == 1 ? 2 : 1;
+  constexpr int WR = 4 / WM, RC = 16 * WR, MTC = MT * WM;
+  constexpr size_t smem = 2 * sizeof(uint32_t) * ((size_t)NW * RC * (KC * 4 + 4) + (size_t)KC * MTC * kTileWords);
+  auto kern = w4_mma_kernel<MT, WM, EPI, KC>;
+  static thread_local bool configured[64] = {false};
+  int dev = 0;
+  TB_CUDA_TRY(cudaGetDevice(&dev));
+  if (smem > 32 * 1024 && (dev >= 64 || !configured[dev])) {
+    TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 64) configured[dev] = true;
+  }
+  dim3 grid((unsigned)((p.n + RC - 1) / RC), (unsigned)((p.mt_total + MTC - 1) / MTC));
+  kern<<<grid, 128, smem, stream>>>(p);
+  TB_CUDA_TRY(cudaGetLastError());
+  return TB_OK;
+}
+
+template <int EPI>
+tb_status launch_mma_epi(const MmaParams& p, cudaStream_t stream) {
+  // activation tiles of 8 rows: 1 -> (MT 1, WM 1), 2 -> (1, 2), 3..4 -> (2, 2), 5..8 -> (4, 2)
+  if (p.mt_total <= 1) return launch_mma_cfg<1, 1, EPI, 8>(p, stream);
+  if (p.mt_total <= 2) return launch_mma_cfg<1, 2, EPI, 8>(p, stream);
+  if (p.mt_total <= 4) return launch_mma_cfg<2, 2, EPI, 8>(p, stream);
+  return launch_mma_cfg<4, 2, EPI, 4>(p, stream);
+}
+
+}  // namespace
+
+size_t w4_mma_scratch_bytes(int m, int64_t k) {
+  const int mt = (m + 7) / 8;
+  return (size_t)(k / 32) * mt * kTileWords * sizeof(uint32_t);
+}
+
+// Up to 64 activation rows per pass; `scratch` holds w4_mma_scratch_bytes(min(m, 64), k).
+tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
+  if (a.k % 32 != 0 || (reinterpret_cast<uintptr_t>(a.w) & 15) || (a.w2 && (reinterpret_cast<uintptr_t>(a.w2) & 15)) ||
+      ((a.k / 2) % 16) != 0)
+    return fail(TB_ERR_ARG, "w4 mma: k must be a multiple of 32 and the weights 16-byte aligned");
+  for (int m0 = 0; m0 < a.m; m0 += 64) {
+    const int mc = a.m - m0 < 64 ? a.m - m0 : 64;
+    const int mt = (mc + 7) / 8;
+    quantize_x_kernel<<<mt * 8, 256, 0, stream>>>(a.x + (int64_t)m0 * a.k, a.norm_w, a.eps, static_cast<uint32_t*>(scratch), mc,
+                                                  (int)a.k, mt, a.x_normed_out ? a.x_normed_out + (int64_t)m0 * a.k : nullptr);
+    TB_CUDA_TRY(cudaGetLastError());
+    MmaParams p;
+    p.xq = static_cast<const uint32_t*>(scratch);
+    p.w[0] = a.w; p.w[1] = a.w2;
+    p.scales[0] = a.scales; p.scales[1] = a.scales2;
+    p.bias[0] = a.bias; p.bias[1] = a.bias2;
+    p.resid = a.resid ? a.resid + (int64_t)m0 * a.n : nullptr;
+    p.out = a.out + (int64_t)m0 * a.n;
+    p.m = mc; p.n = (int)a.n; p.k = (int)a.k; p.nb32 = (int)(a.k / 32);
+    p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
+    p.ng = (int)(a.k / a.g);
+    p.mt_total = mt;
+    tb_status s = a.w2 ? launch_mma_epi<1>(p, stream) : launch_mma_epi<0>(p, stream);
+    if (s != TB_OK) return s;
+  }
+  return TB_OK;
+}
+
+}  // namespace tb
