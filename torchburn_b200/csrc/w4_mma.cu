@@ -30,10 +30,10 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // of 8-element word t of the block, for activation row 8*mt + g; then sx[8], corr[8].
 // One CTA per activation row (rows >= M are written as zeros).
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict__ x, const float* __restrict__ norm_w,
+__global__ void __launch_bounds__(128) quantize_x_kernel(const float* __restrict__ x, const float* __restrict__ norm_w,
                                                          float eps, uint32_t* __restrict__ xq, int m_rows, int k,
                                                          int mt_total, float* __restrict__ x_normed_out) {
-  __shared__ float s_part[8];
+  __shared__ float s_part[4];
   pdl_wait();
   const int m = blockIdx.x;
   const int nb32 = k >> 5;
@@ -53,10 +53,11 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    for (int i = 0; i < 4; ++i) tot += s_part[i];
     inv_rms = 1.0f / sqrtf(tot / (float)k + eps);
   }
-  for (int blk = threadIdx.x; blk < nb32; blk += blockDim.x) {
+  // blockIdx.y selects a slice of 128 blocks of K
+  for (int blk = blockIdx.y * 128 + threadIdx.x; blk < min(nb32, (int)(blockIdx.y + 1) * 128); blk += blockDim.x) {
     float v[32];
     if (live) {
       const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)m * k) + blk * 8;
@@ -118,10 +119,12 @@ struct MmaParams {
 
 // 4 warps = WR row groups (16 weight rows each) x WM groups of MT activation tiles (8 rows
 // each).  KC blocks of K per pipeline stage, two stages (cp.async).
-template <int MT, int WM, int EPI, int KC>
+// SPLITK (one activation tile only): the four warps share the same 16 weight rows and take
+// every fourth block of K instead, so that a narrow matrix still fills the machine.
+template <int MT, int WM, int EPI, int KC, bool SPLITK>
 __global__ void __launch_bounds__(128) w4_mma_kernel(const MmaParams p) {
   constexpr int NW = EPI == 1 ? 2 : 1;
-  constexpr int WR = 4 / WM;
+  constexpr int WR = SPLITK ? 1 : 4 / WM;
   constexpr int RC = 16 * WR;             // weight rows per CTA
   constexpr int MTC = MT * WM;            // activation tiles per CTA
   constexpr int WROW = KC * 4 + 4;        // words per staged weight row (16 bytes of padding)
@@ -133,7 +136,7 @@ __global__ void __launch_bounds__(128) w4_mma_kernel(const MmaParams p) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int wr = warp / WM, wm = warp % WM;
+  const int wr = SPLITK ? 0 : warp / WM, wm = SPLITK ? 0 : warp % WM;
   const int row_base = blockIdx.x * RC;
   const int mt0 = blockIdx.y * MTC;       // first activation tile of this CTA
   const int64_t bpr = (int64_t)p.k >> 1;
@@ -186,7 +189,7 @@ __global__ void __launch_bounds__(128) w4_mma_kernel(const MmaParams p) {
 #pragma unroll
     for (int c = 0; c < KC; ++c) {
       const int blk = ch * KC + c;
-      if (blk < p.nb32) {
+      if (blk < p.nb32 && (!SPLITK || (c & 3) == warp)) {
         const int sidx = blk >> p.gshift;
 #pragma unroll
         for (int q = 0; q < NW; ++q) {
@@ -217,6 +220,25 @@ __global__ void __launch_bounds__(128) w4_mma_kernel(const MmaParams p) {
     __syncthreads();
   }
 
+  if (SPLITK) {
+    // sum the four warps' partial accumulators (they cover disjoint blocks of K)
+    float* red = reinterpret_cast<float*>(sm);
+#pragma unroll
+    for (int q = 0; q < NW; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[((warp * NW + q) * 4 + i) * 32 + lane] = acc[q][0][i];
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int q = 0; q < NW; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) v += red[((w * NW + q) * 4 + i) * 32 + lane];
+        acc[q][0][i] = v;
+      }
+  }
   // accumulator i: row (g + 8 * (i >> 1)), activation row (tile * 8 + 2 * t + (i & 1))
 #pragma unroll
   for (int nt = 0; nt < MT; ++nt)
@@ -238,12 +260,12 @@ __global__ void __launch_bounds__(128) w4_mma_kernel(const MmaParams p) {
     }
 }
 
-template <int MT, int WM, int EPI, int KC>
+template <int MT, int WM, int EPI, int KC, bool SPLITK>
 tb_status launch_mma_cfg(const MmaParams& p, cudaStream_t stream) {
   constexpr int NW = EPI == 1 ? 2 : 1;
-  constexpr int WR = 4 / WM, RC = 16 * WR, MTC = MT * WM;
+  constexpr int WR = SPLITK ? 1 : 4 / WM, RC = 16 * WR, MTC = MT * WM;
   constexpr size_t smem = 2 * sizeof(uint32_t) * ((size_t)NW * RC * (KC * 4 + 4) + (size_t)KC * MTC * kTileWords);
-  auto kern = w4_mma_kernel<MT, WM, EPI, KC>;
+  auto kern = w4_mma_kernel<MT, WM, EPI, KC, SPLITK>;
   static thread_local bool configured[64] = {false};
   int dev = 0;
   TB_CUDA_TRY(cudaGetDevice(&dev));
@@ -260,10 +282,14 @@ tb_status launch_mma_cfg(const MmaParams& p, cudaStream_t stream) {
 template <int EPI>
 tb_status launch_mma_epi(const MmaParams& p, cudaStream_t stream) {
   // activation tiles of 8 rows: 1 -> (MT 1, WM 1), 2 -> (1, 2), 3..4 -> (2, 2), 5..8 -> (4, 2)
-  if (p.mt_total <= 1) return launch_mma_cfg<1, 1, EPI, 8>(p, stream);
-  if (p.mt_total <= 2) return launch_mma_cfg<1, 2, EPI, 8>(p, stream);
-  if (p.mt_total <= 4) return launch_mma_cfg<2, 2, EPI, 8>(p, stream);
-  return launch_mma_cfg<4, 2, EPI, 4>(p, stream);
+  if (p.mt_total <= 1) {
+    // narrow matrices: 16 rows per CTA with the warps splitting K keeps >= 1 CTA per SM busy
+    if (p.n < 64 * 2 * sm_count()) return launch_mma_cfg<1, 1, EPI, 8, true>(p, stream);
+    return launch_mma_cfg<1, 1, EPI, 8, false>(p, stream);
+  }
+  if (p.mt_total <= 2) return launch_mma_cfg<1, 2, EPI, 8, false>(p, stream);
+  if (p.mt_total <= 4) return launch_mma_cfg<2, 2, EPI, 8, false>(p, stream);
+  return launch_mma_cfg<4, 2, EPI, 4, false>(p, stream);
 }
 
 }  // namespace
@@ -281,7 +307,7 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
   for (int m0 = 0; m0 < a.m; m0 += 64) {
     const int mc = a.m - m0 < 64 ? a.m - m0 : 64;
     const int mt = (mc + 7) / 8;
-    quantize_x_kernel<<<mt * 8, 256, 0, stream>>>(a.x + (int64_t)m0 * a.k, a.norm_w, a.eps, static_cast<uint32_t*>(scratch), mc,
+    quantize_x_kernel<<<dim3((unsigned)(mt * 8), (unsigned)((a.k / 32 + 127) / 128)), 128, 0, stream>>>(a.x + (int64_t)m0 * a.k, a.norm_w, a.eps, static_cast<uint32_t*>(scratch), mc,
                                                   (int)a.k, mt, a.x_normed_out ? a.x_normed_out + (int64_t)m0 * a.k : nullptr);
     TB_CUDA_TRY(cudaGetLastError());
     MmaParams p;
