@@ -41,6 +41,8 @@ import numpy as np
 
 LLAMA8B = dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_layers=32, num_heads=32,
                num_kv_heads=8, head_dim=128, group_size=32, rms_norm_eps=1e-6, rope_theta=500000.0)
+QWEN05B = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_layers=24, num_heads=14,
+               num_kv_heads=2, head_dim=64, group_size=32, rms_norm_eps=1e-6, rope_theta=1000000.0)
 CONTEXT = 4096
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
@@ -211,7 +213,7 @@ def run_reference(args):
 
 def workload_config(c, batch, n_gpus):
     return {
-        "workload": f"llama-3-8b-shaped INT4 (group {c['group_size']}) W4A32 decode, batch {batch}, fp32 KV at context {CONTEXT}",
+        "workload": f"{'llama-3-8b' if c['hidden_size'] == 4096 else 'qwen2.5-0.5b'}-shaped INT4 (group {c['group_size']}) W4A32 decode, batch {batch}, fp32 KV at context {CONTEXT}",
         "hidden": c["hidden_size"], "layers": c["num_layers"], "heads": f"{c['num_heads']}q/{c['num_kv_heads']}kv",
         "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
         "batch": batch, "context": CONTEXT, "parallelism": f"tp{n_gpus}",
@@ -362,7 +364,10 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=device)
     import torchburn_b200 as tb
 
+    global CONTEXT
     c = dict(LLAMA8B)
+    if args.model == "qwen05b":  # BASELINE config 3 (single GPU, context 1024); not the headline workload
+        c, CONTEXT = dict(QWEN05B), 1024
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     max_seq = CONTEXT + 64 * ((K + W + 63) // 64) + 64
     embed, layers, fnorm, lm_p, lm_s = build_model(torch, tb, c, device, tp, rank)
@@ -447,7 +452,8 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
     if args.quick:
-        print(json.dumps({"value": value, "ms_per_step": ms_per_step, "e2e": e2e_value, "n_gpus": tp}), flush=True)
+        print(json.dumps({"value": value, "ms_per_step": ms_per_step, "e2e": e2e_value, "n_gpus": tp, "batch": B, "model": args.model,
+                          "weights_only_frac_of_measured": step_weight_bytes(c) / tp / (ms_per_step * 1e-3) / 1e9 / measured_peak()[0]}), flush=True)
         if tp > 1:
             dist.barrier()
             dec.close()
@@ -506,6 +512,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--model", default="llama8b", choices=["llama8b", "qwen05b"], help="qwen05b: BASELINE config 3, use with --quick")
     ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: plain ncclAllReduce instead of the fused kernel")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between kernels (A/B of programmatic dependent launch)")
