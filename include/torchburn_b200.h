@@ -319,6 +319,35 @@ tb_status tb_decoder_decode_greedy(tb_decoder* dec, int64_t token_id, int64_t of
  * argmax back as the next token without leaving the device; out_tokens [n_new]. */
 tb_status tb_decoder_generate_greedy(tb_decoder* dec, int64_t first_token, int64_t start_offset,
                                      int64_t n_new, int64_t* out_tokens);
+/* Host-side sampling, src/llm/decoder.rs:878-1020.  tb_apply_repetition_penalty: each distinct
+ * in-vocabulary token of `recent` once, positive logits divided by the penalty, negative ones
+ * multiplied (no-op for penalty <= 1).  tb_sample_logits: greedy when temperature <= 0, not
+ * finite, or top_k == 1; otherwise softmax((top-k logits - max) / temperature), optional
+ * nucleus cut (an item is dropped once the mass before it exceeds top_p), then the first
+ * candidate whose running mass reaches uniform01 * kept mass.  The reference draws uniform01
+ * from its thread RNG; here the caller passes it.  tb_push_recent_window keeps the last 64
+ * tokens (`recent` must have room for 64); returns the new length. */
+tb_status tb_apply_repetition_penalty(float* logits, int64_t vocab, const int64_t* recent,
+                                      int64_t n_recent, float penalty);
+tb_status tb_sample_logits(const float* logits, int64_t vocab, float temperature, int64_t top_k,
+                           float top_p, float uniform01, int64_t* token);
+int64_t tb_push_recent_window(int64_t* recent, int64_t n_recent, int64_t token);
+/* decode_and_sample, src/llm/decoder.rs:753-777 / decode_and_sample_inner :835-852: one step,
+ * logits to the host, penalty, sampling.  Greedy settings without a penalty stay on the device
+ * (8 bytes read back).  `rng_state` (non-zero) is advanced by a xorshift64 step per draw. */
+tb_status tb_decoder_decode_and_sample(tb_decoder* dec, int64_t token_id, int64_t offset,
+                                       float temperature, int64_t top_k, float repetition_penalty,
+                                       const int64_t* recent, int64_t n_recent, float top_p,
+                                       uint64_t* rng_state, int64_t* next_token);
+/* generate_loop, src/llm/decoder.rs:791-832: stops at eos_token_id (negative = none) or after
+ * max_new_tokens; recent_seed (may be NULL) seeds the 64-token penalty window.  out_tokens
+ * [max_new_tokens]; *n_out tokens written; *end_offset = seq_len + *n_out. */
+tb_status tb_decoder_generate_loop(tb_decoder* dec, int64_t first_token, int64_t seq_len,
+                                   int64_t max_new_tokens, float temperature, int64_t top_k,
+                                   float repetition_penalty, float top_p, int64_t eos_token_id,
+                                   const int64_t* recent_seed, int64_t n_recent_seed,
+                                   uint64_t* rng_state, int64_t* out_tokens, int64_t* n_out,
+                                   int64_t* end_offset);
 /* Layer-0 intermediates of the last step by name, like debug_step_stages,
  * src/wgpu/profiler.rs:75: "embed", "normed", "qkv", "attn", "x_attn", "h",
  * "x_out".  Only recorded when the decoder was created with TB_DECODER_NO_GRAPH.

@@ -93,6 +93,8 @@ def lib():
         L.tbo_decoder_debug_stage.argtypes = [p, C.c_char_p, C.POINTER(p)]
         L.tbo_decoder_debug_stage.restype = i64
         L.tbo_argmax.argtypes = [p, i64]; L.tbo_argmax.restype = i64
+        L.tbo_apply_repetition_penalty.argtypes = [p, i64, p, i64, f32]
+        L.tbo_sample_logits.argtypes = [p, i64, f32, i64, f32, f32]; L.tbo_sample_logits.restype = i64
         _lib = L
     return _lib
 
@@ -233,6 +235,18 @@ def fused_swiglu_mlp(x, gw, gs, gb, uw, us, ub, dw, ds, db, group_size: int) -> 
 def argmax(logits) -> int:
     l = _f32(logits)
     return int(lib().tbo_argmax(_ptr(l), l.size))
+
+
+def apply_repetition_penalty(logits, recent, penalty: float) -> np.ndarray:
+    l = _f32(logits).copy()
+    r = np.ascontiguousarray(recent, dtype=np.int64)
+    lib().tbo_apply_repetition_penalty(_ptr(l), l.size, _ptr(r), r.size, penalty)
+    return l
+
+
+def sample_logits(logits, temperature: float, top_k: int, top_p: float, u: float) -> int:
+    l = _f32(logits)
+    return int(lib().tbo_sample_logits(_ptr(l), l.size, temperature, top_k, top_p, u))
 
 
 LAYER_KEYS = ["input_norm_w", "qkv_w", "qkv_s", "o_w", "o_s", "post_norm_w", "gate_w", "gate_s",

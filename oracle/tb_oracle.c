@@ -777,3 +777,84 @@ int64_t tbo_argmax(const float* logits, int64_t n) {
     if (logits[i] > bv) { bv = logits[i]; best = i; }
   return best;
 }
+
+/* ---------------------------------------------------------------- sampling */
+
+/* src/llm/decoder.rs:878-899: each distinct in-vocabulary token once. */
+void tbo_apply_repetition_penalty(float* logits, int64_t vocab, const int64_t* recent, int64_t n_recent,
+                                  float penalty) {
+  if (penalty <= 1.0f || n_recent <= 0) return;
+  for (int64_t i = 0; i < n_recent; ++i) {
+    int64_t t = recent[i];
+    if (t < 0 || t >= vocab) continue;
+    int dup = 0;
+    for (int64_t j = 0; j < i; ++j)
+      if (recent[j] == t) { dup = 1; break; }
+    if (dup) continue;
+    float l = logits[t];
+    logits[t] = l > 0.0f ? l / penalty : l * penalty;
+  }
+}
+
+/* src/llm/decoder.rs:908-1020 with the random draw passed in as `u` in [0,1).
+ * Branches restated: greedy; k >= vocab; running top-k for k <= 1024.  (The k > 1024 branch
+ * uses an unstable selection whose order is unspecified; callers compare sets there.) */
+int64_t tbo_sample_logits(const float* logits, int64_t vocab, float temperature, int64_t top_k, float top_p,
+                          float u) {
+  if (vocab == 0) return 0;
+  if (!isfinite(temperature) || temperature <= 0.0f || top_k == 1) return tbo_argmax(logits, vocab);
+  int64_t k = top_k < vocab ? top_k : vocab;
+  if (k < 1) k = 1;
+  int64_t* idx = (int64_t*)malloc(sizeof(int64_t) * (size_t)k);
+  float* val = (float*)malloc(sizeof(float) * (size_t)k);
+  int64_t cnt = 0;
+  if (k >= vocab) {
+    for (int64_t i = 0; i < vocab; ++i) { idx[i] = i; val[i] = isfinite(logits[i]) ? logits[i] : -INFINITY; }
+    cnt = vocab;
+  } else {
+    float min_val = -INFINITY;
+    int64_t min_pos = 0;
+    for (int64_t i = 0; i < vocab; ++i) {
+      float v = isfinite(logits[i]) ? logits[i] : -INFINITY;
+      if (cnt < k) {
+        idx[cnt] = i; val[cnt] = v; ++cnt;
+        if (v < min_val || cnt == 1) { min_val = v; min_pos = cnt - 1; }
+      } else if (v > min_val) {
+        idx[min_pos] = i; val[min_pos] = v;
+        float nm = val[0]; int64_t np = 0;
+        for (int64_t j = 0; j < cnt; ++j) if (val[j] < nm) { nm = val[j]; np = j; }
+        min_val = nm; min_pos = np;
+      }
+    }
+  }
+  float mx = -INFINITY;
+  for (int64_t j = 0; j < cnt; ++j) if (val[j] > mx) mx = val[j];
+  float inv_temp = 1.0f / temperature;
+  for (int64_t j = 0; j < cnt; ++j) val[j] = expf((val[j] - mx) * inv_temp);
+  float pre = 0.f;
+  for (int64_t j = 0; j < cnt; ++j) pre += val[j];
+  int64_t kept = cnt;
+  if (top_p > 0.0f && top_p < 1.0f && kept > 1 && pre > 0.0f) {
+    /* descending by probability (insertion sort keeps equal items in order) */
+    for (int64_t a = 1; a < cnt; ++a) {
+      float v = val[a]; int64_t id = idx[a]; int64_t b = a - 1;
+      while (b >= 0 && val[b] < v) { val[b + 1] = val[b]; idx[b + 1] = idx[b]; --b; }
+      val[b + 1] = v; idx[b + 1] = id;
+    }
+    float inv = 1.0f / pre, cum = 0.f;
+    for (int64_t j = 0; j < cnt; ++j) {
+      if (cum > top_p) { kept = j; break; }
+      cum += val[j] * inv;
+    }
+  }
+  float ks = 0.f;
+  for (int64_t j = 0; j < kept; ++j) ks += val[j];
+  float r = u * ks, acc = 0.f;
+  int64_t out = idx[0];
+  for (int64_t j = 0; j < kept; ++j) {
+    acc += val[j];
+    if (acc >= r) { out = idx[j]; break; }
+  }
+  free(idx); free(val);
+  return out;
+}

@@ -138,6 +138,12 @@ int64_t tbo_decoder_debug_stage(const tbo_decoder* d, const char* name, const fl
 /* src/llm/decoder.rs:878-1020 greedy branch: argmax (first maximum wins). */
 int64_t tbo_argmax(const float* logits, int64_t n);
 
+/* src/llm/decoder.rs:878-899 and :908-1020 (the random draw is the argument u). */
+void tbo_apply_repetition_penalty(float* logits, int64_t vocab, const int64_t* recent, int64_t n_recent,
+                                  float penalty);
+int64_t tbo_sample_logits(const float* logits, int64_t vocab, float temperature, int64_t top_k, float top_p,
+                          float u);
+
 #ifdef __cplusplus
 }
 #endif

@@ -447,9 +447,17 @@ def test_decoder_api_semantics(torch, tb, oracle):
     # greedy decode on the device == argmax of the logits
     dec.reset_kv_cache()
     dec.prefill_tokens(toks[:-1], 0)
-    nxt = dec.decode_and_sample(toks[-1], len(toks) - 1)
+    nxt = dec.decode_and_sample(toks[-1], len(toks) - 1, temperature=0.0)
     assert nxt == oracle.argmax(z["logits"][-1])
-    assert dec.decode_and_sample(cfg["vocab_size"] + 1, 3) == 0
+    assert dec.decode_and_sample(cfg["vocab_size"] + 1, 3, temperature=0.0) == 0
+    # sampling settings: the token comes from the top-k of the step's logits
+    dec.seed(123)
+    lg = dec.step(toks[-1], len(toks) - 1)
+    topk = set(np.argsort(lg)[-5:].tolist())
+    for _ in range(8):
+        assert dec.decode_and_sample(toks[-1], len(toks) - 1, temperature=0.8, top_k=5, top_p=0.95) in topk
+    pen = dec.decode_and_sample(toks[-1], len(toks) - 1, temperature=0.0, repetition_penalty=1e9, recent_tokens=[int(np.argmax(lg))])
+    assert pen != int(np.argmax(lg)) or lg[int(np.argmax(lg))] <= 0
     # device-lost flag is sticky (src/wgpu/decode.rs:692-716)
     assert not dec.is_device_lost()
     dec.mark_device_lost()
@@ -469,12 +477,16 @@ def test_decoder_generate_loop_matches_oracle_chain(torch, tb, oracle):
         srt = np.sort(lg)
         tok = oracle.argmax(lg)
         want.append((tok, srt[-1] - srt[-2]))
-    got = dec.generate_loop(7, 0, 24)
-    for i, (g, (w, margin)) in enumerate(zip(got, want)):
+    got, end = dec.generate_loop(7, 0, 25, temperature=0.0)
+    assert got[0] == 7 and end == 25 and len(got) == 25  # the first token is part of the output (decoder.rs:815)
+    for i, (g, (w, margin)) in enumerate(zip(got[1:], want)):
         if margin < 1e-3 * np.abs(lg).max():
             break  # a near-tie may legitimately flip; the chains diverge after it
         assert g == w, i
-    assert dec.kv_len() == 24
+    assert dec.kv_len() == 25
+    dec.reset_kv_cache()
+    short, end2 = dec.generate_loop(7, 0, 25, temperature=0.0, eos_token_id=got[3])
+    assert short == got[:3] and end2 == 3  # stops before emitting the end-of-sequence token
 
 
 def test_decoder_batch_matches_single_sequences(torch, tb, oracle):

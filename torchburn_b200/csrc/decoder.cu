@@ -95,6 +95,7 @@ struct tb_decoder {
   bool device_lost = false;
   int launches_per_step = 0;
   TpState* tpst = nullptr;
+  std::vector<float> host_logits;  // sampling on the host
 };
 
 namespace {
@@ -685,6 +686,55 @@ tb_status tb_decoder_decode_greedy(tb_decoder* d, int64_t token_id, int64_t offs
     return TB_OK;
   }
   return tb_decoder_generate_greedy(d, token_id, offset, 1, next_token);
+}
+
+namespace {
+float next_uniform(uint64_t* state) {
+  uint64_t x = *state ? *state : 0x9E3779B97F4A7C15ull;
+  x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+  *state = x;
+  return (float)((x >> 40) & 0xFFFFFF) / 16777216.0f;  // 24 random bits in [0, 1)
+}
+}  // namespace
+
+tb_status tb_decoder_decode_and_sample(tb_decoder* d, int64_t token_id, int64_t offset, float temperature,
+                                       int64_t top_k, float repetition_penalty, const int64_t* recent,
+                                       int64_t n_recent, float top_p, uint64_t* rng_state, int64_t* next_token) {
+  TB_TRY(check_alive(d, "tb_decoder_decode_and_sample"));
+  if (!next_token) return fail(TB_ERR_ARG, "tb_decoder_decode_and_sample: null out");
+  const bool greedy = !std::isfinite(temperature) || temperature <= 0.0f || top_k == 1;
+  const bool penalised = repetition_penalty > 1.0f && n_recent > 0;
+  if (greedy && !penalised) return tb_decoder_decode_greedy(d, token_id, offset, next_token);
+  if (d->host_logits.size() < (size_t)d->V) d->host_logits.resize((size_t)d->V);
+  TB_TRY(tb_decoder_step(d, token_id, offset, d->host_logits.data()));
+  TB_TRY(tb_apply_repetition_penalty(d->host_logits.data(), d->V, recent, n_recent, repetition_penalty));
+  uint64_t local = 0x2545F4914F6CDD1Dull;
+  const float u = next_uniform(rng_state ? rng_state : &local);
+  return tb_sample_logits(d->host_logits.data(), d->V, temperature, top_k, top_p, u, next_token);
+}
+
+tb_status tb_decoder_generate_loop(tb_decoder* d, int64_t first_token, int64_t seq_len, int64_t max_new_tokens,
+                                   float temperature, int64_t top_k, float repetition_penalty, float top_p,
+                                   int64_t eos_token_id, const int64_t* recent_seed, int64_t n_recent_seed,
+                                   uint64_t* rng_state, int64_t* out_tokens, int64_t* n_out, int64_t* end_offset) {
+  TB_TRY(check_alive(d, "tb_decoder_generate_loop"));
+  if (!out_tokens || !n_out || max_new_tokens < 0 || seq_len < 0) return fail(TB_ERR_ARG, "tb_decoder_generate_loop: bad arguments");
+  int64_t recent[64];
+  int64_t nrec = 0;
+  for (int64_t i = 0; i < n_recent_seed; ++i) nrec = tb_push_recent_window(recent, nrec, recent_seed[i]);
+  int64_t next = first_token, generated = 0;
+  uint64_t local = 0x2545F4914F6CDD1Dull;
+  while (generated < max_new_tokens) {  // decoder.rs:811-829
+    if (eos_token_id >= 0 && next == eos_token_id) break;
+    out_tokens[generated++] = next;
+    nrec = tb_push_recent_window(recent, nrec, next);
+    const int64_t offset = seq_len + generated - 1;
+    TB_TRY(tb_decoder_decode_and_sample(d, next, offset, temperature, top_k, repetition_penalty, recent, nrec, top_p,
+                                        rng_state ? rng_state : &local, &next));
+  }
+  *n_out = generated;
+  if (end_offset) *end_offset = seq_len + generated;
+  return TB_OK;
 }
 
 tb_status tb_decoder_debug_stage(tb_decoder* d, const char* name, float* out_host, int64_t cap, int64_t* n) {

@@ -98,6 +98,7 @@ class B200QwenDecoder:
         self.max_batch = max_batch
         self.max_seq_len = max_seq_len
         self._logits = np.empty((max_batch, self.vocab_size), np.float32)
+        self._rng = C.c_uint64(0x9E3779B97F4A7C15)
         del ops  # the library copied everything to the device
 
     def __del__(self):
@@ -163,21 +164,34 @@ class B200QwenDecoder:
         check(lib().tb_decoder_verify_tokens(self._h, start_offset, t.ctypes.data, t.size, out.ctypes.data))
         return out
 
-    def decode_and_sample(self, token_id: int, offset: int, temperature: float = 0.0, top_k: int = 1,
+    def decode_and_sample(self, token_id: int, offset: int, temperature: float = 0.7, top_k: int = 40,
+                          repetition_penalty: float = 1.0, recent_tokens: Optional[Sequence[int]] = None,
                           top_p: float = 1.0) -> int:
-        """decode_and_sample (src/llm/decoder.rs:753-789), greedy settings only
-        (temperature <= 0 or top_k == 1): the argmax runs on the device."""
-        if not (temperature <= 0.0 or top_k == 1 or not np.isfinite(temperature)):
-            raise NotImplementedError("only greedy decoding (temperature <= 0 or top_k == 1) runs on the device")
+        """decode_and_sample (src/llm/decoder.rs:753-777): one step, repetition penalty, sampling.
+        Greedy settings without a penalty keep the argmax on the device."""
+        rec = np.ascontiguousarray(recent_tokens if recent_tokens is not None else [], dtype=np.int64)
         nxt = C.c_int64()
-        check(lib().tb_decoder_decode_greedy(self._h, int(token_id), int(offset), C.byref(nxt)))
+        check(lib().tb_decoder_decode_and_sample(self._h, int(token_id), int(offset), temperature, top_k,
+                                                 repetition_penalty, rec.ctypes.data, rec.size, top_p,
+                                                 C.byref(self._rng), C.byref(nxt)))
         return int(nxt.value)
 
-    def generate_loop(self, first_token: int, start_offset: int, max_new_tokens: int) -> List[int]:
-        """generate_loop (src/llm/decoder.rs:791-832) with greedy settings."""
-        out = np.empty(max_new_tokens, np.int64)
-        check(lib().tb_decoder_generate_greedy(self._h, int(first_token), int(start_offset), max_new_tokens, out.ctypes.data))
-        return [int(t) for t in out]
+    def generate_loop(self, first_token: int, seq_len: int, max_new_tokens: int, temperature: float = 0.7,
+                      top_k: int = 40, repetition_penalty: float = 1.0, top_p: float = 1.0,
+                      eos_token_id: Optional[int] = None, recent_seed: Optional[Sequence[int]] = None):
+        """generate_loop (src/llm/decoder.rs:791-832): returns (tokens, final KV position)."""
+        out = np.empty(max(max_new_tokens, 1), np.int64)
+        seed = np.ascontiguousarray(recent_seed if recent_seed is not None else [], dtype=np.int64)
+        n, end = C.c_int64(), C.c_int64()
+        check(lib().tb_decoder_generate_loop(self._h, int(first_token), int(seq_len), int(max_new_tokens), temperature,
+                                             top_k, repetition_penalty, top_p, -1 if eos_token_id is None else int(eos_token_id),
+                                             seed.ctypes.data, seed.size, C.byref(self._rng), out.ctypes.data,
+                                             C.byref(n), C.byref(end)))
+        return [int(t) for t in out[: n.value]], int(end.value)
+
+    def seed(self, value: int) -> None:
+        """Seeds the sampling RNG (the reference uses an unseeded thread RNG)."""
+        self._rng = C.c_uint64(value or 1)
 
     # ---- extras -------------------------------------------------------------
     def read_kv_cache(self, layer: int, seq: int = 0):
