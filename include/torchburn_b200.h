@@ -155,6 +155,10 @@ tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_
  * of two in [64, 512]; 0 = choose from the shape).  Process-wide; plays the role
  * of TORCHBURN_ROWS_PER_WG, src/wgpu/backend.rs:428-437. */
 void tb_set_attention_chunk(int32_t positions);
+/* Tuning hook: how many resident CTAs per SM the attention grid is sized for (the current
+ * sequence length is divided evenly among them) and the depth of each CTA's ring of
+ * shared-memory stages (at most 8).  0 = automatic for either.  Process-wide. */
+void tb_set_attention_tuning(int32_t ctas_per_sm, int32_t ring_stages);
 /* Tuning hook for the M = 1 GEMV kernels.  product_mode 1 (default): activations are
  * rounded per 32-element block to 24-bit fixed point and multiplied with integer dot
  * products (M >= 2 on the tensor cores); 0: fp32 products for M = 1; 2: integer products on

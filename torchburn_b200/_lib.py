@@ -58,6 +58,7 @@ SIGNATURES = {
     "tb_attention_static_scratch_bytes": (_sz, []),
     "tb_attention_decode_static": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i64, _p]),
     "tb_set_attention_chunk": (None, [_i32]),
+    "tb_set_attention_tuning": (None, [_i32, _i32]),
     "tb_set_gemv_tuning": (None, [_i32, _i32, _i32]),
     "tb_set_stream_tuning": (None, [_i32, _i32, _i32, _i32, _i32]),
     "tb_device_fault_flag": (_i32, []),

@@ -5,25 +5,36 @@
 // rope_apply_head :28-68) and the wgpu shaders rope_append.wgsl / attn_decode.wgsl.
 //
 // The reference walks the sequence serially per q head with a two-pass softmax.
-// Here the sequence of every (sequence, kv head) is cut into chunks of `tc`
-// positions, one CTA per chunk (each warp streaming its own rows straight into registers); the CTA serves all q heads that share the kv
-// head, so each K/V row is read from HBM once per step.  Every CTA writes an
-// un-normalised partial (max, sum, weighted V) to scratch; the last CTA of a
-// (sequence, kv head) to finish - found with a ticket counter - rescales and
-// sums the partials.  The result equals the two-pass softmax up to fp32
-// rounding.  HBM-bound: algorithmic bytes = 2 * Hkv * (offset+1) * d * 4 per
-// sequence and layer.
+// Here the positions [0, offset] of every (sequence, kv head) are divided evenly
+// among the CTAs of a grid row, whatever the current length, so that every SM
+// streams its share.  Inside a CTA one producer lane feeds a ring of shared-memory
+// stages with bulk asynchronous copies (32 K rows + 32 V rows per stage, contiguous
+// in the [Hkv, S, d] cache) and the consumer warps score the rows for all q heads
+// that share the kv head, keep an online softmax and accumulate the weighted V -
+// each K/V row is read from HBM once per step and the bytes in flight do not
+// depend on registers or occupancy.  Every CTA writes an un-normalised partial
+// (max, sum, weighted V) to scratch; the last CTA of a (sequence, kv head) to
+// finish - found with a ticket counter - rescales and sums the partials.  The
+// result equals the two-pass softmax up to fp32 rounding.  HBM-bound:
+// algorithmic bytes = 2 * Hkv * (offset+1) * d * 4 per sequence and layer.
 #include "tb_common.cuh"
 
 namespace tb {
 
 namespace {
 
-constexpr int kAttnWarps = 8;
-constexpr int kAttnThreads = kAttnWarps * 32;
-constexpr int kMaxGq = 8;         // q heads per kv head
-constexpr int kSeqCap = 32768;    // src/llm/decoder.rs:1180
-constexpr uint32_t kWaitLimit = 1u << 22;  // mbarrier polls before a tile load is declared lost
+constexpr int kCW = 4;                 // consumer warps per CTA
+constexpr int kCT = kCW * 32;          // consumer threads
+constexpr int kThreads = kCT + 32;     // + the producer warp
+constexpr int kStageRows = 32;         // K rows (and V rows) per ring stage
+constexpr int kWR = kStageRows / kCW;  // rows of a stage that one consumer warp owns (8)
+constexpr int kRG = kWR / 4;           // groups of 4 rows per warp and stage (2)
+constexpr int kMaxGq = 8;              // q heads per kv head
+constexpr int kMaxStages = 8;
+constexpr int kSeqCap = 32768;         // src/llm/decoder.rs:1180
+constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: a wait that long means a lost copy
+
+__device__ int g_attn_fault = 0;
 
 struct AttnParams {
   const float* qkv;
@@ -35,11 +46,13 @@ struct AttnParams {
   float* out;
   float* part_o;    // [b, Hq, nc, D]
   float* part_ml;   // [b, Hq, nc, 2]
-  int* counters;    // [b, Hkv] tickets, then one error word
-  int* err;
+  int* counters;    // [b, Hkv] tickets
   float* qkv_rot_out;
   int num_heads, num_kv_heads, gq;
-  int tc, nc;
+  int fixed_per;    // positions per CTA when forced, else 0: divide the current length evenly
+  int nc;           // CTAs per (sequence, kv head) = gridDim.x
+  int stages;       // ring depth
+  int region_floats;  // floats of the ring region (also holds the combine / merge buffers)
   int64_t max_seq_len;
   int per_call_tables;
   float scale;
@@ -61,16 +74,21 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
       "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-// Bounded wait for phase `parity`; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait; returns false (and raises the abort flag) when the limit ran out or another
+// thread already gave up.  Nobody spins forever: after an abort every wait returns at once.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -78,8 +96,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
+    if ((i & 255) == 255) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
   }
-  return false;
+}
+// Barrier among the consumer threads only (the producer warp leaves early).
+__device__ __forceinline__ void consumer_barrier() {
+  asm volatile("bar.sync 1, %0;" ::"r"(kCT) : "memory");
 }
 
 // rotate-half with separately rounded products, src/llm/decoder.rs:40-66:
@@ -91,88 +119,297 @@ __device__ __forceinline__ float rope_elem(const float* x, const float* c, const
   return __fadd_rn(__fmul_rn(x[i], c[i]), __fmul_rn(x[i - half], s[i]));
 }
 
-// Shared memory (floats): q_s [gq][D] | kv_new [2][D] | w_acc [8][gq][D] | w_ml [8][gq][2] |
-// wts [gq][nc] | red [1024*gq] | ml [2*gq]   (the last three are used by the merge).  Every
-// region starts on a 16-byte boundary (float4 accesses).
-__host__ __device__ inline size_t attn_smem_floats(int D, int nc, int gq) {
-  return (size_t)gq * D + 2 * D + (size_t)kAttnWarps * gq * D + (size_t)((kAttnWarps * gq * 2 + 3) & ~3) +
-         (size_t)((gq * nc + 3) & ~3) + (size_t)1024 * gq + 2 * gq;
+// Shared memory (floats): q_s [gq][D] | kv_new [2][D] | p_s [kCW][kWR + 1][GQM] | w_ml [kCW][gq][2]
+// | region.  The region is the ring (stages * 2 * 32 * D) while rows stream in; afterwards it
+// holds w_acc [kCW][gq][D] for the combine and, in the CTA that merges, wts [gq][nc] | ml [gq] |
+// a tile of partials.  Every part starts on a 16-byte boundary (float4 accesses).
+__host__ __device__ inline size_t up4(size_t v) { return (v + 3) & ~(size_t)3; }
+__host__ __device__ inline size_t attn_fixed_floats(int D, int gq, int gqm) {
+  return up4((size_t)gq * D) + 2 * (size_t)D + up4((size_t)kCW * (kWR + 1) * gqm) + up4((size_t)kCW * gq * 2);
+}
+inline size_t attn_region_floats(int D, int gq, int nc, int stages) {
+  const size_t ring = (size_t)stages * 2 * kStageRows * D;
+  const size_t comb = (size_t)kCW * gq * D;
+  const size_t merge = up4((size_t)gq * nc) + up4(gq) + (size_t)gq * D;
+  size_t r = ring > comb ? ring : comb;
+  return r > merge ? r : merge;
 }
 
-__device__ __forceinline__ float4 ldg_stream_f4(const float4* p) {
-  float4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p));
-  return v;
+// Sums over the 8 lanes that share a K row.  In: v[i] for i < V, this lane's partial sums.
+// Out: v[j] for j < max(1, V/8) holds the complete sum of index
+//   idx = sum_t bit_t(l8) * (V >> (t+1)) + j      (t over the halving steps),
+// so the V sums end up spread over the 8 lanes instead of replicated in all of them.
+template <int V>
+__device__ __forceinline__ void spread_reduce8(float (&v)[V], int l8) {
+  if (V >= 2) {
+    const bool hi = (l8 & 1) != 0;
+#pragma unroll
+    for (int j = 0; j < V / 2; ++j) {
+      const float send = hi ? v[j] : v[j + V / 2];
+      const float keep = hi ? v[j + V / 2] : v[j];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+    }
+  } else {
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+  }
+  if (V >= 4) {
+    const bool hi = (l8 & 2) != 0;
+#pragma unroll
+    for (int j = 0; j < V / 4; ++j) {
+      const float send = hi ? v[j] : v[j + V / 4];
+      const float keep = hi ? v[j + V / 4] : v[j];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+  } else {
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+  }
+  if (V >= 8) {
+    const bool hi = (l8 & 4) != 0;
+#pragma unroll
+    for (int j = 0; j < V / 8; ++j) {
+      const float send = hi ? v[j] : v[j + V / 8];
+      const float keep = hi ? v[j + V / 8] : v[j];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+  } else {
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 4);
+  }
 }
 
-// One CTA = one chunk of tc positions of one (sequence, kv head).  Inside the CTA every warp is
-// on its own: in each pass it takes 8 rows of the chunk, loads their K and V rows straight into
-// registers (all 16 KB requested before anything is consumed), scores them for the gq query
-// heads (8 lanes per row, shuffle reduction), keeps an online softmax (running max / sum) and
-// accumulates the weighted V with one float4 column per lane.  No block-wide barrier sits in
-// that loop; the warps meet once to combine their (max, sum, acc) triples.
-template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const AttnParams p) {
-  constexpr int F4 = D / 32;        // float4 per lane and row in the score phase (8 lanes per row)
-  constexpr int CPR = D / 4;        // float4 columns per row
-  constexpr int RPL = 32 / CPR;     // rows per warp-wide load in the V phase
-  constexpr int VL = 8 / RPL;       // V loads per lane and pass
-  constexpr int SL = kAttnThreads / CPR;  // chunk slices in the merge
+// Per-warp softmax state.  After spread_reduce8 a lane owns NV (row, q head) scores of the
+// warp's 8 rows; it keeps the running max and sum of its q heads (all lanes that own the same
+// head hold the same values) and a float4 column of the weighted V for every head.
+template <int D, int GQM>
+struct WarpState {
+  static constexpr int V = kRG * GQM;
+  static constexpr int NV = V >= 8 ? V / 8 : 1;
+  float m_run[NV], l_run[NV];
+  float4 acc[GQM];
+};
+
+// One consumer warp takes `nr` (1..8) rows that lie in shared memory: K rows at kb, V rows at vb.
+template <int D, int GQM, bool QREG>
+__device__ __forceinline__ void consume_rows(const float* __restrict__ kb, const float* __restrict__ vb, int nr,
+                                             int gq, float scale, const float4 (&qreg)[QREG ? GQM : 1][D / 32],
+                                             const float* __restrict__ q_s, float* __restrict__ p_w,
+                                             WarpState<D, GQM>& st, int lane) {
+  constexpr int F4 = D / 32;   // float4 per lane and row in the score phase (8 lanes per row)
+  constexpr int CPR = D / 4;   // float4 columns per row
+  constexpr int RPL = 32 / CPR;  // rows per warp-wide V load
+  constexpr int V = kRG * GQM;
+  constexpr int NV = WarpState<D, GQM>::NV;
+  constexpr int HSTEPS = V >= 8 ? 3 : (V == 4 ? 2 : (V == 2 ? 1 : 0));
+  const int l8 = lane & 7, rsub = lane >> 3;
+
+  // ---- scores of 8 rows x GQM heads: partial dot products, then the spread reduction ----
+  float v[V];
+#pragma unroll
+  for (int rg = 0; rg < kRG; ++rg) {
+    const int row = rg * 4 + rsub;
+    float4 kf[F4];
+#pragma unroll
+    for (int i = 0; i < F4; ++i)
+      kf[i] = row < nr ? reinterpret_cast<const float4*>(kb)[row * CPR + l8 + 8 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int g = 0; g < GQM; ++g) {
+      float a0 = 0.f, a1 = 0.f;
+      if (g < gq) {
+#pragma unroll
+        for (int i = 0; i < F4; ++i) {
+          const float4 qv = QREG ? qreg[QREG ? g : 0][i] : reinterpret_cast<const float4*>(q_s)[g * CPR + l8 + 8 * i];
+          a0 = fmaf(qv.x, kf[i].x, a0);
+          a1 = fmaf(qv.y, kf[i].y, a1);
+          a0 = fmaf(qv.z, kf[i].z, a0);
+          a1 = fmaf(qv.w, kf[i].w, a1);
+        }
+      }
+      v[rg * GQM + g] = a0 + a1;
+    }
+  }
+  spread_reduce8<V>(v, l8);
+  // which (row group, head) this lane's value(s) belong to
+  int idx0 = 0;
+#pragma unroll
+  for (int t = 0; t < HSTEPS; ++t) idx0 += ((l8 >> t) & 1) * (V >> (t + 1));
+  const bool writer = l8 < V;  // for V < 8 the sums are replicated over the unused lane bits
+
+  bool need = false;
+  float e[NV], resc[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int idx = idx0 + j;
+    const int rg = idx / GQM;
+    const int row = rg * 4 + rsub;
+    const float s = row < nr ? v[j] * scale : -INFINITY;
+    // max over the 8 rows of the same head: the row lives in lane bits 3-4 and (two groups) bit 0
+    float mx = s;
+    if (kRG == 2) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+    const float m_new = fmaxf(st.m_run[j], mx);   // finite: row 0 is always valid
+    e[j] = expf(s - m_new);                        // 0 for rows past nr
+    float ps = e[j];
+    if (kRG == 2) ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+    resc[j] = expf(st.m_run[j] - m_new);           // exp(-inf) = 0 the first time
+    need |= m_new > st.m_run[j];
+    st.l_run[j] = st.l_run[j] * resc[j] + ps;
+    st.m_run[j] = m_new;
+  }
+  // weights (and, in row kWR, the rescale factors) to shared memory: p_w[row][g]
+  if (writer) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int idx = idx0 + j;
+      const int rg = idx / GQM, g = idx % GQM;
+      p_w[(rg * 4 + rsub) * GQM + g] = e[j];
+      if (rg == 0 && rsub == 0) p_w[kWR * GQM + g] = resc[j];
+    }
+  }
+  const bool any_need = __any_sync(0xffffffffu, need);
+  __syncwarp();
+  if (any_need) {
+#pragma unroll
+    for (int g = 0; g < GQM; ++g) {
+      const float r = p_w[kWR * GQM + g];
+      st.acc[g].x *= r; st.acc[g].y *= r; st.acc[g].z *= r; st.acc[g].w *= r;
+    }
+  }
+  // ---- weighted V: one float4 column per lane ----
+  const int vc4 = lane % CPR, vrs = lane / CPR;
+#pragma unroll
+  for (int j = 0; j < kWR / RPL; ++j) {
+    const int r = j * RPL + vrs;
+    if (r < nr) {
+      const float4 vv = reinterpret_cast<const float4*>(vb)[r * CPR + vc4];
+      float pg[GQM];
+      if (GQM >= 4) {
+#pragma unroll
+        for (int q4 = 0; q4 < GQM / 4; ++q4) {
+          const float4 t = reinterpret_cast<const float4*>(p_w + r * GQM)[q4];
+          pg[q4 * 4 + 0] = t.x; pg[q4 * 4 + 1] = t.y; pg[q4 * 4 + 2] = t.z; pg[q4 * 4 + 3] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < GQM; ++g) pg[g] = p_w[r * GQM + g];
+      }
+#pragma unroll
+      for (int g = 0; g < GQM; ++g) {
+        st.acc[g].x = fmaf(pg[g], vv.x, st.acc[g].x);
+        st.acc[g].y = fmaf(pg[g], vv.y, st.acc[g].y);
+        st.acc[g].z = fmaf(pg[g], vv.z, st.acc[g].z);
+        st.acc[g].w = fmaf(pg[g], vv.w, st.acc[g].w);
+      }
+    }
+  }
+  __syncwarp();  // p_w is rewritten by the next call
+}
+
+template <int D, int GQM>
+__global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
+  constexpr int F4 = D / 32;
+  constexpr int CPR = D / 4;
+  constexpr bool QREG = GQM * F4 <= 16;
+  constexpr int V = kRG * GQM;
+  constexpr int NV = WarpState<D, GQM>::NV;
+  constexpr int HSTEPS = V >= 8 ? 3 : (V == 4 ? 2 : (V == 2 ? 1 : 0));
   static_assert(D == 32 || D == 64 || D == 128, "head_dim");
 
   extern __shared__ __align__(128) float smem[];
-  const int gq = p.gq, tc = p.tc;
-  float* q_s = smem;
-  float* kv_new = q_s + gq * D;
-  float* w_acc = kv_new + 2 * D;
-  float* w_ml = w_acc + (size_t)kAttnWarps * gq * D;
-  float* wts = w_ml + ((kAttnWarps * gq * 2 + 3) & ~3);
-  float* red = wts + (((size_t)gq * p.nc + 3) & ~(size_t)3);
-  float* ml = red + 1024 * gq;
+  __shared__ __align__(8) uint64_t full[kMaxStages];
+  __shared__ __align__(8) uint64_t empty[kMaxStages];
+  __shared__ int s_abort;
   __shared__ int s_last;
 
-  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int gq = p.gq;
+  float* q_s = smem;
+  float* kv_new = q_s + up4((size_t)gq * D);
+  float* p_s = kv_new + 2 * D;
+  float* w_ml = p_s + up4((size_t)kCW * (kWR + 1) * GQM);
+  float* region = w_ml + up4((size_t)kCW * gq * 2);
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qkv_dim = (p.num_heads + 2 * p.num_kv_heads) * D;
 
-  if (tid == 32)
-    prefetch_l2_slice(p.prefetch, (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),
-                      (int)(gridDim.x * gridDim.y * gridDim.z));
-  pdl_wait();
-  pdl_launch_dependents();
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kCW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
 
+  // Before griddepcontrol.wait only data from at least two kernels back may be touched: the
+  // offsets (written at the start of the step) and the cache rows of earlier steps.  The kernel
+  // directly ahead produces qkv and nothing else, and it signals its dependents only after its
+  // own wait, so everything older is complete when this code runs.  The plan and the whole
+  // K/V stream therefore start while that kernel is still draining; only the q-dependent
+  // work waits.
   const int off = p.offsets[b];
   const bool seq_ok = off >= 0 && (int64_t)off < p.max_seq_len;
   const int t_end = seq_ok ? min(off + 1, kSeqCap) : 0;  // attend to [0, t_end)
-  const int t0 = chunk * tc;
-  const int nvalid_chunks = (t_end + tc - 1) / tc;
+  int per = p.fixed_per;
+  if (per <= 0) {
+    per = (t_end + p.nc - 1) / p.nc;
+    per = max(kStageRows, (per + kStageRows - 1) & ~(kStageRows - 1));
+  }
+  const int nvalid = (t_end + per - 1) / per;   // CTAs of this grid row that have positions
+  const int t0 = split * per;
   const bool active = t0 < t_end;
-  const int rows = active ? min(tc, t_end - t0) : 0;
+  const int rows = active ? min(per, t_end - t0) : 0;
+  // The CTA that holds position `off` appends the new k (rotated) and v to the cache.  That
+  // row is the last one of its range; it is taken from shared memory, not from the cache.
+  const bool has_new = active && off >= t0 && off < t0 + rows;
+  const int ring_rows = rows - (has_new ? 1 : 0);
+  const int nstages = (ring_rows + kStageRows - 1) / kStageRows;
   float* kc = p.k_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
   float* vc = p.v_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
-  const float* qkv_b = p.qkv + (int64_t)b * qkv_dim;
+  const int stage_floats = 2 * kStageRows * D;
 
+  if (warp == kCW) {
+    // ---------------- producer: one lane feeds the ring ----------------
+    if (lane == 1)
+      prefetch_l2_slice(p.prefetch, (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),
+                        (int)(gridDim.x * gridDim.y * gridDim.z));
+    if (lane == 0) {
+      for (int i = 0; i < nstages; ++i) {
+        const int s = i % p.stages, round = i / p.stages;
+        if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
+        const int nr = min(kStageRows, ring_rows - i * kStageRows);
+        const uint32_t bytes = (uint32_t)nr * D * sizeof(float);
+        float* dst = region + (size_t)s * stage_floats;
+        mbar_expect_tx(&full[s], 2 * bytes);
+        bulk_g2s(dst, kc + (int64_t)(t0 + i * kStageRows) * D, bytes, &full[s]);
+        bulk_g2s(dst + kStageRows * D, vc + (int64_t)(t0 + i * kStageRows) * D, bytes, &full[s]);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* qkv_b = p.qkv + (int64_t)b * qkv_dim;
   if (active) {
     const float* cs = p.cos_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
     const float* sn = p.sin_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
     // q heads of this kv head, rotated, into shared memory.
-    for (int i = tid; i < gq * D; i += kAttnThreads) {
+    for (int i = tid; i < gq * D; i += kCT) {
       const int g = i / D, e = i - g * D;
       const float* xh = qkv_b + (int64_t)(kvh * gq + g) * D;
       const float v = rope_elem(xh, cs, sn, e, D / 2);
       q_s[g * D + e] = v;
-      if (p.qkv_rot_out && chunk == 0)
+      if (p.qkv_rot_out && split == 0)
         p.qkv_rot_out[(int64_t)b * qkv_dim + (int64_t)(kvh * gq + g) * D + e] = v;
     }
-    // The chunk that holds position `off` appends the new k (rotated) and v to the cache and
-    // keeps a copy: its rows are read below while that store may still be in flight.
-    const int new_row = off - t0;  // in [0, tc) only for that chunk
-    if (new_row >= 0 && new_row < tc) {
+    if (has_new) {
       const float* kx = qkv_b + (int64_t)p.num_heads * D + (int64_t)kvh * D;
       const float* vx = kx + (int64_t)p.num_kv_heads * D;
-      for (int e = tid; e < D; e += kAttnThreads) {
+      for (int e = tid; e < D; e += kCT) {
         const float kr = rope_elem(kx, cs, sn, e, D / 2);
         const float vr = vx[e];
         kc[(int64_t)off * D + e] = kr;
@@ -186,139 +423,94 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
         }
       }
     }
-    __syncthreads();
+    consumer_barrier();
 
-    const int l8 = lane & 7, rsub = lane >> 3;   // score phase: 8 lanes per row, 4 rows per group
-    const int vc4 = lane % CPR, vrs = lane / CPR; // V phase: one float4 column per lane
-    float m_run[kMaxGq], l_run[kMaxGq];
-    float4 acc[kMaxGq];
+    const int l8 = lane & 7;
+    float4 qreg[QREG ? GQM : 1][F4];
+    if (QREG) {
 #pragma unroll
-    for (int g = 0; g < kMaxGq; ++g) {
-      m_run[g] = -INFINITY;
-      l_run[g] = 0.f;
-      acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int g = 0; g < GQM; ++g)
+#pragma unroll
+        for (int i = 0; i < F4; ++i)
+          qreg[QREG ? g : 0][i] = g < gq ? reinterpret_cast<const float4*>(q_s)[g * CPR + l8 + 8 * i]
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int base = warp * 8; base < rows; base += kAttnWarps * 8) {
-      // ---- request the 8 K rows and 8 V rows of this pass ----
-      float4 kreg[2][F4];
-      float4 vreg[VL];
+    WarpState<D, GQM> st;
 #pragma unroll
-      for (int rg = 0; rg < 2; ++rg) {
-        const int r = base + rg * 4 + rsub;
-        const float4* krow = reinterpret_cast<const float4*>(kc + (int64_t)(t0 + (r < rows ? r : 0)) * D);
-#pragma unroll
-        for (int i = 0; i < F4; ++i) kreg[rg][i] = ldg_stream_f4(krow + l8 + 8 * i);
-      }
-#pragma unroll
-      for (int j = 0; j < VL; ++j) {
-        const int r = base + j * RPL + vrs;
-        vreg[j] = ldg_stream_f4(reinterpret_cast<const float4*>(vc + (int64_t)(t0 + (r < rows ? r : 0)) * D) + vc4);
-      }
-      // the freshly appended row comes from shared memory
-      if (new_row >= base && new_row < base + 8) {
-#pragma unroll
-        for (int rg = 0; rg < 2; ++rg)
-          if (base + rg * 4 + rsub == new_row) {
-#pragma unroll
-            for (int i = 0; i < F4; ++i) kreg[rg][i] = reinterpret_cast<const float4*>(kv_new)[l8 + 8 * i];
-          }
-#pragma unroll
-        for (int j = 0; j < VL; ++j)
-          if (base + j * RPL + vrs == new_row) vreg[j] = reinterpret_cast<const float4*>(kv_new + D)[vc4];
-      }
-      // ---- scores: sg[rg][g] = (q_g . k_row) * scale, identical in the row's 8 lanes ----
-      float sg[2][kMaxGq];
-#pragma unroll
-      for (int rg = 0; rg < 2; ++rg) {
-        const bool rv = base + rg * 4 + rsub < rows;
-#pragma unroll
-        for (int g = 0; g < kMaxGq; ++g) {
-          float a = 0.f;
-          if (g < gq) {
-            const float4* q4 = reinterpret_cast<const float4*>(q_s + g * D);
-#pragma unroll
-            for (int i = 0; i < F4; ++i) {
-              const float4 qv = q4[l8 + 8 * i];
-              a = fmaf(qv.x, kreg[rg][i].x, a);
-              a = fmaf(qv.y, kreg[rg][i].y, a);
-              a = fmaf(qv.z, kreg[rg][i].z, a);
-              a = fmaf(qv.w, kreg[rg][i].w, a);
-            }
-            a += __shfl_xor_sync(0xffffffffu, a, 1);
-            a += __shfl_xor_sync(0xffffffffu, a, 2);
-            a += __shfl_xor_sync(0xffffffffu, a, 4);
-          }
-          sg[rg][g] = rv ? a * p.scale : -INFINITY;
-        }
-      }
-      // ---- online softmax over the pass's 8 rows, then the weighted V ----
-#pragma unroll
-      for (int g = 0; g < kMaxGq; ++g) {
-        if (g < gq) {
-          float mx = fmaxf(sg[0][g], sg[1][g]);
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-          const float m_new = fmaxf(m_run[g], mx);  // finite: the pass has at least one valid row
-          const float resc = expf(m_run[g] - m_new); // exp(-inf) = 0 on the first pass
-          const float e0 = expf(sg[0][g] - m_new), e1 = expf(sg[1][g] - m_new);
-          float ps = (l8 == 0) ? e0 + e1 : 0.f;      // each row counted once
-          ps += __shfl_xor_sync(0xffffffffu, ps, 8);
-          ps += __shfl_xor_sync(0xffffffffu, ps, 16);
-          ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-          ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-          ps += __shfl_xor_sync(0xffffffffu, ps, 4);
-          l_run[g] = l_run[g] * resc + ps;
-          m_run[g] = m_new;
-          acc[g].x *= resc; acc[g].y *= resc; acc[g].z *= resc; acc[g].w *= resc;
-#pragma unroll
-          for (int j = 0; j < VL; ++j) {
-            const int r8 = j * RPL + vrs;                 // row of this lane's V load within the pass
-            const float pw = __shfl_sync(0xffffffffu, (j * RPL) / 4 == 0 ? e0 : e1, (r8 & 3) * 8);
-            acc[g].x = fmaf(pw, vreg[j].x, acc[g].x);
-            acc[g].y = fmaf(pw, vreg[j].y, acc[g].y);
-            acc[g].z = fmaf(pw, vreg[j].z, acc[g].z);
-            acc[g].w = fmaf(pw, vreg[j].w, acc[g].w);
-          }
-        }
-      }
+    for (int j = 0; j < NV; ++j) {
+      st.m_run[j] = -INFINITY;
+      st.l_run[j] = 0.f;
     }
-    // lanes that share a column (head_dim < 128) add up their rows
 #pragma unroll
-    for (int g = 0; g < kMaxGq; ++g) {
+    for (int g = 0; g < GQM; ++g) st.acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float* p_w = p_s + (size_t)warp * (kWR + 1) * GQM;
+
+#pragma unroll 1
+    for (int i = 0; i < nstages; ++i) {
+      const int s = i % p.stages;
+      const bool ok = mbar_wait(&full[s], (uint32_t)(i / p.stages) & 1u, &s_abort);
+      const int nr_stage = min(kStageRows, ring_rows - i * kStageRows);
+      const int nr = min(kWR, nr_stage - warp * kWR);
+      if (ok && nr > 0) {
+        const float* kb = region + (size_t)s * stage_floats + (size_t)warp * kWR * D;
+        consume_rows<D, GQM, QREG>(kb, kb + kStageRows * D, nr, gq, p.scale, qreg, q_s, p_w, st, lane);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    if (has_new && warp == 0) consume_rows<D, GQM, QREG>(kv_new, kv_new + D, 1, gq, p.scale, qreg, q_s, p_w, st, lane);
+
+    // ---- the warps' (max, sum, weighted V) into the region that was the ring ----
+    consumer_barrier();  // every warp is done with the ring
+    float* w_acc = region;
+#pragma unroll
+    for (int g = 0; g < GQM; ++g) {
       if (g < gq) {
 #pragma unroll
-        for (int o = CPR; o < 32; o <<= 1) {
-          acc[g].x += __shfl_xor_sync(0xffffffffu, acc[g].x, o);
-          acc[g].y += __shfl_xor_sync(0xffffffffu, acc[g].y, o);
-          acc[g].z += __shfl_xor_sync(0xffffffffu, acc[g].z, o);
-          acc[g].w += __shfl_xor_sync(0xffffffffu, acc[g].w, o);
+        for (int o = CPR; o < 32; o <<= 1) {  // lanes that share a column (head_dim < 128)
+          st.acc[g].x += __shfl_xor_sync(0xffffffffu, st.acc[g].x, o);
+          st.acc[g].y += __shfl_xor_sync(0xffffffffu, st.acc[g].y, o);
+          st.acc[g].z += __shfl_xor_sync(0xffffffffu, st.acc[g].z, o);
+          st.acc[g].w += __shfl_xor_sync(0xffffffffu, st.acc[g].w, o);
         }
-        if (lane < CPR) reinterpret_cast<float4*>(w_acc + ((size_t)warp * gq + g) * D)[lane] = acc[g];
-        if (lane == 0) {
-          w_ml[(warp * gq + g) * 2 + 0] = m_run[g];
-          w_ml[(warp * gq + g) * 2 + 1] = l_run[g];
+        if (lane < CPR) reinterpret_cast<float4*>(w_acc + ((size_t)warp * gq + g) * D)[lane] = st.acc[g];
+      }
+    }
+    {
+      int idx0 = 0;
+#pragma unroll
+      for (int t = 0; t < HSTEPS; ++t) idx0 += ((l8 >> t) & 1) * (V >> (t + 1));
+      if (lane < 8 && l8 < V) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int idx = idx0 + j;
+          const int rg = idx / GQM, g = idx % GQM;
+          if (rg == 0 && g < gq) {
+            w_ml[(warp * gq + g) * 2 + 0] = st.m_run[j];
+            w_ml[(warp * gq + g) * 2 + 1] = st.l_run[j];
+          }
         }
       }
     }
-    __syncthreads();
-    // ---- combine the 8 warps: the chunk's partial (max, sum, weighted V) ----
-    for (int i = tid; i < gq * D; i += kAttnThreads) {
+    consumer_barrier();
+    // ---- combine the warps: this CTA's partial ----
+    for (int i = tid; i < gq * D; i += kCT) {
       const int g = i / D, e = i - g * D;
       float mx = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kAttnWarps; ++w) mx = fmaxf(mx, w_ml[(w * gq + g) * 2]);
+      for (int w = 0; w < kCW; ++w) mx = fmaxf(mx, w_ml[(w * gq + g) * 2]);
       float o = 0.f, l = 0.f;
 #pragma unroll
-      for (int w = 0; w < kAttnWarps; ++w) {
+      for (int w = 0; w < kCW; ++w) {
         const float mw = w_ml[(w * gq + g) * 2];
         const float f = mw == -INFINITY ? 0.f : expf(mw - mx);  // warps without rows contribute nothing
         o = fmaf(w_acc[((size_t)w * gq + g) * D + e], f, o);
         l = fmaf(w_ml[(w * gq + g) * 2 + 1], f, l);
       }
       const int h = kvh * gq + g;
-      p.part_o[(((int64_t)b * p.num_heads + h) * p.nc + chunk) * D + e] = o;
+      p.part_o[(((int64_t)b * p.num_heads + h) * p.nc + split) * D + e] = o;
       if (e == 0) {
-        float* dst = p.part_ml + (((int64_t)b * p.num_heads + h) * p.nc + chunk) * 2;
+        float* dst = p.part_ml + (((int64_t)b * p.num_heads + h) * p.nc + split) * 2;
         dst[0] = mx;
         dst[1] = l;
       }
@@ -327,96 +519,140 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
 
   // ---- ticket: the last CTA of this (sequence, kv head) merges the partials ----
   __threadfence();
-  __syncthreads();
+  consumer_barrier();
   if (tid == 0) {
+    if (s_abort) atomicExch(&g_attn_fault, 1);
     const int ticket = atomicAdd(&p.counters[b * p.num_kv_heads + kvh], 1);
     s_last = (ticket == (int)gridDim.x - 1);
   }
-  __syncthreads();
+  consumer_barrier();
   if (!s_last) return;
   __threadfence();
   if (tid == 0) p.counters[b * p.num_kv_heads + kvh] = 0;  // ready for the next launch
 
   const int h0 = kvh * gq;
-  if (nvalid_chunks == 0) {
-    for (int i = tid; i < gq * D; i += kAttnThreads) p.out[((int64_t)b * p.num_heads + h0) * D + i] = 0.f;
+  if (nvalid == 0) {
+    for (int i = tid; i < gq * D; i += kCT) p.out[((int64_t)b * p.num_heads + h0) * D + i] = 0.f;
     return;
   }
-  // weights of every chunk: warp g owns q head g
-  if (warp < gq) {
-    const float* pml = p.part_ml + ((int64_t)b * p.num_heads + h0 + warp) * p.nc * 2;
+  // Layout of the region now: wts [gq][nc] | ml [gq] | tile [gq][cc][D], cc partials at a time.
+  float* wts = region;
+  float* ml = wts + up4((size_t)gq * p.nc);
+  float* tile = ml + up4(gq);
+  const int cc = (int)min((int64_t)nvalid, (int64_t)(p.region_floats - (tile - region)) / ((int64_t)gq * D));
+  const float* po = p.part_o + ((int64_t)b * p.num_heads + h0) * p.nc * D;
+  // Request the first tile of partials (asynchronous copies, no registers held) before the
+  // weights are worked out, so that both trips to L2 overlap.
+  auto request_tile = [&](int c0, int n) {
+    for (int i = tid; i < gq * n * CPR; i += kCT) {
+      const int g = i / (n * CPR), r = i - g * (n * CPR);  // r = chunk-in-tile * CPR + column
+      const float* src = po + ((int64_t)g * p.nc + c0) * D + (int64_t)r * 4;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(tile + ((size_t)g * cc) * D + (size_t)r * 4)),
+                   "l"(src)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  request_tile(0, min(cc, nvalid));
+  // weights of every partial: one warp per q head
+  for (int g = warp; g < gq; g += kCW) {
+    const float* pml = p.part_ml + ((int64_t)b * p.num_heads + h0 + g) * p.nc * 2;
     float mx = -INFINITY;
-    for (int c = lane; c < nvalid_chunks; c += 32) mx = fmaxf(mx, __ldcg(pml + c * 2));
+    for (int c = lane; c < nvalid; c += 32) mx = fmaxf(mx, __ldcg(pml + c * 2));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float tot = 0.f;
-    for (int c = lane; c < nvalid_chunks; c += 32) {
+    for (int c = lane; c < nvalid; c += 32) {
       const float w = expf(__ldcg(pml + c * 2) - mx);
-      wts[warp * p.nc + c] = w;
+      wts[g * p.nc + c] = w;
       tot = fmaf(__ldcg(pml + c * 2 + 1), w, tot);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-    if (lane == 0) ml[warp] = 1.0f / fmaxf(tot, 1e-30f);  // src/llm/decoder.rs:1203
+    if (lane == 0) ml[g] = 1.0f / fmaxf(tot, 1e-30f);  // src/llm/decoder.rs:1203
   }
-  __syncthreads();
-  {
-    const int c4 = tid % CPR, sl = tid / CPR;
-    float4 acc[kMaxGq];
+  // Each thread owns float4 outputs o = tid, tid + kCT, ... of the gq * CPR in this kv head.
+  constexpr int OPT = (GQM * CPR + kCT - 1) / kCT;
+  float4 acc[OPT];
 #pragma unroll
-    for (int g = 0; g < kMaxGq; ++g) acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4* po = reinterpret_cast<const float4*>(p.part_o + ((int64_t)b * p.num_heads + h0) * p.nc * D);
-    for (int c = sl; c < nvalid_chunks; c += SL) {
+  for (int k = 0; k < OPT; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = 0; c0 < nvalid; c0 += cc) {
+    const int n = min(cc, nvalid - c0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    consumer_barrier();  // the tile and (first time) the weights are in shared memory
 #pragma unroll
-      for (int g = 0; g < kMaxGq; ++g) {
-        if (g < gq) {
-          const float4 v = __ldcg(po + ((int64_t)g * p.nc + c) * CPR + c4);
-          const float w = wts[g * p.nc + c];
-          acc[g].x = fmaf(w, v.x, acc[g].x);
-          acc[g].y = fmaf(w, v.y, acc[g].y);
-          acc[g].z = fmaf(w, v.z, acc[g].z);
-          acc[g].w = fmaf(w, v.w, acc[g].w);
+    for (int k = 0; k < OPT; ++k) {
+      const int o = tid + k * kCT;
+      if (o < gq * CPR) {
+        const int g = o / CPR, col = o - g * CPR;
+        const float4* t4 = reinterpret_cast<const float4*>(tile + ((size_t)g * cc) * D) + col;
+        const float* w = wts + g * p.nc + c0;
+        for (int c = 0; c < n; ++c) {
+          const float4 v = t4[c * CPR];
+          const float wc = w[c];
+          acc[k].x = fmaf(wc, v.x, acc[k].x);
+          acc[k].y = fmaf(wc, v.y, acc[k].y);
+          acc[k].z = fmaf(wc, v.z, acc[k].z);
+          acc[k].w = fmaf(wc, v.w, acc[k].w);
         }
       }
     }
-#pragma unroll
-    for (int g = 0; g < kMaxGq; ++g)
-      if (g < gq) reinterpret_cast<float4*>(red + ((size_t)sl * gq + g) * D)[c4] = acc[g];
+    if (c0 + cc < nvalid) {
+      consumer_barrier();  // everybody is done with the tile before it is overwritten
+      request_tile(c0 + cc, min(cc, nvalid - c0 - cc));
+    }
   }
-  __syncthreads();
-  for (int i = tid; i < gq * D; i += kAttnThreads) {
-    const int g = i / D, e = i - g * D;
-    float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < SL; ++w) s += red[((size_t)w * gq + g) * D + e];
-    p.out[((int64_t)b * p.num_heads + h0 + g) * D + e] = s * ml[g];
+  for (int k = 0; k < OPT; ++k) {
+    const int o = tid + k * kCT;
+    if (o < gq * CPR) {
+      const int g = o / CPR, col = o - g * CPR;
+      const float r = ml[g];
+      reinterpret_cast<float4*>(p.out + ((int64_t)b * p.num_heads + h0 + g) * D)[col] =
+          make_float4(acc[k].x * r, acc[k].y * r, acc[k].z * r, acc[k].w * r);
+    }
   }
-}
-
-int pick_chunk(int batch, int num_kv_heads, int gq, int head_dim, int64_t max_seq_len) {
-  // The smallest chunk (a multiple of the 64 rows one pass of a CTA covers) for which the
-  // whole grid is resident at once (two CTAs per SM), so that no CTA waits for a second wave.
-  (void)gq; (void)head_dim;
-  const int64_t cols = (int64_t)batch * num_kv_heads;
-  const int64_t cap = max_seq_len < kSeqCap ? max_seq_len : kSeqCap;
-  int tc = 64;
-  while (tc < 512 && cols * ((cap + tc - 1) / tc) > (int64_t)2 * sm_count()) tc <<= 1;
-  return tc;
 }
 
 int g_chunk_override = 0;
+int g_ctas_per_sm = 0;   // 0 = automatic (2)
+int g_ring_stages = 0;   // 0 = automatic
 
 struct AttnLayout {
-  int tc, nc;
+  int fixed_per;  // 0 = divide the current length evenly among the nc CTAs
+  int nc;         // CTAs per (sequence, kv head)
+  int stages;
   size_t part_o, part_ml;
 };
 
+// Upper bound of CTAs per (sequence, kv head) that the scratch block is sized for.
+int max_splits(int64_t max_seq_len) {
+  const int64_t cap = max_seq_len < kSeqCap ? max_seq_len : kSeqCap;
+  return (int)((cap + 31) / 32);
+}
+
 AttnLayout attn_layout(int batch, int num_heads, int num_kv_heads, int head_dim, int64_t max_seq_len) {
   AttnLayout L;
-  const int gq = num_heads / num_kv_heads;
-  L.tc = g_chunk_override > 0 ? g_chunk_override : pick_chunk(batch, num_kv_heads, gq, head_dim, max_seq_len);
   const int64_t cap = max_seq_len < kSeqCap ? max_seq_len : kSeqCap;
-  L.nc = (int)((cap + L.tc - 1) / L.tc);
+  const int64_t cols = (int64_t)batch * num_kv_heads;
+  // Ring depth: 96 KB of stages for head_dim 128 (two CTAs per SM), fewer bytes for narrower heads.
+  const int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : 2;
+  L.stages = head_dim == 128 ? 3 : (head_dim == 64 ? 4 : 6);
+  if (cps == 1) L.stages *= 2;
+  if (g_ring_stages > 0) L.stages = g_ring_stages;
+  if (L.stages > kMaxStages) L.stages = kMaxStages;
+  if (g_chunk_override > 0) {
+    L.fixed_per = g_chunk_override;
+    L.nc = (int)((cap + L.fixed_per - 1) / L.fixed_per);
+  } else {
+    // two resident CTAs per SM, all of them busy whatever the current length
+    L.fixed_per = 0;
+    int64_t nc = ((int64_t)cps * sm_count()) / cols;
+    const int64_t most = (cap + kStageRows - 1) / kStageRows;
+    if (nc > most) nc = most;
+    if (nc < 1) nc = 1;
+    L.nc = (int)nc;
+  }
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
   L.part_o = up((size_t)batch * num_heads * L.nc * head_dim * sizeof(float));
   L.part_ml = up((size_t)batch * num_heads * L.nc * 2 * sizeof(float));
@@ -426,14 +662,23 @@ AttnLayout attn_layout(int batch, int num_heads, int num_kv_heads, int head_dim,
 }  // namespace
 
 void set_attention_chunk_override(int tc) { g_chunk_override = tc; }
+void set_attention_tuning(int ctas_per_sm, int stages) {
+  g_ctas_per_sm = ctas_per_sm;
+  g_ring_stages = stages;
+}
+
+int attention_fault_flag() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attn_fault, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
 
 // Scratch = partials + ticket counters.  The counters must be zero before the
 // first launch; every launch leaves them zero again.
 size_t attention_scratch_bytes(int batch, int num_heads, int num_kv_heads, int head_dim,
                                int64_t max_seq_len) {
-  // sized for the smallest chunk so that a later override cannot outgrow it
-  const int64_t cap = max_seq_len < kSeqCap ? max_seq_len : kSeqCap;
-  const int nc = (int)((cap + 31) / 32);
+  // sized for the largest number of CTAs per (sequence, kv head) any setting can ask for
+  const int nc = max_splits(max_seq_len);
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
   return up((size_t)batch * num_heads * nc * head_dim * sizeof(float)) +
          up((size_t)batch * num_heads * nc * 2 * sizeof(float)) +
@@ -448,6 +693,25 @@ size_t attention_counters_offset(int batch, int num_heads, int num_kv_heads, int
   return total - cb;
 }
 
+template <int D, int GQM>
+static tb_status launch_attn(const AttnParams& p, const cudaLaunchConfig_t& cfg) {
+  if (cfg.dynamicSmemBytes > 32 * 1024)
+    TB_CUDA_TRY(cudaFuncSetAttribute(attn_decode_kernel<D, GQM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)cfg.dynamicSmemBytes));
+  TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<D, GQM>, p));
+  return TB_OK;
+}
+
+template <int D>
+static tb_status launch_attn_d(const AttnParams& p, const cudaLaunchConfig_t& cfg, int gqm) {
+  switch (gqm) {
+    case 1: return launch_attn<D, 1>(p, cfg);
+    case 2: return launch_attn<D, 2>(p, cfg);
+    case 4: return launch_attn<D, 4>(p, cfg);
+    default: return launch_attn<D, 8>(p, cfg);
+  }
+}
+
 tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   if (!a.qkv || !a.k_cache || !a.v_cache || !a.cos_t || !a.sin_t || !a.offsets || !a.out || !a.scratch)
     return fail(TB_ERR_ARG, "attention: null operand");
@@ -458,10 +722,17 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   if (a.head_dim != 32 && a.head_dim != 64 && a.head_dim != 128)
     return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: head_dim %d (supported: 32, 64, 128)", a.head_dim);
   if (a.batch < 1 || a.max_seq_len < 1) return fail(TB_ERR_SHAPE, "attention: empty shape");
+  if ((reinterpret_cast<uintptr_t>(a.k_cache) | reinterpret_cast<uintptr_t>(a.v_cache)) & 15)
+    return fail(TB_ERR_ARG, "attention: the KV caches must be 16-byte aligned");
 
   const AttnLayout L = attn_layout(a.batch, a.num_heads, a.num_kv_heads, a.head_dim, a.max_seq_len);
+  if (L.fixed_per && (L.fixed_per < 64 || L.fixed_per > 512 || (L.fixed_per & (L.fixed_per - 1))))
+    return fail(TB_ERR_ARG, "attention: chunk %d is not a power of two in [64, 512]", L.fixed_per);
+  if (L.nc > max_splits(a.max_seq_len)) return fail(TB_ERR_SHAPE, "attention: %d splits exceed the scratch layout", L.nc);
   size_t cbytes = 0;
   const size_t coff = attention_counters_offset(a.batch, a.num_heads, a.num_kv_heads, a.head_dim, a.max_seq_len, &cbytes);
+  const int gqm = gq <= 1 ? 1 : (gq <= 2 ? 2 : (gq <= 4 ? 4 : 8));
+  const int D = a.head_dim;
   AttnParams p;
   p.qkv = a.qkv; p.k_cache = a.k_cache; p.v_cache = a.v_cache;
   p.cos_t = a.cos_t; p.sin_t = a.sin_t; p.offsets = a.offsets; p.out = a.out;
@@ -469,22 +740,21 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.part_o = reinterpret_cast<float*>(base);
   p.part_ml = reinterpret_cast<float*>(base + L.part_o);
   p.counters = reinterpret_cast<int*>(base + coff);
-  p.err = p.counters + (size_t)a.batch * a.num_kv_heads;
   p.qkv_rot_out = a.q_rot_out;
   p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.gq = gq;
-  p.tc = L.tc; p.nc = L.nc;
+  p.fixed_per = L.fixed_per; p.nc = L.nc; p.stages = L.stages;
+  const size_t region = attn_region_floats(D, gq, L.nc, L.stages);
+  p.region_floats = (int)region;
   p.max_seq_len = a.max_seq_len;
   p.per_call_tables = a.per_call_tables ? 1 : 0;
   p.scale = 1.0f / sqrtf((float)a.head_dim);
   p.prefetch = a.prefetch;
 
-  const int D = a.head_dim;
-  if (L.tc < 64 || L.tc > 512 || (L.tc & (L.tc - 1)))
-    return fail(TB_ERR_ARG, "attention: chunk %d is not a power of two in [64, 512]", L.tc);
-  const size_t smem = sizeof(float) * attn_smem_floats(D, L.nc, gq);
+  const size_t smem = sizeof(float) * (attn_fixed_floats(D, gq, gqm) + region);
+  if (smem > 200 * 1024) return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: attention needs %zu bytes of shared memory", smem);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)L.nc, (unsigned)a.num_kv_heads, (unsigned)a.batch);
-  cfg.blockDim = dim3(kAttnThreads);
+  cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -492,22 +762,9 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 1 : 0;
-  auto set_smem = [&](auto kern) -> cudaError_t {
-    if (smem > 32 * 1024)
-      return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return cudaSuccess;
-  };
-  if (D == 128) {
-    TB_CUDA_TRY(set_smem(attn_decode_kernel<128>));
-    TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, p));
-  } else if (D == 64) {
-    TB_CUDA_TRY(set_smem(attn_decode_kernel<64>));
-    TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, p));
-  } else {
-    TB_CUDA_TRY(set_smem(attn_decode_kernel<32>));
-    TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<32>, p));
-  }
-  return TB_OK;
+  if (D == 128) return launch_attn_d<128>(p, cfg, gqm);
+  if (D == 64) return launch_attn_d<64>(p, cfg, gqm);
+  return launch_attn_d<32>(p, cfg, gqm);
 }
 
 // ---------------------------------------------------------------------------

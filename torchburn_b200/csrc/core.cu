@@ -209,6 +209,9 @@ tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_
 }
 
 void tb_set_attention_chunk(int32_t tc) { set_attention_chunk_override(tc); }
+void tb_set_attention_tuning(int32_t ctas_per_sm, int32_t ring_stages) {
+  set_attention_tuning(ctas_per_sm < 0 ? 0 : ctas_per_sm, ring_stages < 0 ? 0 : ring_stages);
+}
 
 void tb_set_gemv_tuning(int32_t xmode, int32_t rows_per_warp, int32_t warps) { set_gemv_tuning(xmode, rows_per_warp, warps); }
 
@@ -216,7 +219,11 @@ void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb,
   set_stream_tuning(enabled, ctas_per_sm, ring_kb, epl, groups);
 }
 
-int32_t tb_device_fault_flag(void) { return stream_fault_flag(); }
+int32_t tb_device_fault_flag(void) {
+  const int a = stream_fault_flag(), b = attention_fault_flag();
+  if (a < 0 || b < 0) return -1;
+  return (a | b) ? 1 : 0;
+}
 
 /* ------------------------------------------------------------ QuantizedLinear */
 

@@ -136,6 +136,10 @@ size_t attention_counters_offset(int batch, int num_heads, int num_kv_heads, int
                                  int64_t max_seq_len, size_t* counter_bytes);
 // Tuning hook: force the positions per attention CTA (0 = automatic).
 void set_attention_chunk_override(int tc);
+// Tuning hook: resident CTAs per SM the grid is sized for and ring depth (0 = automatic).
+void set_attention_tuning(int ctas_per_sm, int stages);
+// 1 once a bounded wait of the attention kernel ran out (results of that launch are invalid).
+int attention_fault_flag();
 tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream);
 // The library's built-in scratch block for tb_attention_decode_static (attention.cu).
 size_t static_attention_scratch_capacity();
