@@ -151,6 +151,17 @@ tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_
                                      int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
                                      int64_t max_seq_len, void* stream);
 
+/* Profiling hook in the role of the reference's timestamp queries (src/wgpu/profiler.rs:1-120).
+ * After a device buffer is registered, every launch of the streaming GEMV and of the attention
+ * kernel - launches recorded into a CUDA graph included, so register before the first step of a
+ * decoder - takes the next block of 4104 64-bit words: words 0-1 = {kind (1 GEMV, 2 attention),
+ * grid size}, then for each of the first 512 CTAs eight %globaltimer values in ns: 0 entry,
+ * 1 past the grid dependency wait, 2 activations ready, 3 first stage arrived, 4 last stage
+ * consumed, 5 exit, 6 first copy requested, 7 last copy requested.  NULL switches it off.
+ * tb_debug_timeline_blocks returns how many blocks were handed out. */
+void tb_debug_timeline(void* device_buffer, int64_t bytes);
+int32_t tb_debug_timeline_blocks(void);
+
 /* Tuning hook: positions of the KV sequence handled per attention CTA (a power
  * of two in [64, 512]; 0 = choose from the shape).  Process-wide; plays the role
  * of TORCHBURN_ROWS_PER_WG, src/wgpu/backend.rs:428-437. */

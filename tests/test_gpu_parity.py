@@ -561,3 +561,33 @@ def test_decoder_qwen05b_config3_full_width(torch, tb, oracle):
     dec_ng.copy_kv_cache_from_tensors(list(ks), list(vs), 1023)
     c = dec_ng.step(int(toks[1023]), 1023)
     assert max_rel_err(c, a) < 1e-6
+
+
+def test_decoder_width_2048_persistent_kernels_match_oracle(torch, tb, oracle):
+    # Hidden 2048 / intermediate 4096 is the narrowest shape at which every projection of a
+    # layer takes the persistent streaming kernel, i.e. the path the Llama-3-8B-sized workload
+    # runs (split RMSNorm: pre-weighted activations and per-8 sums of squares between kernels).
+    # Non-trivial norm weights; logits and the layer-0 stages against the oracle, and the graph
+    # replay against direct launches (which use the unsplit norm) within fp32 rounding.
+    cfg = dict(vocab_size=1024, hidden_size=2048, intermediate_size=4096, num_layers=3, num_heads=16,
+               num_kv_heads=4, head_dim=128, group_size=32, max_seq_len=96, rms_norm_eps=1e-5, rope_theta=5e5, tied=False)
+    embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 21, oracle.quantize_int4_grouped)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    dbg = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, debug=True)
+    toks = np.random.default_rng(5).integers(0, cfg["vocab_size"], 40)
+    for off, t in enumerate(toks):
+        want = ref.step(int(t), off)
+        got = dec.step(int(t), off)
+        assert max_rel_err(got, want) < LOGIT_TOL, off
+        if off % 13 == 0:
+            got_dbg = dbg.step(int(t), off)
+            assert max_rel_err(got_dbg, want) < LOGIT_TOL
+            assert max_rel_err(got, got_dbg) < 1e-4
+            for name in ("normed", "x_attn", "h", "x_out"):
+                assert max_rel_err(dbg.debug_stage(name), ref.debug_stage(name)) < STAGE_TOL, (off, name)
+        else:
+            dbg.step(int(t), off)
+    gk, gv = dec.read_kv_cache(2)
+    ek, ev = ref.kv_cache(2)
+    assert max_rel_err(gk[:, :40], ek[:, :40]) < STAGE_TOL and max_rel_err(gv[:, :40], ev[:, :40]) < STAGE_TOL

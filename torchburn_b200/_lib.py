@@ -5,7 +5,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libtorchburn_b200.so")
+# TORCHBURN_B200_LIB points at a library built elsewhere (default: the in-tree build).
+LIB_PATH = os.environ.get("TORCHBURN_B200_LIB") or os.path.join(_HERE, "lib", "libtorchburn_b200.so")
 
 TB_OK = 0
 TB_HOST, TB_DEVICE = 0, 1
@@ -57,6 +58,8 @@ SIGNATURES = {
     "tb_attention_decode": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i64, _p]),
     "tb_attention_static_scratch_bytes": (_sz, []),
     "tb_attention_decode_static": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i64, _p]),
+    "tb_debug_timeline": (None, [_p, _i64]),
+    "tb_debug_timeline_blocks": (_i32, []),
     "tb_set_attention_chunk": (None, [_i32]),
     "tb_set_attention_tuning": (None, [_i32, _i32]),
     "tb_set_gemv_tuning": (None, [_i32, _i32, _i32]),

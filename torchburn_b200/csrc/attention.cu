@@ -23,7 +23,10 @@ namespace tb {
 
 namespace {
 
-constexpr int kCW = 4;                 // consumer warps per CTA
+#ifndef TB_ATTN_CW
+#define TB_ATTN_CW 4
+#endif
+constexpr int kCW = TB_ATTN_CW;        // consumer warps per CTA
 constexpr int kCT = kCW * 32;          // consumer threads
 constexpr int kThreads = kCT + 32;     // + the producer warp
 constexpr int kStageRows = 32;         // K rows (and V rows) per ring stage
@@ -57,6 +60,7 @@ struct AttnParams {
   int per_call_tables;
   float scale;
   PrefetchList prefetch;
+  unsigned long long* tl;  // timestamps of this launch or null
 };
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -307,7 +311,7 @@ __device__ __forceinline__ void consume_rows(const float* __restrict__ kb, const
 }
 
 template <int D, int GQM>
-__global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kThreads, kCW == 8 ? 2 : 1) attn_decode_kernel(const AttnParams p) {
   constexpr int F4 = D / 32;
   constexpr int CPR = D / 4;
   constexpr bool QREG = GQM * F4 <= 16;
@@ -342,6 +346,11 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  const int cta_lin = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+  if (tid == 0) {
+    tl_mark(p.tl, cta_lin, 0);
+    if (cta_lin == 0) tl_header(p.tl, 2, (int)(gridDim.x * gridDim.y * gridDim.z));
+  }
 
   // Before griddepcontrol.wait only data from at least two kernels back may be touched: the
   // offsets (written at the start of the step) and the cache rows of earlier steps.  The kernel
@@ -379,6 +388,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
       for (int i = 0; i < nstages; ++i) {
         const int s = i % p.stages, round = i / p.stages;
         if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
+        if (i == 0) tl_mark(p.tl, cta_lin, 6);
+        if (i == nstages - 1) tl_mark(p.tl, cta_lin, 7);
         const int nr = min(kStageRows, ring_rows - i * kStageRows);
         const uint32_t bytes = (uint32_t)nr * D * sizeof(float);
         float* dst = region + (size_t)s * stage_floats;
@@ -393,6 +404,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
   // ---------------- consumers ----------------
   pdl_wait();
   pdl_launch_dependents();
+  if (tid == 0) tl_mark(p.tl, cta_lin, 1);
   const float* qkv_b = p.qkv + (int64_t)b * qkv_dim;
   if (active) {
     const float* cs = p.cos_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
@@ -424,6 +436,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
       }
     }
     consumer_barrier();
+    if (tid == 0) tl_mark(p.tl, cta_lin, 2);
 
     const int l8 = lane & 7;
     float4 qreg[QREG ? GQM : 1][F4];
@@ -449,6 +462,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     for (int i = 0; i < nstages; ++i) {
       const int s = i % p.stages;
       const bool ok = mbar_wait(&full[s], (uint32_t)(i / p.stages) & 1u, &s_abort);
+      if (tid == 0 && i == 0) tl_mark(p.tl, cta_lin, 3);
       const int nr_stage = min(kStageRows, ring_rows - i * kStageRows);
       const int nr = min(kWR, nr_stage - warp * kWR);
       if (ok && nr > 0) {
@@ -461,7 +475,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     if (has_new && warp == 0) consume_rows<D, GQM, QREG>(kv_new, kv_new + D, 1, gq, p.scale, qreg, q_s, p_w, st, lane);
 
     // ---- the warps' (max, sum, weighted V) into the region that was the ring ----
-    consumer_barrier();  // every warp is done with the ring
+    consumer_barrier();
+    if (tid == 0) tl_mark(p.tl, cta_lin, 4);  // every warp is done with the ring
     float* w_acc = region;
 #pragma unroll
     for (int g = 0; g < GQM; ++g) {
@@ -526,9 +541,11 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     s_last = (ticket == (int)gridDim.x - 1);
   }
   consumer_barrier();
+  if (tid == 0 && !s_last) tl_mark(p.tl, cta_lin, 5);
   if (!s_last) return;
   __threadfence();
   if (tid == 0) p.counters[b * p.num_kv_heads + kvh] = 0;  // ready for the next launch
+  if (tid == 0) tl_mark(p.tl, cta_lin, 6);
 
   const int h0 = kvh * gq;
   if (nvalid == 0) {
@@ -580,6 +597,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
     const int n = min(cc, nvalid - c0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     consumer_barrier();  // the tile and (first time) the weights are in shared memory
+    if (tid == 0) tl_mark(p.tl, cta_lin, 7);
 #pragma unroll
     for (int k = 0; k < OPT; ++k) {
       const int o = tid + k * kCT;
@@ -612,6 +630,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
           make_float4(acc[k].x * r, acc[k].y * r, acc[k].z * r, acc[k].w * r);
     }
   }
+  if (tid == 0) tl_mark(p.tl, cta_lin, 5);
 }
 
 int g_chunk_override = 0;
@@ -636,10 +655,13 @@ AttnLayout attn_layout(int batch, int num_heads, int num_kv_heads, int head_dim,
   const int64_t cap = max_seq_len < kSeqCap ? max_seq_len : kSeqCap;
   const int64_t cols = (int64_t)batch * num_kv_heads;
   // Ring depth: 96 KB of stages for head_dim 128 (two CTAs per SM), fewer bytes for narrower heads.
-  const int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : 2;
+  static const int e_cps = getenv("TB_ATTN_CPS") ? atoi(getenv("TB_ATTN_CPS")) : 0;
+  static const int e_stages = getenv("TB_ATTN_STAGES") ? atoi(getenv("TB_ATTN_STAGES")) : 0;
+  const int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (e_cps > 0 ? e_cps : 2);
   L.stages = head_dim == 128 ? 3 : (head_dim == 64 ? 4 : 6);
   if (cps == 1) L.stages *= 2;
   if (g_ring_stages > 0) L.stages = g_ring_stages;
+  else if (e_stages > 0) L.stages = e_stages;
   if (L.stages > kMaxStages) L.stages = kMaxStages;
   if (g_chunk_override > 0) {
     L.fixed_per = g_chunk_override;
@@ -749,6 +771,7 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.per_call_tables = a.per_call_tables ? 1 : 0;
   p.scale = 1.0f / sqrtf((float)a.head_dim);
   p.prefetch = a.prefetch;
+  p.tl = timeline_next_block();
 
   const size_t smem = sizeof(float) * (attn_fixed_floats(D, gq, gqm) + region);
   if (smem > 200 * 1024) return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: attention needs %zu bytes of shared memory", smem);

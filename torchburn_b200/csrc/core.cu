@@ -9,6 +9,22 @@
 namespace tb {
 
 namespace {
+unsigned long long* g_tl_base = nullptr;
+int64_t g_tl_blocks = 0, g_tl_next = 0;
+}  // namespace
+void timeline_register(void* device_buffer, int64_t bytes) {
+  g_tl_base = static_cast<unsigned long long*>(device_buffer);
+  g_tl_blocks = device_buffer ? bytes / (int64_t)(kTlBlock * sizeof(unsigned long long)) : 0;
+  g_tl_next = 0;
+}
+unsigned long long* timeline_next_block() {
+  if (!g_tl_base || g_tl_next >= g_tl_blocks) return nullptr;
+  return g_tl_base + (g_tl_next++) * kTlBlock;
+}
+int timeline_blocks_used() { return (int)g_tl_next; }
+
+
+namespace {
 thread_local char g_err[512] = "";
 }
 
@@ -218,6 +234,9 @@ void tb_set_gemv_tuning(int32_t xmode, int32_t rows_per_warp, int32_t warps) { s
 void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb, int32_t epl, int32_t groups) {
   set_stream_tuning(enabled, ctas_per_sm, ring_kb, epl, groups);
 }
+
+void tb_debug_timeline(void* device_buffer, int64_t bytes) { timeline_register(device_buffer, bytes); }
+int32_t tb_debug_timeline_blocks(void) { return timeline_blocks_used(); }
 
 int32_t tb_device_fault_flag(void) {
   const int a = stream_fault_flag(), b = attention_fault_flag();

@@ -62,6 +62,10 @@ struct tb_decoder {
   float *cos_t = nullptr, *sin_t = nullptr;
   float *k_cache = nullptr, *v_cache = nullptr;  // [L][B][Hkv_l][S][d]
   float *x = nullptr, *qkv = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr;
+  // Split RMSNorm (batch 1, one GPU): the residual-stream producers also write x times the next
+  // norm's weights and the sums of squares of x per 8 elements; the consumers start from those.
+  float *xn = nullptr, *ss8 = nullptr;
+  bool split_norm = false;
   float* partial = nullptr;  // tensor parallel: this rank's partial sums [B, H]
   float* logits_l = nullptr; // tensor parallel: this rank's logit slice [B, V_l]
   int32_t *d_tokens = nullptr, *d_offsets = nullptr, *d_eff = nullptr;
@@ -145,6 +149,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
   };
   TB_TRY(snap(d->dbg_embed, d->x, d->H));
   // L2 prefetch chain (see PrefetchList): each kernel requests what the kernels after it read.
+  const bool sn = d->split_norm && b == 1 && !debug;
   const bool pfc = d->prefetch_chain && !debug;
   const size_t wq = (size_t)(d->H / 2), sq = sizeof(float) * (size_t)(d->H / d->G);
   auto add_mat = [&](PrefetchList& pf, const uint8_t* w, const float* sc, int64_t n, int64_t k) {
@@ -167,6 +172,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x = d->x; a.w = W.qkv_w; a.scales = W.qkv_s; a.bias = W.qkv_b; a.out = d->qkv;
       a.norm_w = W.input_norm_w; a.eps = d->cfg.rms_norm_eps;
       a.x_normed_out = dbg ? d->dbg_normed : nullptr;
+      if (sn && l > 0) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
       a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 1);
       if (l == 0) add_kv(a.prefetch, 0);  // later layers: requested by the previous layer's gate/up
       a.xq_scratch = d->xq_scratch;
@@ -198,6 +204,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       add_mat(a.prefetch, W.down_w, W.down_s, d->H, d->I_l);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
+      if (sn) { a.out_scaled = d->xn; a.out_scale_w = W.post_norm_w; a.out_ss8 = d->ss8; }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
@@ -208,6 +215,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       GemvArgs a;
       a.x = d->x; a.w = W.gate_w; a.scales = W.gate_s; a.w2 = W.up_w; a.scales2 = W.up_s; a.out = d->h;
       a.norm_w = W.post_norm_w; a.eps = d->cfg.rms_norm_eps;
+      if (sn) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
       a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 8);
       if (l + 1 < d->L) {
         add_mat(a.prefetch, d->layers[l + 1].qkv_w, d->layers[l + 1].qkv_s, d->tq_l, d->H);
@@ -228,6 +236,10 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.pdl = pdl && !debug && (pm & 16);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
+      if (sn) {
+        a.out_scaled = d->xn; a.out_ss8 = d->ss8;
+        a.out_scale_w = l + 1 < d->L ? d->layers[l + 1].input_norm_w : d->final_norm_w;
+      }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
@@ -240,6 +252,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     GemvArgs a;
     a.x = d->x; a.w = d->lm_w; a.scales = d->lm_s;
     a.norm_w = d->final_norm_w; a.eps = d->cfg.rms_norm_eps;
+    if (sn) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
     a.m = b; a.n = d->V_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 32);
     a.out = d->tp == 1 ? d->logits : d->logits_l;
     a.xq_scratch = d->xq_scratch;
@@ -372,6 +385,12 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   d->pdl = !(c.flags & TB_DECODER_NO_PDL);
   if (const char* pmv = getenv("TB_PDL_MASK")) d->pdl_mask = atoi(pmv);
   if (const char* pfv = getenv("TB_L2_PREFETCH")) d->prefetch_chain = atoi(pfv) != 0;
+  {
+    // Split RMSNorm needs the persistent M = 1 kernel for every projection of a layer.
+    auto ok_k = [&](int64_t k) { return k % 32 == 0 && k >= 2048 && k <= 15360 && ((k / d->G) * 4) % 16 == 0; };
+    d->split_norm = tp == 1 && ok_k(d->H) && ok_k(d->q_dim_l) && ok_k(d->I_l);
+    if (const char* snv = getenv("TB_SPLIT_NORM")) d->split_norm = d->split_norm && atoi(snv) != 0;
+  }
   cudaGetDevice(&d->device);
 
   tb_status s = TB_OK;
@@ -430,6 +449,8 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   CRC(cudaMemset(d->k_cache, 0, kv_elems * sizeof(float)));
   CRC(cudaMemset(d->v_cache, 0, kv_elems * sizeof(float)));
   CR(dalloc(&d->x, (size_t)B * H));
+  CR(dalloc(&d->xn, (size_t)H));
+  CR(dalloc(&d->ss8, (size_t)(H / 8 + 4)));
   CR(dalloc(&d->qkv, (size_t)B * d->tq_l));
   CR(dalloc(&d->attn, (size_t)B * d->q_dim_l));
   CR(dalloc(&d->h, (size_t)B * d->I_l));
@@ -496,6 +517,7 @@ void tb_decoder_destroy(tb_decoder* d) {
     cudaFree(o.down_w); cudaFree(o.down_s); cudaFree(o.qkv_b);
   }
   cudaFree(d->cos_t); cudaFree(d->sin_t); cudaFree(d->k_cache); cudaFree(d->v_cache);
+  cudaFree(d->xn); cudaFree(d->ss8);
   cudaFree(d->x); cudaFree(d->qkv); cudaFree(d->attn); cudaFree(d->h); cudaFree(d->logits);
   cudaFree(d->partial); cudaFree(d->logits_l);
   cudaFree(d->d_tokens); cudaFree(d->d_offsets); cudaFree(d->d_eff); cudaFree(d->d_hist); cudaFree(d->d_hist_pos);

@@ -72,6 +72,32 @@ __device__ __forceinline__ void prefetch_l2_slice(const PrefetchList& pf, int ct
 }
 #endif
 
+// ---- per-CTA timestamps of the hot kernels (off unless a buffer was registered) -------------
+// The role of the reference's timestamp queries (src/wgpu/profiler.rs).  Every launch of an
+// instrumented kernel gets the next block of kTlBlock 64-bit words of the registered device
+// buffer: words 0-7 = {kind, grid size, 0...}, then 8 event slots for each of the first
+// kTlCtas CTAs, holding %globaltimer values in ns.
+constexpr int kTlCtas = 512;
+constexpr int kTlBlock = (1 + kTlCtas) * 8;
+unsigned long long* timeline_next_block();   // null when no buffer is registered or it is full
+void timeline_register(void* device_buffer, int64_t bytes);
+int timeline_blocks_used();
+#ifdef __CUDACC__
+__device__ __forceinline__ void tl_mark(unsigned long long* tl, int cta, int ev) {
+  if (tl != nullptr && cta < kTlCtas) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    tl[(1 + cta) * 8 + ev] = t;
+  }
+}
+__device__ __forceinline__ void tl_header(unsigned long long* tl, int kind, int grid) {
+  if (tl != nullptr) {
+    tl[0] = (unsigned long long)kind;
+    tl[1] = (unsigned long long)grid;
+  }
+}
+#endif
+
 // ---- argument blocks of the kernel launchers (all pointers DEVICE) ----------
 
 // One grouped-INT4 projection y = W x (+ epilogue).  See w4_gemv.cu.
@@ -88,6 +114,15 @@ struct GemvArgs {
   const float* resid = nullptr;    // out = resid + y when not null: [m, n]
   float* out = nullptr;            // [m, n]
   float* x_normed_out = nullptr;   // optional copy of the normalised x (debug): [m, k]
+  // Split RMSNorm (M = 1, persistent kernel only).  A producer launch may also write
+  // out_scaled = out * out_scale_w (the next norm's weights) and out_ss8[i] = sum of out^2 over
+  // rows 8i..8i+7.  A consumer launch whose x is such a pre-weighted vector passes x_ss8 (and eps,
+  // no norm_w): its row sums are divided by sqrt(sum(x_ss8)/k + eps).  This halves the bytes every
+  // CTA pulls from L2 before its first product and takes the norm's barrier off that path.
+  const float* x_ss8 = nullptr;
+  float* out_scaled = nullptr;
+  const float* out_scale_w = nullptr;
+  float* out_ss8 = nullptr;
   int m = 1;
   int64_t n = 0, k = 0;
   int g = 32;

@@ -471,6 +471,8 @@ tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
   const int k_pad = (int)((a.k + 1023) / 1024 * 1024);
 
   if (w4_stream_supported(a)) return launch_w4_stream(a, stream);
+  if (a.x_ss8 || a.out_scaled || a.out_ss8)
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: the split RMSNorm needs the persistent M = 1 kernel for this shape");
   if (a.m >= 2 && g_mma_enabled && ((a.k / 2) % 16) == 0) {
     if (a.xq_scratch) return launch_w4_mma(a, a.xq_scratch, stream);
     void* tmp = nullptr;

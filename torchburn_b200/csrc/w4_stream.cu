@@ -39,6 +39,11 @@ struct StreamParams {
   const float* resid;
   float* out;
   float* x_normed_out;
+  const float* x_ss8;        // not null: x is already multiplied by the norm weights, x_ss8[i] = sum of squares of
+                             // the un-weighted elements 8i..8i+7; the row sums are divided by the rms at the end
+  float* out_scaled;         // optional second output out * out_scale_w (the next kernel's pre-weighted x)
+  const float* out_scale_w;
+  float* out_ss8;            // optional: sums of squares of out over groups of 8 rows
   float eps;
   int n, k, nb32, gshift, ng;
   int nwarps;        // consumer warps per group = ceil(k / EPL / 32)
@@ -47,6 +52,9 @@ struct StreamParams {
   int stage_bytes;   // bytes of one stage
   int rounds;        // ceil(n / 8): the unit of work distribution (8 rows)
   PrefetchList prefetch;
+  unsigned long long* tl;  // timestamps of this launch or null
+  int x_copies;      // x is stored this many times, k floats apart; CTA c reads copy c % x_copies
+  int hold;          // stages the producer may request before the activations have arrived (-1: no limit)
   int trigger;       // where launch_dependents is signalled: 0 start, 1 after the last stage was requested, 2 end
 };
 
@@ -147,6 +155,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   __shared__ float s_ss[16];
   __shared__ int s_abort;
   __shared__ int s_waited;
+  __shared__ int s_xready;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nwarps = p.nwarps, groups = p.groups;
@@ -161,11 +170,14 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   if (tid == 0) {
     s_abort = 0;
     s_waited = 0;
+    s_xready = 0;
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], nwarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tl_mark(p.tl, (int)blockIdx.x, 0);
+    if (blockIdx.x == 0) tl_header(p.tl, 1, (int)gridDim.x);
   }
   __syncthreads();
 
@@ -176,9 +188,17 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
     // this kernel has completed (kernels further down the chain rely on that).
     if (lane == 1) prefetch_l2_slice(p.prefetch, (int)blockIdx.x, (int)gridDim.x);
     if (lane == 0) {
+      if (p.trigger == 3) asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int i = 0; i < total_stages; ++i) {
         const int s = i % p.stages, round = i / p.stages;
         if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
+        if (i == p.hold) {
+          // keep the path to L2 clear until the consumers' loads of x have come back
+          const long long t0 = clock64();
+          while (*reinterpret_cast<volatile int*>(&s_xready) == 0 && clock64() - t0 < kWaitCycles) {}
+        }
+        if (i == 0 && p.hold != -2) tl_mark(p.tl, (int)blockIdx.x, 6);
+        if (i == total_stages - 1) tl_mark(p.tl, (int)blockIdx.x, 7);
         const int row0 = (round0 + i / SPR) * TR + (i % SPR) * RS;
         const int cnt = max(0, min(RS, p.n - row0));
         unsigned char* dst = ring + (size_t)s * p.stage_bytes;
@@ -212,6 +232,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (p.trigger == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) *reinterpret_cast<volatile int*>(&s_waited) = 1;
+  if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 1);
 
   const int grp = warp / nwarps, gw = warp - grp * nwarps;
   const int part = gw * 32 + lane;                 // index of this lane's EPL-element slice of K
@@ -223,8 +244,15 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   float inv_rms = 1.f;
   {
     float v[EPL];
+    // The norm weights travel together with x: one trip to L2 instead of two in a row.
+    float4 nwv[NORM ? EPL / 4 : 1];
+    if (NORM && has_part) {
+      const float4* nw = reinterpret_cast<const float4*>(p.norm_w) + part * (EPL / 4);
+#pragma unroll
+      for (int j = 0; j < EPL / 4; ++j) nwv[j] = __ldg(nw + j);
+    }
     if (has_part) {
-      const float4* xg = reinterpret_cast<const float4*>(p.x) + part * (EPL / 4);
+      const float4* xg = reinterpret_cast<const float4*>(p.x + (size_t)(blockIdx.x % p.x_copies) * p.k) + part * (EPL / 4);
 #pragma unroll
       for (int j = 0; j < EPL / 4; ++j) {
         const float4 t = xg[j];
@@ -248,10 +276,9 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
       for (int w = 0; w < nwarps; ++w) tot += s_ss[grp * nwarps + w];
       inv_rms = 1.0f / sqrtf(tot / (float)p.k + p.eps);
       if (has_part) {
-        const float4* nw = reinterpret_cast<const float4*>(p.norm_w) + part * (EPL / 4);
 #pragma unroll
         for (int j = 0; j < EPL / 4; ++j) {
-          const float4 t = nw[j];
+          const float4 t = nwv[j];
           if (p.x_normed_out != nullptr && blockIdx.x == 0 && grp == 0)
             reinterpret_cast<float4*>(p.x_normed_out)[part * (EPL / 4) + j] =
                 make_float4((v[4 * j] * inv_rms) * t.x, (v[4 * j + 1] * inv_rms) * t.y,
@@ -261,21 +288,52 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
       }
     }
     float amax = abs_max<EPL>(v);
+    if (p.hold == -2 && tid == 0 && amax >= 0.f) tl_mark(p.tl, (int)blockIdx.x, 6);
     if (EPL == 16) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // the block's other half
     quantize_part<EPL>(v, amax, dig, sx, corr);
     if (!has_part) { sx = 0.f; corr = 0.f; }
   }
 
+  if (!NORM && p.x_ss8 != nullptr && gw == 0) {
+    // RMSNorm with pre-weighted x: only the warp that writes the results needs 1/rms, and only
+    // at the end, so these loads stay off the path to the first product.  Fixed summation
+    // order (lane-sequential, then a butterfly): every CTA computes the same value.
+    float ss = 0.f;
+    const int n8 = p.k >> 3;
+    for (int i = lane * 4; i < n8; i += 128) {
+      const float4 t = *reinterpret_cast<const float4*>(p.x_ss8 + i);
+      ss += (t.x + t.y) + (t.z + t.w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    inv_rms = 1.0f / sqrtf(ss / (float)p.k + p.eps);
+  }
+  if (tid == 0) *reinterpret_cast<volatile int*>(&s_xready) = 1;
+  if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 2);
   const int sidx = blk >> p.gshift;
   int buf = 0;
 #pragma unroll 1
   for (int rd = 0; rd < my_rounds; ++rd) {
     float pa[NW][TR];
+    // The round that ends with an epilogue: its per-row operands (bias, residual, next norm's
+    // weight) are requested now, so that they have arrived when the row sums are complete.
+    float pre_b0 = 0.f, pre_b1 = 0.f, pre_res = 0.f, pre_sw = 0.f;
+    if (gw == 0 && ((rd & 3) == 3 || rd == my_rounds - 1)) {
+      const int row = (round0 + (rd & ~3)) * TR + lane;
+      if (lane < ((rd & 3) + 1) * TR && row < p.n) {
+        if (p.bias[0]) pre_b0 = p.bias[0][row];
+        if (EPI == 1 && p.bias[1]) pre_b1 = p.bias[1][row];
+        if (EPI == 0 && p.resid) pre_res = p.resid[row];
+        if (p.out_scaled != nullptr) pre_sw = p.out_scale_w[row];
+      }
+    }
 #pragma unroll
     for (int ss = 0; ss < SPR; ++ss) {
       const int it = rd * SPR + ss;
       const int s = it % p.stages;
       const bool ok = mbar_wait(&full[s], (uint32_t)(it / p.stages) & 1u, &s_abort);
+      if (tid == 0 && it == 0) tl_mark(p.tl, (int)blockIdx.x, 3);
+      if (tid == 0 && it == my_rounds * SPR - 1) tl_mark(p.tl, (int)blockIdx.x, 4);
       const unsigned char* st = ring + (size_t)s * p.stage_bytes;
 #pragma unroll
       for (int q = 0; q < NW; ++q) {
@@ -312,6 +370,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
     if (slot != 3 && rd != my_rounds - 1) continue;
     // ---- up to 32 rows gathered: sum over the warps, epilogue, one coalesced store ----
     asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(group_threads) : "memory");
+    float v_out = 0.f;  // this lane's finished row (0 when it has none): input of the sums of squares
     if (gw == 0 && lane < (slot + 1) * TR) {
       const int row = (round0 + (rd & ~3)) * TR + lane;
       float acc[NW];
@@ -324,19 +383,30 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
       if (row < p.n) {
         float v;
         if (EPI == 1) {
-          const float g = acc[0] + (p.bias[0] ? p.bias[0][row] : 0.f);
-          const float u = acc[NW - 1] + (p.bias[1] ? p.bias[1][row] : 0.f);
+          const float g = acc[0] + pre_b0;
+          const float u = acc[NW - 1] + pre_b1;
           v = (g / (1.0f + expf(-g))) * u;  // src/llm/decoder.rs:1319-1322
         } else {
-          v = acc[0] + (p.bias[0] ? p.bias[0][row] : 0.f);
-          if (p.resid) v = p.resid[row] + v;
+          v = acc[0] + pre_b0;
+          if (p.resid) v = pre_res + v;
         }
         p.out[row] = v;
+        if (p.out_scaled != nullptr) p.out_scaled[row] = v * pre_sw;
+        v_out = v;
       }
+    }
+    if (p.out_ss8 != nullptr && gw == 0) {
+      float sq = v_out * v_out;
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      const int row = (round0 + (rd & ~3)) * TR + lane;
+      if ((lane & 7) == 0 && lane < (slot + 1) * TR && row < p.n) p.out_ss8[row >> 3] = sq;
     }
     buf ^= 1;
   }
-  if (p.trigger == 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 5);
+  if (p.trigger >= 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (s_abort && tid == 0) atomicExch(&g_stream_fault, 1);
 }
 
@@ -416,21 +486,34 @@ bool w4_stream_supported(const GemvArgs& a) {
   if (!al16(a.w) || !al16(a.scales) || !al16(a.x)) return false;
   if (a.w2 && (!al16(a.w2) || !al16(a.scales2))) return false;
   if (a.norm_w && !al16(a.norm_w)) return false;
+  if (a.x_ss8 && (a.norm_w || !al16(a.x_ss8) || a.k % 32 != 0)) return false;
+  if ((a.out_scaled != nullptr) != (a.out_scale_w != nullptr)) return false;
   return true;
 }
 
+static int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+
 tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
+  static const int e_trigger = env_int("TB_STREAM_TRIGGER", 1), e_cps = env_int("TB_STREAM_CPS", 0),
+                   e_ring = env_int("TB_STREAM_RING_KB", 0), e_epl = env_int("TB_STREAM_EPL", 0), e_hold = env_int("TB_STREAM_HOLD", -1), e_xc = env_int("TB_STREAM_XCOPIES", 1);
   StreamParams p;
   p.x = a.x;
   p.w[0] = a.w; p.w[1] = a.w2;
   p.scales[0] = a.scales; p.scales[1] = a.scales2;
   p.bias[0] = a.bias; p.bias[1] = a.bias2;
   p.norm_w = a.norm_w; p.resid = a.resid; p.out = a.out; p.x_normed_out = a.x_normed_out;
+  p.x_ss8 = a.x_ss8; p.out_scaled = a.out_scaled; p.out_scale_w = a.out_scale_w; p.out_ss8 = a.out_ss8;
   p.eps = a.eps;
   p.prefetch = a.prefetch;
+  p.tl = timeline_next_block();
   // Dependents may start once this CTA's last HBM request is out (measured: start, that point and
   // the end of the kernel differ by < 1% on the decode step; the early start helps small kernels).
-  p.trigger = 1;
+  p.trigger = e_trigger;
+  p.hold = e_hold;
+  p.x_copies = e_xc > 0 ? e_xc : 1;
   p.n = (int)a.n; p.k = (int)a.k; p.nb32 = (int)(a.k / 32);
   p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
   p.ng = (int)(a.k / a.g);
@@ -438,12 +521,13 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   // K split: half a block per lane in the latency regime (few tiles per CTA: more lanes work
   // on each row), a whole block per lane in the throughput regime (fewer instructions per
   // element); wide K runs one CTA per SM with twice the ring.
-  int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (p.k >= 8192 ? 1 : 3);
+  int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (e_cps > 0 ? e_cps : (p.k >= 8192 ? 1 : 3));
   int grid = sm_count() * cps;
   if (grid > p.rounds) grid = p.rounds;
   const int rounds_per_cta = (p.rounds + grid - 1) / grid;
   int epl = (rounds_per_cta <= 4 && p.nb32 * 2 <= 14 * 32) ? 16 : 32;
   if (g_force_epl == 16 || g_force_epl == 32) epl = g_force_epl;
+  else if (e_epl == 16 || e_epl == 32) epl = e_epl;
   p.nwarps = (p.k / epl + 31) / 32;
   if (p.nwarps > 15) { epl = 32; p.nwarps = (p.nb32 + 31) / 32; }
   // One consumer group: every consumer warp observes every stage of the ring in order,
@@ -452,7 +536,7 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   const int nw = a.w2 ? 2 : 1;
   const int per_row = nw * (p.k / 2 + p.ng * 4);
   // Stage: at most ~20 KB; ring: as many stages as fit the budget (2..8).
-  const int ring_budget = g_ring_kb > 0 ? g_ring_kb * 1024 : (cps >= 3 ? 40 * 1024 : kRingBytesMax / cps);
+  const int ring_budget = g_ring_kb > 0 ? g_ring_kb * 1024 : (e_ring > 0 ? e_ring * 1024 : (cps >= 3 ? 40 * 1024 : kRingBytesMax / cps));
   int rs = 8;
   while (rs > 1 && (rs * per_row > 20 * 1024 || rs * per_row * 3 > ring_budget)) rs >>= 1;
   p.stage_bytes = rs * per_row;
