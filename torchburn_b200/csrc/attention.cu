@@ -34,6 +34,7 @@ constexpr int kWR = kStageRows / kCW;  // rows of a stage that one consumer warp
 constexpr int kRG = kWR / 4;           // groups of 4 rows per warp and stage (2)
 constexpr int kMaxGq = 8;              // q heads per kv head
 constexpr int kMaxStages = 8;
+constexpr int kChunkRows = 512;        // positions whose scores are held in shared memory at a time
 constexpr int kSeqCap = 32768;         // src/llm/decoder.rs:1180
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: a wait that long means a lost copy
 
@@ -55,6 +56,7 @@ struct AttnParams {
   int fixed_per;    // positions per CTA when forced, else 0: divide the current length evenly
   int nc;           // CTAs per (sequence, kv head) = gridDim.x
   int stages;       // ring depth
+  int pre_stages;   // stages requested before the consumers have asked for q (the rest follows their request)
   int region_floats;  // floats of the ring region (also holds the combine / merge buffers)
   int64_t max_seq_len;
   int per_call_tables;
@@ -123,16 +125,16 @@ __device__ __forceinline__ float rope_elem(const float* x, const float* c, const
   return __fadd_rn(__fmul_rn(x[i], c[i]), __fmul_rn(x[i - half], s[i]));
 }
 
-// Shared memory (floats): q_s [gq][D] | kv_new [2][D] | p_s [kCW][kWR + 1][GQM] | w_ml [kCW][gq][2]
-// | region.  The region is the ring (stages * 2 * 32 * D) while rows stream in; afterwards it
-// holds w_acc [kCW][gq][D] for the combine and, in the CTA that merges, wts [gq][nc] | ml [gq] |
-// a tile of partials.  Every part starts on a 16-byte boundary (float4 accesses).
+// Shared memory (floats): q_s [gq][D] | kv_new [2][D] | S [kChunkRows + 1][GQM] | region.  The
+// region is the ring (stages * 32 * D) while rows stream in; afterwards it holds w_acc
+// [kCW][gq][D] for the combine and, in the CTA that merges, wts [gq][nc] | ml [gq] | a tile of
+// partials.  Every part starts on a 16-byte boundary (float4 accesses).
 __host__ __device__ inline size_t up4(size_t v) { return (v + 3) & ~(size_t)3; }
 __host__ __device__ inline size_t attn_fixed_floats(int D, int gq, int gqm) {
-  return up4((size_t)gq * D) + 2 * (size_t)D + up4((size_t)kCW * (kWR + 1) * gqm) + up4((size_t)kCW * gq * 2);
+  return up4((size_t)gq * D) + 2 * (size_t)D + up4((size_t)(kChunkRows + 1) * gqm);
 }
 inline size_t attn_region_floats(int D, int gq, int nc, int stages) {
-  const size_t ring = (size_t)stages * 2 * kStageRows * D;
+  const size_t ring = (size_t)stages * kStageRows * D;
   const size_t comb = (size_t)kCW * gq * D;
   const size_t merge = up4((size_t)gq * nc) + up4(gq) + (size_t)gq * D;
   size_t r = ring > comb ? ring : comb;
@@ -180,32 +182,21 @@ __device__ __forceinline__ void spread_reduce8(float (&v)[V], int l8) {
   }
 }
 
-// Per-warp softmax state.  After spread_reduce8 a lane owns NV (row, q head) scores of the
-// warp's 8 rows; it keeps the running max and sum of its q heads (all lanes that own the same
-// head hold the same values) and a float4 column of the weighted V for every head.
-template <int D, int GQM>
-struct WarpState {
-  static constexpr int V = kRG * GQM;
-  static constexpr int NV = V >= 8 ? V / 8 : 1;
-  float m_run[NV], l_run[NV];
-  float4 acc[GQM];
-};
-
-// One consumer warp takes `nr` (1..8) rows that lie in shared memory: K rows at kb, V rows at vb.
+// Scores of up to 8 rows (K rows in shared memory at kb) against the q heads of this kv head.
+// Lanes work 8 to a row (4 rows at a time, two such groups); spread_reduce8 leaves every
+// (row, head) sum in one lane, which scales it, stores it at S[(srow0 + row) * GQM + head] and
+// folds it into its running maximum lmax.
 template <int D, int GQM, bool QREG>
-__device__ __forceinline__ void consume_rows(const float* __restrict__ kb, const float* __restrict__ vb, int nr,
-                                             int gq, float scale, const float4 (&qreg)[QREG ? GQM : 1][D / 32],
-                                             const float* __restrict__ q_s, float* __restrict__ p_w,
-                                             WarpState<D, GQM>& st, int lane) {
-  constexpr int F4 = D / 32;   // float4 per lane and row in the score phase (8 lanes per row)
+__device__ __forceinline__ void score_rows(const float* __restrict__ kb, int nr, int srow0, int gq, float scale,
+                                           const float4 (&qreg)[QREG ? GQM : 1][D / 32],
+                                           const float* __restrict__ q_s, float* __restrict__ S,
+                                           float (&lmax)[kRG * GQM >= 8 ? kRG * GQM / 8 : 1], int lane) {
+  constexpr int F4 = D / 32;   // float4 per lane and row (8 lanes per row)
   constexpr int CPR = D / 4;   // float4 columns per row
-  constexpr int RPL = 32 / CPR;  // rows per warp-wide V load
   constexpr int V = kRG * GQM;
-  constexpr int NV = WarpState<D, GQM>::NV;
+  constexpr int NV = V >= 8 ? V / 8 : 1;
   constexpr int HSTEPS = V >= 8 ? 3 : (V == 4 ? 2 : (V == 2 ? 1 : 0));
   const int l8 = lane & 7, rsub = lane >> 3;
-
-  // ---- scores of 8 rows x GQM heads: partial dot products, then the spread reduction ----
   float v[V];
 #pragma unroll
   for (int rg = 0; rg < kRG; ++rg) {
@@ -231,56 +222,30 @@ __device__ __forceinline__ void consume_rows(const float* __restrict__ kb, const
     }
   }
   spread_reduce8<V>(v, l8);
-  // which (row group, head) this lane's value(s) belong to
   int idx0 = 0;
 #pragma unroll
   for (int t = 0; t < HSTEPS; ++t) idx0 += ((l8 >> t) & 1) * (V >> (t + 1));
-  const bool writer = l8 < V;  // for V < 8 the sums are replicated over the unused lane bits
-
-  bool need = false;
-  float e[NV], resc[NV];
-#pragma unroll
-  for (int j = 0; j < NV; ++j) {
-    const int idx = idx0 + j;
-    const int rg = idx / GQM;
-    const int row = rg * 4 + rsub;
-    const float s = row < nr ? v[j] * scale : -INFINITY;
-    // max over the 8 rows of the same head: the row lives in lane bits 3-4 and (two groups) bit 0
-    float mx = s;
-    if (kRG == 2) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-    const float m_new = fmaxf(st.m_run[j], mx);   // finite: row 0 is always valid
-    e[j] = expf(s - m_new);                        // 0 for rows past nr
-    float ps = e[j];
-    if (kRG == 2) ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-    ps += __shfl_xor_sync(0xffffffffu, ps, 8);
-    ps += __shfl_xor_sync(0xffffffffu, ps, 16);
-    resc[j] = expf(st.m_run[j] - m_new);           // exp(-inf) = 0 the first time
-    need |= m_new > st.m_run[j];
-    st.l_run[j] = st.l_run[j] * resc[j] + ps;
-    st.m_run[j] = m_new;
-  }
-  // weights (and, in row kWR, the rescale factors) to shared memory: p_w[row][g]
-  if (writer) {
+  if (l8 < V) {  // for V < 8 the sums are replicated over the unused lane bits: one copy writes
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int idx = idx0 + j;
       const int rg = idx / GQM, g = idx % GQM;
-      p_w[(rg * 4 + rsub) * GQM + g] = e[j];
-      if (rg == 0 && rsub == 0) p_w[kWR * GQM + g] = resc[j];
+      const int row = rg * 4 + rsub;
+      if (row < nr) {  // rows past nr are neither stored (S ends after the chunk) nor read
+        const float sc = v[j] * scale;
+        S[(srow0 + row) * GQM + g] = sc;
+        lmax[j] = fmaxf(lmax[j], sc);
+      }
     }
   }
-  const bool any_need = __any_sync(0xffffffffu, need);
-  __syncwarp();
-  if (any_need) {
-#pragma unroll
-    for (int g = 0; g < GQM; ++g) {
-      const float r = p_w[kWR * GQM + g];
-      st.acc[g].x *= r; st.acc[g].y *= r; st.acc[g].z *= r; st.acc[g].w *= r;
-    }
-  }
-  // ---- weighted V: one float4 column per lane ----
+}
+
+// acc[g] += sum over up to 8 rows of p[row][g] * V[row][:], one float4 column per lane.
+template <int D, int GQM>
+__device__ __forceinline__ void weigh_rows(const float* __restrict__ vb, int nr, int srow0,
+                                           const float* __restrict__ S, float4 (&acc)[GQM], int lane) {
+  constexpr int CPR = D / 4;
+  constexpr int RPL = 32 / CPR;  // rows per warp-wide V load
   const int vc4 = lane % CPR, vrs = lane / CPR;
 #pragma unroll
   for (int j = 0; j < kWR / RPL; ++j) {
@@ -291,47 +256,54 @@ __device__ __forceinline__ void consume_rows(const float* __restrict__ kb, const
       if (GQM >= 4) {
 #pragma unroll
         for (int q4 = 0; q4 < GQM / 4; ++q4) {
-          const float4 t = reinterpret_cast<const float4*>(p_w + r * GQM)[q4];
+          const float4 t = reinterpret_cast<const float4*>(S + (srow0 + r) * GQM)[q4];
           pg[q4 * 4 + 0] = t.x; pg[q4 * 4 + 1] = t.y; pg[q4 * 4 + 2] = t.z; pg[q4 * 4 + 3] = t.w;
         }
       } else {
 #pragma unroll
-        for (int g = 0; g < GQM; ++g) pg[g] = p_w[r * GQM + g];
+        for (int g = 0; g < GQM; ++g) pg[g] = S[(srow0 + r) * GQM + g];
       }
 #pragma unroll
       for (int g = 0; g < GQM; ++g) {
-        st.acc[g].x = fmaf(pg[g], vv.x, st.acc[g].x);
-        st.acc[g].y = fmaf(pg[g], vv.y, st.acc[g].y);
-        st.acc[g].z = fmaf(pg[g], vv.z, st.acc[g].z);
-        st.acc[g].w = fmaf(pg[g], vv.w, st.acc[g].w);
+        acc[g].x = fmaf(pg[g], vv.x, acc[g].x);
+        acc[g].y = fmaf(pg[g], vv.y, acc[g].y);
+        acc[g].z = fmaf(pg[g], vv.z, acc[g].z);
+        acc[g].w = fmaf(pg[g], vv.w, acc[g].w);
       }
     }
   }
-  __syncwarp();  // p_w is rewritten by the next call
 }
 
+// One CTA = one share of the positions of one (sequence, kv head).  The share is walked in
+// chunks of at most kChunkRows positions; for every chunk the producer lane streams the K
+// rows and then the V rows through the ring (32 rows per stage).  The consumer warps score the
+// K stages as they land (8 rows of a stage per warp) into S, the CTA then takes the exact
+// maximum and the exponentials of the chunk (a two-pass softmax inside the chunk; the running
+// max / sum / weighted V are rescaled only between chunks), and the V stages are weighted as
+// they land.  No softmax dependency sits inside either streaming loop.
 template <int D, int GQM>
-__global__ void __launch_bounds__(kThreads, kCW == 8 ? 2 : 1) attn_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
   constexpr int F4 = D / 32;
   constexpr int CPR = D / 4;
-  constexpr bool QREG = GQM * F4 <= 16;
+  constexpr bool QREG = GQM * F4 <= 16 && kCW == 4;
   constexpr int V = kRG * GQM;
-  constexpr int NV = WarpState<D, GQM>::NV;
+  constexpr int NV = V >= 8 ? V / 8 : 1;
   constexpr int HSTEPS = V >= 8 ? 3 : (V == 4 ? 2 : (V == 2 ? 1 : 0));
   static_assert(D == 32 || D == 64 || D == 128, "head_dim");
 
   extern __shared__ __align__(128) float smem[];
   __shared__ __align__(8) uint64_t full[kMaxStages];
   __shared__ __align__(8) uint64_t empty[kMaxStages];
+  __shared__ float s_wmax[kCW][kMaxGq], s_wsum[kCW][kMaxGq], s_ml[2][kMaxGq];
   __shared__ int s_abort;
   __shared__ int s_last;
+  __shared__ int s_qreq;
 
   const int gq = p.gq;
   float* q_s = smem;
   float* kv_new = q_s + up4((size_t)gq * D);
-  float* p_s = kv_new + 2 * D;
-  float* w_ml = p_s + up4((size_t)kCW * (kWR + 1) * GQM);
-  float* region = w_ml + up4((size_t)kCW * gq * 2);
+  float* S = kv_new + 2 * D;                             // [(kChunkRows + 1)][GQM]
+  float* region = S + up4((size_t)(kChunkRows + 1) * GQM);
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -339,6 +311,7 @@ __global__ void __launch_bounds__(kThreads, kCW == 8 ? 2 : 1) attn_decode_kernel
 
   if (tid == 0) {
     s_abort = 0;
+    s_qreq = 0;
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], kCW);
@@ -374,29 +347,42 @@ __global__ void __launch_bounds__(kThreads, kCW == 8 ? 2 : 1) attn_decode_kernel
   // row is the last one of its range; it is taken from shared memory, not from the cache.
   const bool has_new = active && off >= t0 && off < t0 + rows;
   const int ring_rows = rows - (has_new ? 1 : 0);
-  const int nstages = (ring_rows + kStageRows - 1) / kStageRows;
+  const int nchunks = active ? max(1, (ring_rows + kChunkRows - 1) / kChunkRows) : 0;
   float* kc = p.k_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
   float* vc = p.v_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
-  const int stage_floats = 2 * kStageRows * D;
+  const int stage_floats = kStageRows * D;
 
   if (warp == kCW) {
     // ---------------- producer: one lane feeds the ring ----------------
     if (lane == 1)
-      prefetch_l2_slice(p.prefetch, (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),
-                        (int)(gridDim.x * gridDim.y * gridDim.z));
+      prefetch_l2_slice(p.prefetch, cta_lin, (int)(gridDim.x * gridDim.y * gridDim.z));
     if (lane == 0) {
-      for (int i = 0; i < nstages; ++i) {
-        const int s = i % p.stages, round = i / p.stages;
-        if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
-        if (i == 0) tl_mark(p.tl, cta_lin, 6);
-        if (i == nstages - 1) tl_mark(p.tl, cta_lin, 7);
-        const int nr = min(kStageRows, ring_rows - i * kStageRows);
-        const uint32_t bytes = (uint32_t)nr * D * sizeof(float);
-        float* dst = region + (size_t)s * stage_floats;
-        mbar_expect_tx(&full[s], 2 * bytes);
-        bulk_g2s(dst, kc + (int64_t)(t0 + i * kStageRows) * D, bytes, &full[s]);
-        bulk_g2s(dst + kStageRows * D, vc + (int64_t)(t0 + i * kStageRows) * D, bytes, &full[s]);
+      int i = 0;
+      bool lost = false;
+      for (int c = 0; c < nchunks && !lost; ++c) {
+        const int cr0 = c * kChunkRows;
+        const int crn = min(kChunkRows, ring_rows - cr0);
+        const int nt = (crn + kStageRows - 1) / kStageRows;
+        for (int pass = 0; pass < 2 && !lost; ++pass) {
+          const float* src = (pass == 0 ? kc : vc) + (int64_t)(t0 + cr0) * D;
+          for (int t = 0; t < nt; ++t, ++i) {
+            const int s = i % p.stages, round = i / p.stages;
+            if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) { lost = true; break; }
+            if (i == 0) tl_mark(p.tl, cta_lin, 6);
+            if (i == p.pre_stages) {
+              // The consumers' small loads of q must not queue behind the whole K/V stream:
+              // only the first stages go out ahead of them, the rest follows their request.
+              const long long w0 = clock64();
+              while (*reinterpret_cast<volatile int*>(&s_qreq) < kCW && clock64() - w0 < kWaitCycles) {}
+            }
+            const int nr = min(kStageRows, crn - t * kStageRows);
+            const uint32_t bytes = (uint32_t)nr * D * sizeof(float);
+            mbar_expect_tx(&full[s], bytes);
+            bulk_g2s(region + (size_t)s * stage_floats, src + (int64_t)t * kStageRows * D, bytes, &full[s]);
+          }
+        }
       }
+      tl_mark(p.tl, cta_lin, 7);
     }
     return;
   }
@@ -409,14 +395,36 @@ __global__ void __launch_bounds__(kThreads, kCW == 8 ? 2 : 1) attn_decode_kernel
   if (active) {
     const float* cs = p.cos_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
     const float* sn = p.sin_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
-    // q heads of this kv head, rotated, into shared memory.
-    for (int i = tid; i < gq * D; i += kCT) {
-      const int g = i / D, e = i - g * D;
-      const float* xh = qkv_b + (int64_t)(kvh * gq + g) * D;
-      const float v = rope_elem(xh, cs, sn, e, D / 2);
-      q_s[g * D + e] = v;
-      if (p.qkv_rot_out && split == 0)
-        p.qkv_rot_out[(int64_t)b * qkv_dim + (int64_t)(kvh * gq + g) * D + e] = v;
+    // q heads of this kv head, rotated, into shared memory.  All loads are issued first; then the
+    // producer is told that it may go on (see pre_stages); then the arithmetic.
+    constexpr int QIT = kMaxGq * 128 / kCT;
+    float xa[QIT], xb[QIT], ca[QIT], sa[QIT];
+#pragma unroll
+    for (int k = 0; k < QIT; ++k) {
+      const int i = tid + k * kCT;
+      if (i < gq * D) {
+        const int g = i / D, e = i - g * D;
+        const float* xh = qkv_b + (int64_t)(kvh * gq + g) * D;
+        xa[k] = xh[e];
+        xb[k] = xh[e < D / 2 ? e + D / 2 : e - D / 2];
+        ca[k] = cs[e];
+        sa[k] = sn[e];
+      }
+    }
+    __syncwarp();
+    if (lane == 0) atomicAdd(&s_qreq, 1);
+#pragma unroll
+    for (int k = 0; k < QIT; ++k) {
+      const int i = tid + k * kCT;
+      if (i < gq * D) {
+        const int g = i / D, e = i - g * D;
+        // rotate-half with separately rounded products (rope_elem)
+        const float v = e < D / 2 ? __fsub_rn(__fmul_rn(xa[k], ca[k]), __fmul_rn(xb[k], sa[k]))
+                                  : __fadd_rn(__fmul_rn(xa[k], ca[k]), __fmul_rn(xb[k], sa[k]));
+        q_s[g * D + e] = v;
+        if (p.qkv_rot_out && split == 0)
+          p.qkv_rot_out[(int64_t)b * qkv_dim + (int64_t)(kvh * gq + g) * D + e] = v;
+      }
     }
     if (has_new) {
       const float* kx = qkv_b + (int64_t)p.num_heads * D + (int64_t)kvh * D;
@@ -448,86 +456,132 @@ __global__ void __launch_bounds__(kThreads, kCW == 8 ? 2 : 1) attn_decode_kernel
           qreg[QREG ? g : 0][i] = g < gq ? reinterpret_cast<const float4*>(q_s)[g * CPR + l8 + 8 * i]
                                          : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    WarpState<D, GQM> st;
+    int idx0 = 0;
 #pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      st.m_run[j] = -INFINITY;
-      st.l_run[j] = 0.f;
+    for (int t = 0; t < HSTEPS; ++t) idx0 += ((l8 >> t) & 1) * (V >> (t + 1));
+    float m_run[GQM], l_run[GQM];
+    float4 acc[GQM];
+#pragma unroll
+    for (int g = 0; g < GQM; ++g) {
+      m_run[g] = -INFINITY;
+      l_run[g] = 0.f;
+      acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-#pragma unroll
-    for (int g = 0; g < GQM; ++g) st.acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float* p_w = p_s + (size_t)warp * (kWR + 1) * GQM;
+    const int g_t = tid % GQM;  // the head whose exponentials this thread takes in the softmax pass
 
+    int it = 0;  // stages consumed so far (same order as the producer's)
 #pragma unroll 1
-    for (int i = 0; i < nstages; ++i) {
-      const int s = i % p.stages;
-      const bool ok = mbar_wait(&full[s], (uint32_t)(i / p.stages) & 1u, &s_abort);
-      if (tid == 0 && i == 0) tl_mark(p.tl, cta_lin, 3);
-      const int nr_stage = min(kStageRows, ring_rows - i * kStageRows);
-      const int nr = min(kWR, nr_stage - warp * kWR);
-      if (ok && nr > 0) {
-        const float* kb = region + (size_t)s * stage_floats + (size_t)warp * kWR * D;
-        consume_rows<D, GQM, QREG>(kb, kb + kStageRows * D, nr, gq, p.scale, qreg, q_s, p_w, st, lane);
+    for (int c = 0; c < nchunks; ++c) {
+      const int cr0 = c * kChunkRows;
+      const int crn = min(kChunkRows, ring_rows - cr0);
+      const int nt = (crn + kStageRows - 1) / kStageRows;
+      const bool new_here = has_new && c == nchunks - 1;
+      if (c > 0) consumer_barrier();  // the previous chunk's weights in S have been used
+      // ---- K stages: scores into S ----
+      float lmax[NV];
+#pragma unroll
+      for (int j = 0; j < NV; ++j) lmax[j] = -INFINITY;
+#pragma unroll 1
+      for (int t = 0; t < nt; ++t, ++it) {
+        const int s = it % p.stages;
+        const bool ok = mbar_wait(&full[s], (uint32_t)(it / p.stages) & 1u, &s_abort);
+        if (tid == 0 && it == 0) tl_mark(p.tl, cta_lin, 3);
+        const int nr = min(kWR, crn - t * kStageRows - warp * kWR);
+        if (ok && nr > 0)
+          score_rows<D, GQM, QREG>(region + (size_t)s * stage_floats + (size_t)warp * kWR * D, nr,
+                                   t * kStageRows + warp * kWR, gq, p.scale, qreg, q_s, S, lmax, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
+      if (new_here && warp == 0) score_rows<D, GQM, QREG>(kv_new, 1, crn, gq, p.scale, qreg, q_s, S, lmax, lane);
+      // the warp's maximum per head: the rows sit in lane bits 3-4 and (row group) bit 0
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        float mx = lmax[j];
+        if (kRG == 2) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const int idx = idx0 + j;
+        if (lane < 8 && l8 < V && idx / GQM == 0) s_wmax[warp][idx % GQM] = mx;
+      }
+      consumer_barrier();
+      // ---- exact softmax statistics of the chunk; S becomes the weights ----
+      float resc[GQM];
+      float m_t = 0.f;
+#pragma unroll
+      for (int g = 0; g < GQM; ++g) {
+        float mc = s_wmax[0][g];
+#pragma unroll
+        for (int w = 1; w < kCW; ++w) mc = fmaxf(mc, s_wmax[w][g]);
+        const float m_new = fmaxf(m_run[g], mc);      // finite for every real head: the chunk has a row
+        resc[g] = expf(m_run[g] - m_new);              // exp(-inf) = 0 for the first chunk
+        m_run[g] = m_new;
+        if (g == g_t) m_t = m_new;
+      }
+      const int n_s = (crn + (new_here ? 1 : 0)) * GQM;
+      float ls = 0.f;
+      for (int i = tid; i < n_s; i += kCT) {
+        const float e = expf(S[i] - m_t);
+        S[i] = e;
+        ls += e;
+      }
+#pragma unroll
+      for (int o = GQM; o < 32; o <<= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+      if (lane < GQM) s_wsum[warp][lane] = ls;
+      consumer_barrier();
+#pragma unroll
+      for (int g = 0; g < GQM; ++g) {
+        float t = s_wsum[0][g];
+#pragma unroll
+        for (int w = 1; w < kCW; ++w) t += s_wsum[w][g];
+        l_run[g] = l_run[g] * resc[g] + t;
+        if (c > 0) { acc[g].x *= resc[g]; acc[g].y *= resc[g]; acc[g].z *= resc[g]; acc[g].w *= resc[g]; }
+      }
+      // ---- V stages: weighted sum ----
+#pragma unroll 1
+      for (int t = 0; t < nt; ++t, ++it) {
+        const int s = it % p.stages;
+        const bool ok = mbar_wait(&full[s], (uint32_t)(it / p.stages) & 1u, &s_abort);
+        const int nr = min(kWR, crn - t * kStageRows - warp * kWR);
+        if (ok && nr > 0)
+          weigh_rows<D, GQM>(region + (size_t)s * stage_floats + (size_t)warp * kWR * D, nr,
+                             t * kStageRows + warp * kWR, S, acc, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      if (new_here && warp == 0) weigh_rows<D, GQM>(kv_new + D, 1, crn, S, acc, lane);
     }
-    if (has_new && warp == 0) consume_rows<D, GQM, QREG>(kv_new, kv_new + D, 1, gq, p.scale, qreg, q_s, p_w, st, lane);
 
-    // ---- the warps' (max, sum, weighted V) into the region that was the ring ----
-    consumer_barrier();
-    if (tid == 0) tl_mark(p.tl, cta_lin, 4);  // every warp is done with the ring
+    // ---- this CTA's partial: the warps' weighted V summed, with the share's max and sum ----
+    consumer_barrier();  // every warp is done with the ring
+    if (tid == 0) tl_mark(p.tl, cta_lin, 4);
     float* w_acc = region;
 #pragma unroll
     for (int g = 0; g < GQM; ++g) {
       if (g < gq) {
 #pragma unroll
         for (int o = CPR; o < 32; o <<= 1) {  // lanes that share a column (head_dim < 128)
-          st.acc[g].x += __shfl_xor_sync(0xffffffffu, st.acc[g].x, o);
-          st.acc[g].y += __shfl_xor_sync(0xffffffffu, st.acc[g].y, o);
-          st.acc[g].z += __shfl_xor_sync(0xffffffffu, st.acc[g].z, o);
-          st.acc[g].w += __shfl_xor_sync(0xffffffffu, st.acc[g].w, o);
+          acc[g].x += __shfl_xor_sync(0xffffffffu, acc[g].x, o);
+          acc[g].y += __shfl_xor_sync(0xffffffffu, acc[g].y, o);
+          acc[g].z += __shfl_xor_sync(0xffffffffu, acc[g].z, o);
+          acc[g].w += __shfl_xor_sync(0xffffffffu, acc[g].w, o);
         }
-        if (lane < CPR) reinterpret_cast<float4*>(w_acc + ((size_t)warp * gq + g) * D)[lane] = st.acc[g];
-      }
-    }
-    {
-      int idx0 = 0;
-#pragma unroll
-      for (int t = 0; t < HSTEPS; ++t) idx0 += ((l8 >> t) & 1) * (V >> (t + 1));
-      if (lane < 8 && l8 < V) {
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-          const int idx = idx0 + j;
-          const int rg = idx / GQM, g = idx % GQM;
-          if (rg == 0 && g < gq) {
-            w_ml[(warp * gq + g) * 2 + 0] = st.m_run[j];
-            w_ml[(warp * gq + g) * 2 + 1] = st.l_run[j];
-          }
-        }
+        if (lane < CPR) reinterpret_cast<float4*>(w_acc + ((size_t)warp * gq + g) * D)[lane] = acc[g];
+        if (tid == 0) { s_ml[0][g] = m_run[g]; s_ml[1][g] = l_run[g]; }
       }
     }
     consumer_barrier();
-    // ---- combine the warps: this CTA's partial ----
     for (int i = tid; i < gq * D; i += kCT) {
       const int g = i / D, e = i - g * D;
-      float mx = -INFINITY;
+      float o = 0.f;
 #pragma unroll
-      for (int w = 0; w < kCW; ++w) mx = fmaxf(mx, w_ml[(w * gq + g) * 2]);
-      float o = 0.f, l = 0.f;
-#pragma unroll
-      for (int w = 0; w < kCW; ++w) {
-        const float mw = w_ml[(w * gq + g) * 2];
-        const float f = mw == -INFINITY ? 0.f : expf(mw - mx);  // warps without rows contribute nothing
-        o = fmaf(w_acc[((size_t)w * gq + g) * D + e], f, o);
-        l = fmaf(w_ml[(w * gq + g) * 2 + 1], f, l);
-      }
+      for (int w = 0; w < kCW; ++w) o += w_acc[((size_t)w * gq + g) * D + e];
       const int h = kvh * gq + g;
       p.part_o[(((int64_t)b * p.num_heads + h) * p.nc + split) * D + e] = o;
       if (e == 0) {
         float* dst = p.part_ml + (((int64_t)b * p.num_heads + h) * p.nc + split) * 2;
-        dst[0] = mx;
-        dst[1] = l;
+        dst[0] = s_ml[0][g];
+        dst[1] = s_ml[1][g];
       }
     }
   }
@@ -570,16 +624,39 @@ __global__ void __launch_bounds__(kThreads, kCW == 8 ? 2 : 1) attn_decode_kernel
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  // The (max, sum) pairs are requested first - they gate the weights - then the tile.
+  float2 mlv[2][2];
+#pragma unroll
+  for (int hs = 0; hs < 2; ++hs)
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int g = warp + hs * kCW, c = lane + 32 * k;
+      mlv[hs][k] = (g < gq && c < nvalid)
+                       ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + (((int64_t)b * p.num_heads + h0 + g) * p.nc + c) * 2))
+                       : make_float2(-INFINITY, 0.f);
+    }
   request_tile(0, min(cc, nvalid));
   // weights of every partial: one warp per q head
-  for (int g = warp; g < gq; g += kCW) {
+#pragma unroll
+  for (int hs = 0; hs < 2; ++hs) {
+    const int g = warp + hs * kCW;
+    if (g >= gq) continue;
     const float* pml = p.part_ml + ((int64_t)b * p.num_heads + h0 + g) * p.nc * 2;
-    float mx = -INFINITY;
-    for (int c = lane; c < nvalid; c += 32) mx = fmaxf(mx, __ldcg(pml + c * 2));
+    float mx = fmaxf(mlv[hs][0].x, mlv[hs][1].x);
+    for (int c = lane + 64; c < nvalid; c += 32) mx = fmaxf(mx, __ldcg(pml + c * 2));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float tot = 0.f;
-    for (int c = lane; c < nvalid; c += 32) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int c = lane + 32 * k;
+      if (c < nvalid) {
+        const float w = expf(mlv[hs][k].x - mx);
+        wts[g * p.nc + c] = w;
+        tot = fmaf(mlv[hs][k].y, w, tot);
+      }
+    }
+    for (int c = lane + 64; c < nvalid; c += 32) {
       const float w = expf(__ldcg(pml + c * 2) - mx);
       wts[g * p.nc + c] = w;
       tot = fmaf(__ldcg(pml + c * 2 + 1), w, tot);
@@ -658,8 +735,8 @@ AttnLayout attn_layout(int batch, int num_heads, int num_kv_heads, int head_dim,
   static const int e_cps = getenv("TB_ATTN_CPS") ? atoi(getenv("TB_ATTN_CPS")) : 0;
   static const int e_stages = getenv("TB_ATTN_STAGES") ? atoi(getenv("TB_ATTN_STAGES")) : 0;
   const int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (e_cps > 0 ? e_cps : 2);
-  L.stages = head_dim == 128 ? 3 : (head_dim == 64 ? 4 : 6);
-  if (cps == 1) L.stages *= 2;
+  L.stages = head_dim == 128 ? 6 : 8;
+  if (cps == 1 && L.stages < 8) L.stages = 8;
   if (g_ring_stages > 0) L.stages = g_ring_stages;
   else if (e_stages > 0) L.stages = e_stages;
   if (L.stages > kMaxStages) L.stages = kMaxStages;
@@ -765,7 +842,14 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.qkv_rot_out = a.q_rot_out;
   p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.gq = gq;
   p.fixed_per = L.fixed_per; p.nc = L.nc; p.stages = L.stages;
-  const size_t region = attn_region_floats(D, gq, L.nc, L.stages);
+  static const int e_pre = getenv("TB_ATTN_PRE") ? atoi(getenv("TB_ATTN_PRE")) : 2;
+  p.pre_stages = e_pre;
+  // two CTAs per SM when the ring can be cut to make room (wide heads with many q heads per kv head)
+  int stages = L.stages;
+  while (stages > 3 && 2 * (sizeof(float) * (attn_fixed_floats(D, gq, gqm) + attn_region_floats(D, gq, L.nc, stages)) + 2048) > 227 * 1024)
+    --stages;
+  p.stages = stages;
+  const size_t region = attn_region_floats(D, gq, L.nc, stages);
   p.region_floats = (int)region;
   p.max_seq_len = a.max_seq_len;
   p.per_call_tables = a.per_call_tables ? 1 : 0;
