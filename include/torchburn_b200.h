@@ -363,6 +363,22 @@ tb_status tb_decoder_generate_loop(tb_decoder* dec, int64_t first_token, int64_t
                                    const int64_t* recent_seed, int64_t n_recent_seed,
                                    uint64_t* rng_state, int64_t* out_tokens, int64_t* n_out,
                                    int64_t* end_offset);
+/* speculative_accept, src/llm/decoder.rs:583-727.  _rows is the acceptance rule alone (host):
+ * target_logits [k, vocab] are the target model's logits at the k verified positions,
+ * draft_probs [k, vocab] the draft model's probabilities, draft_tokens [k] the proposals.
+ * Leviathan acceptance with probability min(1, p_target / p_draft); on the first rejection the
+ * bonus token is drawn from max(0, p_target - p_draft); when all are accepted it is drawn from
+ * the last row with the top-p cut.  *rng_state is a splitmix64 state owned by the caller (the
+ * reference seeds its own from the clock).  k = 0 gives (0, vocab - 1).  The decoder form first
+ * runs the k draft tokens at offset, offset+1, ... (the KV cache advances as in the reference). */
+tb_status tb_speculative_accept_rows(const float* target_logits, int64_t vocab,
+                                     const int64_t* draft_tokens, int64_t k,
+                                     const float* draft_probs, float temperature, float top_p,
+                                     uint64_t* rng_state, int64_t* accepted, int64_t* bonus);
+tb_status tb_decoder_speculative_accept(tb_decoder* dec, int64_t offset, const int64_t* draft_tokens,
+                                        int64_t k, const float* draft_probs, float temperature,
+                                        float top_p, uint64_t* rng_state, int64_t* accepted,
+                                        int64_t* bonus);
 /* Layer-0 intermediates of the last step by name, like debug_step_stages,
  * src/wgpu/profiler.rs:75: "embed", "normed", "qkv", "attn", "x_attn", "h",
  * "x_out".  Only recorded when the decoder was created with TB_DECODER_NO_GRAPH.

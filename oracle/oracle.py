@@ -93,6 +93,7 @@ def lib():
         L.tbo_decoder_debug_stage.argtypes = [p, C.c_char_p, C.POINTER(p)]
         L.tbo_decoder_debug_stage.restype = i64
         L.tbo_argmax.argtypes = [p, i64]; L.tbo_argmax.restype = i64
+        L.tbo_speculative_accept_rows.argtypes = [p, i64, p, i64, p, f32, f32, p, p]; L.tbo_speculative_accept_rows.restype = i64
         L.tbo_apply_repetition_penalty.argtypes = [p, i64, p, i64, f32]
         L.tbo_sample_logits.argtypes = [p, i64, f32, i64, f32, f32]; L.tbo_sample_logits.restype = i64
         _lib = L
@@ -247,6 +248,19 @@ def apply_repetition_penalty(logits, recent, penalty: float) -> np.ndarray:
 def sample_logits(logits, temperature: float, top_k: int, top_p: float, u: float) -> int:
     l = _f32(logits)
     return int(lib().tbo_sample_logits(_ptr(l), l.size, temperature, top_k, top_p, u))
+
+
+def speculative_accept_rows(target_logits, draft_tokens, draft_probs, temperature: float, top_p: float, seed: int):
+    """Returns (accepted, bonus, new_rng_state)."""
+    tl = _f32(target_logits)
+    dp = _f32(draft_probs)
+    toks = np.ascontiguousarray(draft_tokens, dtype=np.int64)
+    v = tl.shape[-1] if tl.ndim > 1 else tl.size
+    rng = C.c_uint64(seed)
+    bonus = C.c_int64()
+    acc = lib().tbo_speculative_accept_rows(_ptr(tl), v, _ptr(toks), toks.size, _ptr(dp), temperature, top_p,
+                                            C.byref(rng), C.byref(bonus))
+    return int(acc), int(bonus.value), int(rng.value)
 
 
 LAYER_KEYS = ["input_norm_w", "qkv_w", "qkv_s", "o_w", "o_s", "post_norm_w", "gate_w", "gate_s",

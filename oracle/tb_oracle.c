@@ -858,3 +858,95 @@ int64_t tbo_sample_logits(const float* logits, int64_t vocab, float temperature,
   free(idx); free(val);
   return out;
 }
+
+/* ---------------------------------------------------- speculative acceptance */
+
+/* splitmix64 -> [0,1), src/llm/decoder.rs:643-650. */
+static double tbo_splitmix_u01(uint64_t* st) {
+  *st += 0x9E3779B97F4A7C15ull;
+  uint64_t z = *st;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return (double)(z >> 11) / 9007199254740992.0;
+}
+
+/* src/llm/decoder.rs:616-634. */
+static void tbo_softmax_row(const float* logits, int64_t v, float temp, float* out) {
+  float t = (isfinite(temp) && temp > 0.0f) ? temp : 1.0f;
+  float m = -INFINITY;
+  for (int64_t j = 0; j < v; ++j) {
+    float b = isfinite(logits[j]) ? logits[j] : -INFINITY;
+    if (b > m) m = b;
+  }
+  float s = 0.f;
+  for (int64_t j = 0; j < v; ++j) {
+    float x = isfinite(logits[j]) ? logits[j] : -INFINITY;
+    out[j] = expf((x - m) / t);
+    s += out[j];
+  }
+  float inv = 1.0f / (s > 1e-30f ? s : 1e-30f);
+  for (int64_t j = 0; j < v; ++j) out[j] *= inv;
+}
+
+/* src/llm/decoder.rs:651-726 on given target logits [k, v]; returns accepted, *bonus set.
+ * The final sort is a selection in descending order that keeps equal items in index order. */
+int64_t tbo_speculative_accept_rows(const float* target_logits, int64_t v, const int64_t* draft_tokens, int64_t k,
+                                    const float* draft_probs, float temperature, float top_p, uint64_t* rng,
+                                    int64_t* bonus) {
+  *bonus = v - 1;
+  if (k == 0) return 0;
+  if (*rng == 0) *rng = 1;
+  float* tp = (float*)malloc(sizeof(float) * (size_t)v);
+  int64_t accepted = 0;
+  for (int64_t i = 0; i < k; ++i) {
+    tbo_softmax_row(target_logits + i * v, v, temperature, tp);
+    const float* dp = draft_probs + i * v;
+    int64_t tok = draft_tokens[i] < v - 1 ? draft_tokens[i] : v - 1;
+    if (tok < 0) tok = 0;
+    float p_target = tp[tok];
+    float p_draft = dp[tok] > 0.0f ? dp[tok] : 0.0f;
+    float accept = p_target / (p_draft + 1e-12f);
+    if (accept > 1.0f) accept = 1.0f;
+    if (tbo_splitmix_u01(rng) <= (double)accept) { ++accepted; continue; }
+    float s = 0.f;
+    for (int64_t j = 0; j < v; ++j) { float c = tp[j] - dp[j]; s += c > 0.0f ? c : 0.0f; }
+    if (s > 1e-12f) {
+      float r = (float)tbo_splitmix_u01(rng) * s, acc = 0.f;
+      for (int64_t j = 0; j < v; ++j) {
+        float c = tp[j] - dp[j];
+        acc += c > 0.0f ? c : 0.0f;
+        if (acc >= r) { *bonus = j; break; }
+      }
+    } else {
+      int64_t b = 0;
+      for (int64_t j = 1; j < v; ++j) if (tp[j] >= tp[b]) b = j;
+      *bonus = b;
+    }
+    free(tp);
+    return accepted;
+  }
+  tbo_softmax_row(target_logits + (k - 1) * v, v, temperature, tp);
+  /* walk the probabilities in descending order without sorting: repeated selection is O(v*kept),
+   * fine for the test sizes this oracle runs at */
+  char* used = (char*)calloc((size_t)v, 1);
+  int64_t* order = (int64_t*)malloc(sizeof(int64_t) * (size_t)v);
+  for (int64_t i = 0; i < v; ++i) {
+    int64_t best = -1;
+    for (int64_t j = 0; j < v; ++j) if (!used[j] && (best < 0 || tp[j] > tp[best])) best = j;
+    used[best] = 1; order[i] = best;
+  }
+  int64_t kept = v;
+  if (top_p > 0.0f && top_p < 1.0f) {
+    float cum = 0.f;
+    for (int64_t i = 0; i < v; ++i) { if (cum > top_p) { kept = i; break; } cum += tp[order[i]]; }
+    if (kept < 1) kept = 1;
+  }
+  float mass = 0.f;
+  for (int64_t i = 0; i < kept; ++i) mass += tp[order[i]];
+  float r = (float)tbo_splitmix_u01(rng) * (mass > 1e-30f ? mass : 1e-30f), acc = 0.f;
+  *bonus = order[kept - 1];
+  for (int64_t i = 0; i < kept; ++i) { acc += tp[order[i]]; if (acc >= r) { *bonus = order[i]; break; } }
+  free(used); free(order); free(tp);
+  return accepted;
+}

@@ -144,6 +144,12 @@ void tbo_apply_repetition_penalty(float* logits, int64_t vocab, const int64_t* r
 int64_t tbo_sample_logits(const float* logits, int64_t vocab, float temperature, int64_t top_k, float top_p,
                           float u);
 
+/* src/llm/decoder.rs:583-727 after the verify loop: acceptance over given target logits [k, v];
+ * *rng is the splitmix64 state (the reference seeds it from the clock). */
+int64_t tbo_speculative_accept_rows(const float* target_logits, int64_t v, const int64_t* draft_tokens, int64_t k,
+                                    const float* draft_probs, float temperature, float top_p, uint64_t* rng,
+                                    int64_t* bonus);
+
 #ifdef __cplusplus
 }
 #endif

@@ -591,3 +591,45 @@ def test_decoder_width_2048_persistent_kernels_match_oracle(torch, tb, oracle):
     gk, gv = dec.read_kv_cache(2)
     ek, ev = ref.kv_cache(2)
     assert max_rel_err(gk[:, :40], ek[:, :40]) < STAGE_TOL and max_rel_err(gv[:, :40], ev[:, :40]) < STAGE_TOL
+
+
+def test_decoder_speculative_accept_matches_rows_on_verified_logits(torch, tb, oracle):
+    # speculative_accept = verify_tokens at offset.. + the acceptance rule (src/llm/decoder.rs:587-727).
+    # The rule is checked against the oracle on the logits this GPU path itself produces (a second,
+    # identical decoder verifies the same tokens), so that rounding differences between the GPU and
+    # the CPU logits cannot flip an acceptance; the logits themselves are compared with the oracle
+    # decoder elsewhere.
+    cfg = dict(vocab_size=199, hidden_size=64, intermediate_size=128, num_layers=2, num_heads=4, num_kv_heads=2,
+               head_dim=32, group_size=32, max_seq_len=48, rms_norm_eps=1e-6, rope_theta=1e6)
+    embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 31, oracle.quantize_int4_grouped, std=0.3)
+    a = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    b = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    prompt = [3, 50, 7, 120, 9]
+    rng = np.random.default_rng(2)
+    seen = set()
+    for seed in (1, 2, 3, 5, 8, 13, 21, 34):
+        for d in (a, b):
+            d.reset_kv_cache()
+            assert d.prefill_tokens(prompt, 0) == len(prompt)
+        k = 4
+        draft_tokens = rng.integers(0, cfg["vocab_size"], k)
+        rows = b.verify_tokens(len(prompt), draft_tokens)
+        e = np.exp(rows - rows.max(-1, keepdims=True)); target_p = e / e.sum(-1, keepdims=True)
+        draft_probs = (0.5 * target_p + 0.5 / cfg["vocab_size"]).astype(np.float32)
+        draft_tokens[0] = int(target_p[0].argmax())  # make early acceptance likely
+        b.reset_kv_cache(); b.prefill_tokens(prompt, 0)
+        rows = b.verify_tokens(len(prompt), draft_tokens)
+        a.seed(seed)
+        got = a.speculative_accept(len(prompt), draft_tokens, draft_probs, temperature=0.9, top_p=0.95)
+        want = oracle.speculative_accept_rows(rows, draft_tokens, draft_probs, 0.9, 0.95, seed)[:2]
+        assert got == want, (seed, got, want)
+        assert a.kv_len() == len(prompt) + k  # the cache advances over all verified positions
+        seen.add(got[0])
+    assert len(seen) >= 2
+    # the verified logits are the target model's: first row against the oracle decoder
+    ref.prefill_tokens(prompt, 0)
+    assert max_rel_err(rows[0], ref.step(int(draft_tokens[0]), len(prompt))) < LOGIT_TOL
+    assert a.speculative_accept(3, [], np.zeros((0, cfg["vocab_size"]), np.float32)) == (0, cfg["vocab_size"] - 1)
+    with pytest.raises(ValueError):
+        a.speculative_accept(3, [1, 2], np.zeros(5, np.float32))

@@ -90,6 +90,8 @@ SIGNATURES = {
     "tb_sample_logits": (_i32, [_p, _i64, _f32, _i64, _f32, _f32, C.POINTER(_i64)]),
     "tb_push_recent_window": (_i64, [_p, _i64, _i64]),
     "tb_decoder_decode_and_sample": (_i32, [_p, _i64, _i64, _f32, _i64, _f32, _p, _i64, _f32, C.POINTER(C.c_uint64), C.POINTER(_i64)]),
+    "tb_speculative_accept_rows": (_i32, [_p, _i64, _p, _i64, _p, _f32, _f32, _p, _p, _p]),
+    "tb_decoder_speculative_accept": (_i32, [_p, _i64, _p, _i64, _p, _f32, _f32, _p, _p, _p]),
     "tb_decoder_generate_loop": (_i32, [_p, _i64, _i64, _i64, _f32, _i64, _f32, _f32, _i64, _p, _i64, C.POINTER(C.c_uint64), _p, C.POINTER(_i64), C.POINTER(_i64)]),
     "tb_decoder_debug_stage": (_i32, [_p, C.c_char_p, _p, _i64, C.POINTER(_i64)]),
     "tb_decoder_step_timed": (_i32, [_p, _i64, _i64, _p, C.POINTER(_f32 * 3)]),

@@ -604,6 +604,28 @@ tb_status tb_decoder_verify_tokens(tb_decoder* d, int64_t start_offset, const in
   return TB_OK;
 }
 
+tb_status tb_decoder_speculative_accept(tb_decoder* d, int64_t offset, const int64_t* draft_tokens, int64_t k,
+                                        const float* draft_probs, float temperature, float top_p,
+                                        uint64_t* rng_state, int64_t* accepted, int64_t* bonus) {
+  TB_TRY(check_alive(d, "tb_decoder_speculative_accept"));
+  if (!accepted || !bonus || !rng_state || k < 0 || offset < 0 || (k > 0 && (!draft_tokens || !draft_probs)))
+    return fail(TB_ERR_ARG, "tb_decoder_speculative_accept: bad arguments");
+  if (k == 0) {  // src/llm/decoder.rs:594-596
+    *accepted = 0;
+    *bonus = d->V - 1;
+    return TB_OK;
+  }
+  std::vector<float> rows;
+  try {
+    rows.resize((size_t)k * (size_t)d->V);
+  } catch (...) {
+    return fail(TB_ERR_OOM, "tb_decoder_speculative_accept: host allocation failed");
+  }
+  TB_TRY(tb_decoder_verify_tokens(d, offset, draft_tokens, k, rows.data()));
+  return tb_speculative_accept_rows(rows.data(), d->V, draft_tokens, k, draft_probs, temperature, top_p, rng_state,
+                                    accepted, bonus);
+}
+
 tb_status tb_decoder_reset_kv_cache(tb_decoder* d) {
   TB_TRY(check_alive(d, "tb_decoder_reset_kv_cache"));
   const int64_t used = d->kv_used < d->S ? d->kv_used : d->S;

@@ -119,4 +119,102 @@ int64_t tb_push_recent_window(int64_t* recent, int64_t n_recent, int64_t token) 
   return n_recent + 1;
 }
 
+
+// Leviathan acceptance over the target logits of the K verified positions,
+// src/llm/decoder.rs:583-727 (speculative_accept after its verify loop).  The reference seeds a
+// splitmix64 generator from the clock; here the caller owns the state, the stream of draws is
+// the same function of it.
+static double splitmix_u01(uint64_t* st) {
+  *st += 0x9E3779B97F4A7C15ull;
+  uint64_t z = *st;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return (double)(z >> 11) / (double)(1ull << 53);
+}
+
+static void softmax_row(const float* logits, int64_t v, float temp, std::vector<float>& out) {
+  const float t = (std::isfinite(temp) && temp > 0.0f) ? temp : 1.0f;
+  float m = -INFINITY;
+  for (int64_t j = 0; j < v; ++j) m = std::max(m, std::isfinite(logits[j]) ? logits[j] : -INFINITY);
+  out.resize((size_t)v);
+  float s = 0.f;
+  for (int64_t j = 0; j < v; ++j) {
+    const float x = std::isfinite(logits[j]) ? logits[j] : -INFINITY;
+    out[(size_t)j] = std::exp((x - m) / t);
+    s += out[(size_t)j];
+  }
+  const float inv = 1.0f / std::max(s, 1e-30f);
+  for (int64_t j = 0; j < v; ++j) out[(size_t)j] *= inv;
+}
+
+tb_status tb_speculative_accept_rows(const float* target_logits, int64_t vocab, const int64_t* draft_tokens,
+                                     int64_t k, const float* draft_probs, float temperature, float top_p,
+                                     uint64_t* rng_state, int64_t* accepted, int64_t* bonus) {
+  if (!accepted || !bonus || !rng_state || vocab < 1 || k < 0)
+    return fail(TB_ERR_ARG, "tb_speculative_accept_rows: bad arguments");
+  *accepted = 0;
+  *bonus = vocab - 1;
+  if (k == 0) return TB_OK;  // decoder.rs:594-596
+  if (!target_logits || !draft_tokens || !draft_probs) return fail(TB_ERR_ARG, "tb_speculative_accept_rows: null operand");
+  if (*rng_state == 0) *rng_state = 1;  // decoder.rs:642 (.max(1))
+  const int64_t v = vocab;
+  std::vector<float> tp;
+  for (int64_t i = 0; i < k; ++i) {
+    softmax_row(target_logits + i * v, v, temperature, tp);
+    const float* dp = draft_probs + i * v;
+    const int64_t tok = std::min<int64_t>(std::max<int64_t>(draft_tokens[i], 0), v - 1);
+    const float p_target = tp[(size_t)tok];
+    const float p_draft = std::max(dp[tok], 0.0f);
+    const float accept = std::min(p_target / (p_draft + 1e-12f), 1.0f);
+    if (splitmix_u01(rng_state) <= (double)accept) {
+      ++*accepted;
+      continue;
+    }
+    // rejected: resample from max(0, p_target - p_draft)
+    float s = 0.f;
+    for (int64_t j = 0; j < v; ++j) s += std::max(tp[(size_t)j] - dp[j], 0.0f);
+    if (s > 1e-12f) {
+      const float r = (float)splitmix_u01(rng_state) * s;
+      float acc = 0.f;
+      int64_t b = v - 1;
+      for (int64_t j = 0; j < v; ++j) {
+        acc += std::max(tp[(size_t)j] - dp[j], 0.0f);
+        if (acc >= r) { b = j; break; }
+      }
+      *bonus = b;
+    } else {
+      int64_t b = 0;  // max_by keeps the last maximum
+      for (int64_t j = 0; j < v; ++j)
+        if (!(tp[(size_t)j] < tp[(size_t)b])) b = j;
+      *bonus = b;
+    }
+    return TB_OK;
+  }
+  // all accepted: the bonus token comes from the last verified row, with the nucleus cut
+  softmax_row(target_logits + (k - 1) * v, v, temperature, tp);
+  std::vector<int64_t> idx((size_t)v);
+  for (int64_t j = 0; j < v; ++j) idx[(size_t)j] = j;
+  std::stable_sort(idx.begin(), idx.end(), [&](int64_t a, int64_t b) { return tp[(size_t)a] > tp[(size_t)b]; });
+  int64_t kept = v;
+  if (top_p > 0.0f && top_p < 1.0f) {
+    float cum = 0.f;
+    for (int64_t i = 0; i < v; ++i) {
+      if (cum > top_p) { kept = i; break; }
+      cum += tp[(size_t)idx[(size_t)i]];
+    }
+    kept = std::max<int64_t>(kept, 1);
+  }
+  float mass = 0.f;
+  for (int64_t i = 0; i < kept; ++i) mass += tp[(size_t)idx[(size_t)i]];
+  const float r = (float)splitmix_u01(rng_state) * std::max(mass, 1e-30f);
+  float acc = 0.f;
+  int64_t b = idx[(size_t)(kept - 1)];
+  for (int64_t i = 0; i < kept; ++i) {
+    acc += tp[(size_t)idx[(size_t)i]];
+    if (acc >= r) { b = idx[(size_t)i]; break; }
+  }
+  *bonus = b;
+  return TB_OK;
+}
 }  // extern "C"

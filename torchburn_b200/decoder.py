@@ -189,6 +189,20 @@ class B200QwenDecoder:
                                              C.byref(n), C.byref(end)))
         return [int(t) for t in out[: n.value]], int(end.value)
 
+    def speculative_accept(self, offset: int, draft_tokens: Sequence[int], draft_probs, temperature: float = 1.0,
+                           top_p: float = 1.0):
+        """speculative_accept (src/llm/decoder.rs:587-727): verifies the draft tokens at offset,
+        offset+1, ... with this (target) decoder and applies Leviathan acceptance against
+        draft_probs [K, V]; returns (accepted_count, bonus_token)."""
+        toks = np.ascontiguousarray(draft_tokens, dtype=np.int64)
+        probs = np.ascontiguousarray(draft_probs, dtype=np.float32).reshape(-1)
+        if toks.size and probs.size != toks.size * self.vocab_size:
+            raise ValueError("draft_probs must be K x V row-major")  # decoder.rs:598-602
+        acc, bonus = C.c_int64(), C.c_int64()
+        check(lib().tb_decoder_speculative_accept(self._h, int(offset), toks.ctypes.data, toks.size, probs.ctypes.data,
+                                                  temperature, top_p, C.byref(self._rng), C.byref(acc), C.byref(bonus)))
+        return int(acc.value), int(bonus.value)
+
     def seed(self, value: int) -> None:
         """Seeds the sampling RNG (the reference uses an unseeded thread RNG)."""
         self._rng = C.c_uint64(value or 1)
