@@ -200,6 +200,26 @@ tb_status tb_linear_create(tb_linear** out, const uint8_t* qweight, const float*
                            const float* bias, int64_t out_features, int64_t in_features,
                            int32_t group_size, tb_space weight_space);
 void tb_linear_destroy(tb_linear* lin);
+
+/* The interleaved "v2" weight layout (src/quantization/packed_v2.rs:26-143,
+ * python/torchburn/quantization.py:121-170): group size 64 only; each group of a row is one
+ * 34-byte block = 32 bytes of packed nibbles + the scale as IEEE binary16, little-endian; a row
+ * is (in_features / 64) blocks.  All of these are host functions.
+ *   tb_f32_to_f16 / tb_f16_to_f32   f32_to_f16 (round to nearest even) and f16_to_f32 (:30-112)
+ *   tb_pack_v1_to_v2                pack_rows_w4a32_group64_v1_to_v2 (:114-143)
+ *   tb_unpack_v2_to_v1              the inverse; the fp32 scales are the binary16 values
+ *   tb_linear_create_v2             a tb_linear from v2 blocks (host or device), the role of
+ *                                   w4a32_grouped_linear_v2 (quantization.py:172-190): unpacked
+ *                                   once, then the same kernels run with the binary16 scales.
+ * in_features not divisible by 64 -> TB_ERR_SHAPE ("TB_UNSUPPORTED:", as packed_v2.rs:566-596). */
+uint16_t tb_f32_to_f16(float value);
+float tb_f16_to_f32(uint16_t bits);
+tb_status tb_pack_v1_to_v2(const uint8_t* qweight, const float* scales, int64_t out_features,
+                           int64_t in_features, uint8_t* blocks);
+tb_status tb_unpack_v2_to_v1(const uint8_t* blocks, int64_t out_features, int64_t in_features,
+                             uint8_t* qweight, float* scales);
+tb_status tb_linear_create_v2(tb_linear** out, const uint8_t* blocks, const float* bias,
+                              int64_t out_features, int64_t in_features, tb_space weight_space);
 /* QuantizedLinear.forward -> w4a32_grouped_linear (quantization.py:826-866,
  * src/ffi/quantization_ffi.rs:56-85): x [m, in_features] -> out [m, out_features].
  * io_space says where x and out live; host buffers are staged through pinned

@@ -94,6 +94,10 @@ def lib():
         L.tbo_decoder_debug_stage.restype = i64
         L.tbo_argmax.argtypes = [p, i64]; L.tbo_argmax.restype = i64
         L.tbo_speculative_accept_rows.argtypes = [p, i64, p, i64, p, f32, f32, p, p]; L.tbo_speculative_accept_rows.restype = i64
+        L.tbo_f32_to_f16.argtypes = [f32]; L.tbo_f32_to_f16.restype = C.c_uint16
+        L.tbo_f16_to_f32.argtypes = [C.c_uint16]; L.tbo_f16_to_f32.restype = f32
+        L.tbo_pack_v1_to_v2.argtypes = [p, p, i64, i64, p]
+        L.tbo_gemv_w4a32_v2.argtypes = [p, p, p, p, i64, i64]
         L.tbo_apply_repetition_penalty.argtypes = [p, i64, p, i64, f32]
         L.tbo_sample_logits.argtypes = [p, i64, f32, i64, f32, f32]; L.tbo_sample_logits.restype = i64
         _lib = L
@@ -261,6 +265,33 @@ def speculative_accept_rows(target_logits, draft_tokens, draft_probs, temperatur
     acc = lib().tbo_speculative_accept_rows(_ptr(tl), v, _ptr(toks), toks.size, _ptr(dp), temperature, top_p,
                                             C.byref(rng), C.byref(bonus))
     return int(acc), int(bonus.value), int(rng.value)
+
+
+def f32_to_f16(v: float) -> int:
+    return int(lib().tbo_f32_to_f16(v))
+
+
+def f16_to_f32(bits: int) -> float:
+    return float(lib().tbo_f16_to_f32(bits))
+
+
+def pack_v1_to_v2(packed, scales) -> np.ndarray:
+    pk = np.ascontiguousarray(packed, dtype=np.uint8)
+    sc = _f32(scales)
+    n, k = pk.shape[0], pk.shape[1] * 2
+    out = np.empty((n, (k // 64) * 34), np.uint8)
+    lib().tbo_pack_v1_to_v2(_ptr(pk), _ptr(sc), n, k, _ptr(out))
+    return out
+
+
+def gemv_w4a32_v2(x, blocks, bias=None) -> np.ndarray:
+    xv = _f32(x).reshape(-1)
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    n, k = b.shape[0], (b.shape[1] // 34) * 64
+    out = np.empty(n, np.float32)
+    bb = _f32(bias) if bias is not None else None
+    lib().tbo_gemv_w4a32_v2(_ptr(xv), _ptr(b), _ptr(bb), _ptr(out), n, k)
+    return out
 
 
 LAYER_KEYS = ["input_norm_w", "qkv_w", "qkv_s", "o_w", "o_s", "post_norm_w", "gate_w", "gate_s",

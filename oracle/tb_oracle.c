@@ -950,3 +950,73 @@ int64_t tbo_speculative_accept_rows(const float* target_logits, int64_t v, const
   free(used); free(order); free(tp);
   return accepted;
 }
+
+
+/* ------------------------------------------------------------ v2 layout */
+
+/* src/quantization/packed_v2.rs:67-112 (round to nearest even). */
+uint16_t tbo_f32_to_f16(float v) {
+  uint32_t x;
+  memcpy(&x, &v, 4);
+  uint16_t sign = (uint16_t)((x >> 16) & 0x8000u);
+  int exp_abs = (int)((x >> 23) & 0xFF);
+  uint32_t mant = x & 0x007FFFFFu;
+  if (exp_abs == 0xFF) return (uint16_t)(mant == 0 ? (sign | 0x7C00u) : (sign | 0x7E00u));
+  int e = exp_abs - 127;
+  if (e > 15) return (uint16_t)(sign | 0x7C00u);
+  if (e >= -14) {
+    uint32_t h_exp = (uint32_t)(e + 15), h_mant = mant >> 13, rem = mant & 0x1FFFu;
+    uint32_t h = (h_exp << 10) | h_mant;
+    if (rem > 0x1000u || (rem == 0x1000u && (h_mant & 1u) == 1u)) h += 1;
+    return (uint16_t)(sign | h);
+  }
+  if (e < -25) return sign;
+  uint32_t full = mant | 0x00800000u;
+  uint32_t shift = (uint32_t)(-e - 1);
+  uint32_t h_mant = full >> shift, rem = full & ((1u << shift) - 1u), round = 1u << (shift - 1);
+  uint32_t m = h_mant;
+  if (rem > round || (rem == round && (h_mant & 1u) == 1u)) m += 1;
+  return (uint16_t)(sign | m);
+}
+
+/* src/quantization/packed_v2.rs:30-57. */
+float tbo_f16_to_f32(uint16_t bits) {
+  uint32_t sign = (bits >> 15) & 1u, exp = (bits >> 10) & 0x1Fu, mant = bits & 0x3FFu;
+  if (exp == 0) {
+    if (mant == 0) return sign ? -0.0f : 0.0f;
+    float v = ((float)mant / 1024.0f) * ldexpf(1.0f, -14);
+    return sign ? -v : v;
+  }
+  if (exp == 0x1F) return mant == 0 ? (sign ? -INFINITY : INFINITY) : NAN;
+  uint32_t o = (sign << 31) | ((exp + 112u) << 23) | (mant << 13);
+  float f;
+  memcpy(&f, &o, 4);
+  return f;
+}
+
+/* src/quantization/packed_v2.rs:120-143. */
+void tbo_pack_v1_to_v2(const uint8_t* w_packed, const float* scales, int64_t n, int64_t k, uint8_t* out) {
+  int64_t ng = k / 64, src_row = (k + 1) / 2;
+  for (int64_t row = 0; row < n; ++row)
+    for (int64_t g = 0; g < ng; ++g) {
+      uint8_t* dst = out + row * ng * 34 + g * 34;
+      memcpy(dst, w_packed + row * src_row + g * 32, 32);
+      uint16_t h = tbo_f32_to_f16(scales[row * ng + g]);
+      dst[32] = (uint8_t)(h & 0xFF);
+      dst[33] = (uint8_t)(h >> 8);
+    }
+}
+
+/* src/quantization/packed_v2.rs:145-203 (scalar v2 row kernel): per group, dot of x with the
+ * codes times the binary16 scale. */
+void tbo_gemv_w4a32_v2(const float* x, const uint8_t* blocks, const float* bias, float* out, int64_t n, int64_t k) {
+  int64_t ng = k / 64;
+  for (int64_t row = 0; row < n; ++row) {
+    float s = 0.0f;
+    for (int64_t g = 0; g < ng; ++g) {
+      const uint8_t* b = blocks + (row * ng + g) * 34;
+      s += dot_group_scalar(x + g * 64, b, 64) * tbo_f16_to_f32((uint16_t)(b[32] | (b[33] << 8)));
+    }
+    out[row] = s + (bias ? bias[row] : 0.0f);
+  }
+}

@@ -150,6 +150,12 @@ int64_t tbo_speculative_accept_rows(const float* target_logits, int64_t v, const
                                     const float* draft_probs, float temperature, float top_p, uint64_t* rng,
                                     int64_t* bonus);
 
+/* v2 layout, src/quantization/packed_v2.rs:26-203. */
+uint16_t tbo_f32_to_f16(float v);
+float tbo_f16_to_f32(uint16_t bits);
+void tbo_pack_v1_to_v2(const uint8_t* w_packed, const float* scales, int64_t n, int64_t k, uint8_t* out);
+void tbo_gemv_w4a32_v2(const float* x, const uint8_t* blocks, const float* bias, float* out, int64_t n, int64_t k);
+
 #ifdef __cplusplus
 }
 #endif

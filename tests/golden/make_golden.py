@@ -20,7 +20,7 @@ linear's weight replaced by dequant(quantize(weight)) - the definition of the
 W4A32 linear (tests/test_parity.py:51-64) - one token at a time through the
 static KV cache, which is what ``RustQwenDecoder.step_internal`` computes.
 
-Outputs (committed): quantizer_golden.npz, decoder_qwen_tiny_g32.npz,
+Outputs (committed): quantizer_golden.npz, layout_v2_golden.npz, decoder_qwen_tiny_g32.npz,
 decoder_llama_tiny_g64.npz.
 """
 from __future__ import annotations
@@ -157,10 +157,28 @@ def decoder_case(quant, config, model, *, seed, group_size, cfg_kwargs, tokens, 
     return out
 
 
+def v2_cases(quant):
+    """The reference's own v2 quantizer and dequantizer (quantization.py:121-169)."""
+    g = torch.Generator().manual_seed(77)
+    w = torch.randn(6, 256, generator=g) * 0.05
+    w[0, :64] *= 1e-4   # a group whose scale is a binary16 subnormal
+    w[1, 64:128] *= 40  # a large scale
+    packed, scales = quant.quantize_weight_int4_grouped(w, group_size=64)
+    blocked = quant.quantize_weight_int4_grouped_v2(w, group_size=64)
+    deq = quant.dequantize_int4_grouped_v2(blocked, 64)
+    vals = torch.tensor([0.0, -0.0, 1.0, -1.0, 0.5, 2.0, 65504.0, -3.75, 1234.5, 1e-4, 6.0e-5, 6.1e-8, 1e6, -1e6,
+                         0.1, 3.1415927, 2.0 ** -14, 2.0 ** -24, 2.0 ** -25, 65519.0, 65520.0, 1.00048828125])
+    half_bits = vals.half().view(torch.int16).numpy().astype(np.uint16)
+    return {"w": w.numpy(), "packed": packed.numpy(), "scales": scales.numpy(), "blocked": blocked.numpy(),
+            "dequant": deq.numpy(), "f16_inputs": vals.numpy(), "f16_bits": half_bits,
+            "f16_back": vals.half().float().numpy()}
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     quant, config, model = load_reference(ref_root)
     np.savez_compressed(os.path.join(HERE, "quantizer_golden.npz"), **quantizer_cases(quant))
+    np.savez_compressed(os.path.join(HERE, "layout_v2_golden.npz"), **v2_cases(quant))
     qwen = decoder_case(
         quant, config, model, seed=11, group_size=32,
         cfg_kwargs=dict(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=2,

@@ -633,3 +633,38 @@ def test_decoder_speculative_accept_matches_rows_on_verified_logits(torch, tb, o
     assert a.speculative_accept(3, [], np.zeros((0, cfg["vocab_size"]), np.float32)) == (0, cfg["vocab_size"] - 1)
     with pytest.raises(ValueError):
         a.speculative_accept(3, [1, 2], np.zeros(5, np.float32))
+
+
+def test_v2_layout_linear_matches_oracle_v2_kernel(torch, tb, oracle):
+    # python/torchburn/quantization.py:121-190 and tests/test_parity.py:156-206: the v2 blocks carry the
+    # same codes as v1 and binary16 scales; the linear on them equals the scalar v2 kernel of the
+    # reference (oracle) within fp32 rounding and the v1 result within the binary16 budget (5e-3).
+    torch.manual_seed(3)
+    n, k = 96, 512
+    w = torch.randn(n, k) * 0.05
+    x = torch.randn(3, k)
+    bias = torch.randn(n)
+    blocked = tb.quantize_weight_int4_grouped_v2(w.cuda(), group_size=64)
+    packed, scales = tb.quantize_weight_int4_grouped(w.cuda(), group_size=64)
+    assert blocked.shape == (n, (k // 64) * 34) and blocked.dtype == torch.uint8
+    assert np.array_equal(blocked.numpy(), oracle.pack_v1_to_v2(packed.cpu().numpy(), scales.cpu().numpy()))
+    got = tb.w4a32_grouped_linear_v2(x, blocked, bias).numpy()
+    for m in range(3):
+        want = oracle.gemv_w4a32_v2(x[m].numpy(), blocked.numpy(), bias.numpy())
+        assert max_rel_err(got[m], want) < STAGE_TOL
+    v1 = tb.w4a32_grouped_linear(x, packed, scales, bias, group_size=64).numpy()
+    assert max_rel_err(got, v1) < 5e-3
+    deq = tb.dequantize_int4_grouped_v2(blocked).numpy()
+    assert max_rel_err(deq, oracle.dequant_int4_grouped(packed.cpu().numpy(), scales.cpu().numpy(), 64)) < 1e-3
+    # a linear object made straight from the blocks (host or device memory)
+    import ctypes as C
+    L = tb.lib()
+    for space, blk in ((0, blocked.numpy()), (1, blocked.cuda())):
+        h = C.c_void_p()
+        ptr = blk.ctypes.data if space == 0 else blk.data_ptr()
+        tb._lib.check(L.tb_linear_create_v2(C.byref(h), ptr, None, n, k, space))
+        out = np.empty((3, n), np.float32)
+        xs = np.ascontiguousarray(x.numpy())
+        tb._lib.check(L.tb_linear_forward(h, xs.ctypes.data, 3, out.ctypes.data, 0, None))
+        L.tb_linear_destroy(h)
+        assert max_rel_err(out + bias.numpy(), got) < 1e-5

@@ -11,16 +11,19 @@ from ._lib import TorchBurnB200Error, abi_version, device_report, lib, last_erro
 from .decoder import B200QwenDecoder, create_b200_qwen_decoder
 from .quantization import (
     QuantizedLinear,
+    dequantize_int4_grouped_v2,
     fused_attention_step,
     fused_swiglu_mlp,
     fused_swiglu_mlp_batched,
     quantize_weight_int4_grouped,
+    quantize_weight_int4_grouped_v2,
     w4a32_grouped_linear,
+    w4a32_grouped_linear_v2,
 )
 
 __all__ = [
     "TorchBurnB200Error", "abi_version", "device_report", "lib", "last_error",
     "B200QwenDecoder", "create_b200_qwen_decoder", "QuantizedLinear", "fused_attention_step",
     "fused_swiglu_mlp", "fused_swiglu_mlp_batched", "quantize_weight_int4_grouped",
-    "w4a32_grouped_linear",
+    "w4a32_grouped_linear", "quantize_weight_int4_grouped_v2", "dequantize_int4_grouped_v2", "w4a32_grouped_linear_v2",
 ]

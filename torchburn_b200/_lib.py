@@ -66,6 +66,11 @@ SIGNATURES = {
     "tb_set_stream_tuning": (None, [_i32, _i32, _i32, _i32, _i32]),
     "tb_device_fault_flag": (_i32, []),
     "tb_linear_create": (_i32, [_PP, _p, _p, _p, _i64, _i64, _i32, _i32]),
+    "tb_f32_to_f16": (C.c_uint16, [_f32]),
+    "tb_f16_to_f32": (_f32, [C.c_uint16]),
+    "tb_pack_v1_to_v2": (_i32, [_p, _p, _i64, _i64, _p]),
+    "tb_unpack_v2_to_v1": (_i32, [_p, _i64, _i64, _p, _p]),
+    "tb_linear_create_v2": (_i32, [_PP, _p, _p, _i64, _i64, _i32]),
     "tb_linear_destroy": (None, [_p]),
     "tb_linear_forward": (_i32, [_p, _p, _i64, _p, _i32, _p]),
     "tb_linear_device_ptrs": (_i32, [_p, _PP, _PP, _PP]),

@@ -9,6 +9,7 @@ from __future__ import annotations
 import ctypes as C
 from typing import Optional, Tuple
 
+import numpy as np
 import torch
 import torch.nn as nn
 
@@ -98,6 +99,54 @@ def w4a32_grouped_linear(
                                           M, N, K, group_size, _stream_ptr(dev)))
     out = out.reshape(list(x_orig_shape[:-1]) + [N])
     return out.cpu() if on_cpu else out
+
+
+# ---- the interleaved "v2" layout (34-byte blocks, binary16 scales, group 64) -----------------
+def _v2_unpack(blocked: torch.Tensor):
+    """blocked (N, G*34) uint8 -> (packed (N, G*32) uint8, scales (N, G) float32) through the C ABI."""
+    if blocked.dtype != torch.uint8 or blocked.ndim != 2 or blocked.shape[1] % 34 != 0:
+        raise _lib.TorchBurnB200Error(2, "TB_UNSUPPORTED: v2 weights must be a (N, groups*34) uint8 tensor")
+    b = np.ascontiguousarray(blocked.detach().cpu().numpy())
+    n, ng = b.shape[0], b.shape[1] // 34
+    packed = np.empty((n, ng * 32), np.uint8)
+    scales = np.empty((n, ng), np.float32)
+    check(lib().tb_unpack_v2_to_v1(b.ctypes.data, n, ng * 64, packed.ctypes.data, scales.ctypes.data))
+    return torch.from_numpy(packed), torch.from_numpy(scales)
+
+
+def quantize_weight_int4_grouped_v2(weight: torch.Tensor, group_size: int = 64, chunk_size: int = 1024) -> torch.Tensor:
+    """quantize_weight_int4_grouped_v2 of python/torchburn/quantization.py:121-151: the same codes
+    and scales as the v1 quantizer, stored as one 34-byte block per 64-element group."""
+    if group_size != 64:
+        raise ValueError("the v2 layout is defined for group_size 64")
+    N, K = weight.shape
+    if K % group_size != 0:
+        raise ValueError(f"K={K} must be divisible by group_size={group_size}")
+    packed, scales = quantize_weight_int4_grouped(weight, group_size=group_size, chunk_size=chunk_size)
+    p = np.ascontiguousarray(packed.cpu().numpy())
+    sc = np.ascontiguousarray(scales.cpu().numpy(), dtype=np.float32)
+    out = np.empty((N, (K // 64) * 34), np.uint8)
+    check(lib().tb_pack_v1_to_v2(p.ctypes.data, sc.ctypes.data, N, K, out.ctypes.data))
+    return torch.from_numpy(out)
+
+
+def dequantize_int4_grouped_v2(blocked: torch.Tensor, group_size: int = 64) -> torch.Tensor:
+    """dequantize_int4_grouped_v2 of python/torchburn/quantization.py:154-169: the f32 matrix (N, K)."""
+    packed, scales = _v2_unpack(blocked)
+    lo = (packed & 0x0F).to(torch.int8)
+    hi = ((packed >> 4) & 0x0F).to(torch.int8)
+    q = torch.stack([lo, hi], dim=2).reshape(packed.shape[0], -1) - 8
+    return q.float() * scales.repeat_interleave(64, dim=1)
+
+
+def w4a32_grouped_linear_v2(x: torch.Tensor, blocked: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                            group_size: int = 64) -> torch.Tensor:
+    """w4a32_grouped_linear_v2 of python/torchburn/quantization.py:172-190: x (..., K) @ dequant(blocked)^T
+    + bias.  The blocks are unpacked (binary16 scales widened to fp32) and the v1 kernels run."""
+    if group_size != 64:
+        raise ValueError("the v2 layout is defined for group_size 64")
+    packed, scales = _v2_unpack(blocked)
+    return w4a32_grouped_linear(x, packed, scales, bias, group_size=64)
 
 
 class QuantizedLinear(nn.Module):
