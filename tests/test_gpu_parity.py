@@ -668,3 +668,69 @@ def test_v2_layout_linear_matches_oracle_v2_kernel(torch, tb, oracle):
         tb._lib.check(L.tb_linear_forward(h, xs.ctypes.data, 3, out.ctypes.data, 0, None))
         L.tb_linear_destroy(h)
         assert max_rel_err(out + bias.numpy(), got) < 1e-5
+
+
+def test_loader_checkpoint_to_cache_to_decoder(torch, tb, oracle, tmp_path):
+    # python/torchburn/llm/loader.py:376-537 (stream quantize + QKV fusion + tied lm_head), :520-535
+    # (safetensors cache), :542-606 (v2 cache and its migration) and create_rust_qwen_decoder.
+    from torchburn_b200 import loader
+    cfg = dict(vocab_size=160, hidden_size=128, intermediate_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+               head_dim=32, group_size=64, max_seq_len=24, rms_norm_eps=1e-6, rope_theta=1e6)
+    g = torch.Generator().manual_seed(5)
+    H, I, hd, nh, nkv = 128, 256, 32, 4, 2
+    ck = {"model.embed_tokens.weight": torch.randn(160, H, generator=g) * 0.05, "model.norm.weight": 1 + 0.1 * torch.randn(H, generator=g)}
+    for i in range(2):
+        p = f"model.layers.{i}."
+        ck[p + "input_layernorm.weight"] = 1 + 0.1 * torch.randn(H, generator=g)
+        ck[p + "post_attention_layernorm.weight"] = 1 + 0.1 * torch.randn(H, generator=g)
+        for n, rows in (("q", nh * hd), ("k", nkv * hd), ("v", nkv * hd)):
+            ck[p + f"self_attn.{n}_proj.weight"] = torch.randn(rows, H, generator=g) * 0.05
+            ck[p + f"self_attn.{n}_proj.bias"] = torch.randn(rows, generator=g) * 0.05
+        ck[p + "self_attn.o_proj.weight"] = torch.randn(H, nh * hd, generator=g) * 0.05
+        ck[p + "mlp.gate_proj.weight"] = torch.randn(I, H, generator=g) * 0.05
+        ck[p + "mlp.up_proj.weight"] = torch.randn(I, H, generator=g) * 0.05
+        ck[p + "mlp.down_proj.weight"] = torch.randn(H, I, generator=g) * 0.05
+    sd = loader.quantize_checkpoint({k: v.cuda() for k, v in ck.items()}, 2, group_size=64, tie_word_embeddings=True, qkv_bias=True)
+    # fusion order and bit-exact codes against the oracle quantizer on the concatenated rows
+    fused = torch.cat([ck["model.layers.1.self_attn.q_proj.weight"], ck["model.layers.1.self_attn.k_proj.weight"],
+                       ck["model.layers.1.self_attn.v_proj.weight"]]).numpy()
+    ep, es = oracle.quantize_int4_grouped(fused, 64)
+    assert np.array_equal(sd["layers.1.self_attn.qkv_proj.qweight"].numpy(), ep)
+    assert np.array_equal(sd["layers.1.self_attn.qkv_proj.scales"].numpy(), es)
+    assert sd["layers.0.self_attn.qkv_proj.bias"].shape == ((nh + 2 * nkv) * hd,)
+    lp, ls = oracle.quantize_int4_grouped(ck["model.embed_tokens.weight"].numpy(), 64)
+    assert np.array_equal(sd["lm_head.qweight"].numpy(), lp) and np.array_equal(sd["lm_head.scales"].numpy(), ls)
+    with pytest.raises(KeyError):
+        loader.quantize_checkpoint({k: v for k, v in ck.items() if "o_proj" not in k}, 2)
+
+    v1 = loader.save_cache(sd, str(tmp_path / loader.CACHE_V1.format(g=64)))
+    assert loader.find_cache(str(tmp_path)) == v1
+    back = loader.load_cache(v1)
+    assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)
+    v2 = loader.save_cache(loader.migrate_state_dict_to_v2(sd), str(tmp_path / loader.CACHE_V2))
+    assert loader.find_cache(str(tmp_path)) == v2  # the v2 file is preferred (loader.py:92-99)
+    sd2 = loader.load_cache(v2)
+    assert set(sd2) == set(sd)
+    assert torch.equal(sd2["layers.0.mlp.down_proj.qweight"], sd["layers.0.mlp.down_proj.qweight"])
+    assert torch.equal(sd2["layers.0.mlp.down_proj.scales"], sd["layers.0.mlp.down_proj.scales"].half().float())
+    assert os.path.getsize(v2) < os.path.getsize(v1)
+
+    def layers_of(d):
+        out = []
+        for i in range(2):
+            p = f"layers.{i}."
+            out.append({"input_norm_w": d[p + "input_layernorm.weight"].numpy(), "post_norm_w": d[p + "post_attention_layernorm.weight"].numpy(),
+                        "qkv_w": d[p + "self_attn.qkv_proj.qweight"].numpy(), "qkv_s": d[p + "self_attn.qkv_proj.scales"].numpy(),
+                        "qkv_b": d[p + "self_attn.qkv_proj.bias"].numpy(),
+                        "o_w": d[p + "self_attn.o_proj.qweight"].numpy(), "o_s": d[p + "self_attn.o_proj.scales"].numpy(),
+                        "gate_w": d[p + "mlp.gate_proj.qweight"].numpy(), "gate_s": d[p + "mlp.gate_proj.scales"].numpy(),
+                        "up_w": d[p + "mlp.up_proj.qweight"].numpy(), "up_s": d[p + "mlp.up_proj.scales"].numpy(),
+                        "down_w": d[p + "mlp.down_proj.qweight"].numpy(), "down_s": d[p + "mlp.down_proj.scales"].numpy()})
+        return out
+
+    for d in (back, sd2):  # v1 cache, and the v2 cache with its binary16 scales
+        dec = loader.decoder_from_state_dict(d, 2, H, I, nh, nkv, hd, group_size=64, rms_norm_eps=1e-6, max_seq_len=24, rope_theta=1e6)
+        ref = oracle.OracleDecoder(cfg, d["embed_tokens.weight"].numpy(), layers_of(d), d["norm.weight"].numpy(),
+                                   d["lm_head.qweight"].numpy(), d["lm_head.scales"].numpy())
+        for off, t in enumerate([3, 150, 9, 77, 0]):
+            assert max_rel_err(dec.step(t, off), ref.step(t, off)) < LOGIT_TOL
