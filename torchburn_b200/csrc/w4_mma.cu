@@ -279,12 +279,211 @@ tb_status launch_mma_cfg(const MmaParams& p, cudaStream_t stream) {
   return TB_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Second layout of the same products: every warp keeps 16 weight rows for ALL activation tiles
+// (MT tiles of 8 activation rows, accumulators in registers), WR such warps stand side by side
+// and WK warps split the blocks of K of each stage, so that a CTA covers 16 * WR rows and the
+// digit tiles of a stage - which every warp needs - are fetched once per 16 * WR rows instead
+// of once per 16 or 32.  With 64 activation rows the digits are 13 times the bytes of the
+// weights they meet; re-reading them per small row tile was what bounded the first layout.
+// Scales ride in the stage too (no global load inside the K loop); three cp.async stages.
+// ------------------------------------------------------------------------------------------
+template <int MT, int WR, int WK, int EPI, int KC>
+__global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaParams p) {
+  constexpr int NW = EPI == 1 ? 2 : 1;
+  constexpr int NT = 32 * WR * WK;        // threads
+  constexpr int RC = 16 * WR;             // weight rows per CTA
+  constexpr int WROW = KC * 4 + 4;        // words per staged weight row (16 bytes of padding)
+  constexpr int SROW = KC + 1;            // staged scales per row (padded)
+  constexpr int NS = 3;                   // stages
+  extern __shared__ __align__(16) uint32_t sm[];
+  // stage layout: weights [NW][RC][WROW] | scales [NW][RC][SROW] | digits [KC][MT][208]
+  constexpr int W_WORDS = NW * RC * WROW;
+  constexpr int S_WORDS = (NW * RC * SROW + 3) & ~3;
+  constexpr int X_WORDS = KC * MT * kTileWords;
+  constexpr int STAGE = W_WORDS + S_WORDS + X_WORDS;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int wr = warp / WK, wk = warp % WK;
+  const int row_base = blockIdx.x * RC;
+  const int64_t bpr = (int64_t)p.k >> 1;
+  const int nchunks = (p.nb32 + KC - 1) / KC;
+  const int gsh = p.gshift;
+
+  auto issue = [&](int chunk, int stage) {
+    uint32_t* ws = sm + stage * STAGE;
+    float* ss = reinterpret_cast<float*>(ws + W_WORDS);
+    uint32_t* xs = ws + W_WORDS + S_WORDS;
+    const int b0 = chunk * KC;
+    for (int i = tid; i < NW * RC * KC; i += NT) {
+      const int q = i / (RC * KC), r = (i / KC) % RC, c = i % KC;
+      const int row = min(row_base + r, p.n - 1);
+      const int blk = min(b0 + c, p.nb32 - 1);
+      cp_async16(ws + (q * RC + r) * WROW + c * 4, p.w[q] + (int64_t)row * bpr + (int64_t)blk * 16);
+      // one scale per (row, block); blocks of one group repeat the value
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(ss + (q * RC + r) * SROW + c)),
+                   "l"(p.scales[q] + (int64_t)row * p.ng + (blk >> gsh))
+                   : "memory");
+    }
+    for (int i = tid; i < KC * MT * (kTileWords / 4); i += NT) {
+      const int piece = i % (kTileWords / 4), tile = i / (kTileWords / 4);
+      const int c = tile / MT, mt = tile % MT;
+      const int blk = min(b0 + c, p.nb32 - 1);
+      const int mtg = min(mt, p.mt_total - 1);
+      cp_async16(xs + (c * MT + mt) * kTileWords + piece * 4, p.xq + ((size_t)blk * p.mt_total + mtg) * kTileWords + piece * 4);
+    }
+    cp_async_commit();
+  };
+
+  float acc[NW][MT][4];
+#pragma unroll
+  for (int q = 0; q < NW; ++q)
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[q][nt][i] = 0.f;
+
+  pdl_wait();
+  issue(0, 0);
+  if (nchunks > 1) issue(1, 1);
+  for (int ch = 0; ch < nchunks; ++ch) {
+    if (ch + 2 < nchunks) {
+      issue(ch + 2, (ch + 2) % NS);
+      cp_async_wait<2>();
+    } else if (ch + 1 < nchunks) {
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t* ws = sm + (ch % NS) * STAGE;
+    const float* ss = reinterpret_cast<const float*>(ws + W_WORDS);
+    const uint32_t* xs = ws + W_WORDS + S_WORDS;
+#pragma unroll
+    for (int cc = 0; cc < KC / WK; ++cc) {
+      const int c = cc * WK + wk;          // this warp's blocks of the stage
+      const int blk = ch * KC + c;
+      if (blk < p.nb32) {
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          const uint32_t w0 = ws[(q * RC + wr * 16 + g) * WROW + c * 4 + t];
+          const uint32_t w1 = ws[(q * RC + wr * 16 + g + 8) * WROW + c * 4 + t];
+          const uint32_t a[4] = {w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu};
+          const float s0 = ss[(q * RC + wr * 16 + g) * SROW + c];
+          const float s1 = ss[(q * RC + wr * 16 + g + 8) * SROW + c];
+#pragma unroll
+          for (int nt = 0; nt < MT; ++nt) {
+            const uint32_t* tile = xs + (c * MT + nt) * kTileWords;
+            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
+            mma_u8u8(c0, a, tile[(0 * 4 + t) * 8 + g], tile[(3 * 4 + t) * 8 + g]);
+            mma_u8u8(c1, a, tile[(1 * 4 + t) * 8 + g], tile[(4 * 4 + t) * 8 + g]);
+            mma_u8s8(c2, a, tile[(2 * 4 + t) * 8 + g], tile[(5 * 4 + t) * 8 + g]);
+            const float2 sx = *reinterpret_cast<const float2*>(tile + 192 + 2 * t);
+            const float2 cr = *reinterpret_cast<const float2*>(tile + 200 + 2 * t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float f = fmaf(65536.0f, (float)c2[i], (float)(c0[i] + (c1[i] << 8)));
+              const float d = fmaf((i & 1) ? sx.y : sx.x, f, (i & 1) ? cr.y : cr.x);
+              acc[q][nt][i] = fmaf(d, (i & 2) ? s1 : s0, acc[q][nt][i]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  if (WK > 1) {
+    // the WK warps of a row tile cover disjoint blocks of K: sum them in shared memory
+    float* red = reinterpret_cast<float*>(sm);
+    constexpr int PER = NW * MT * 4;
+#pragma unroll
+    for (int q = 0; q < NW; ++q)
+#pragma unroll
+      for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[(warp * PER + (q * MT + nt) * 4 + i) * 32 + lane] = acc[q][nt][i];
+    __syncthreads();
+    if (wk != 0) return;
+#pragma unroll
+    for (int q = 0; q < NW; ++q)
+#pragma unroll
+      for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < WK; ++w) v += red[((wr * WK + w) * PER + (q * MT + nt) * 4 + i) * 32 + lane];
+          acc[q][nt][i] = v;
+        }
+  }
+  // accumulator i: row (g + 8 * (i >> 1)), activation row (tile * 8 + 2 * t + (i & 1))
+#pragma unroll
+  for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row_base + wr * 16 + g + 8 * (i >> 1);
+      const int m = nt * 8 + 2 * t + (i & 1);
+      if (row >= p.n || m >= p.m) continue;
+      float v;
+      if (EPI == 1) {
+        const float gg = acc[0][nt][i] + (p.bias[0] ? p.bias[0][row] : 0.f);
+        const float uu = acc[NW - 1][nt][i] + (p.bias[1] ? p.bias[1][row] : 0.f);
+        v = (gg / (1.0f + expf(-gg))) * uu;  // src/quantization/fused_ops.rs:1305-1311
+      } else {
+        v = acc[0][nt][i] + (p.bias[0] ? p.bias[0][row] : 0.f);
+        if (p.resid) v = p.resid[(int64_t)m * p.n + row] + v;
+      }
+      p.out[(int64_t)m * p.n + row] = v;
+    }
+}
+
+template <int MT, int WR, int WK, int EPI, int KC>
+tb_status launch_rows_cfg(const MmaParams& p, cudaStream_t stream) {
+  constexpr int NW = EPI == 1 ? 2 : 1;
+  constexpr int RC = 16 * WR;
+  constexpr size_t stage_words = (size_t)NW * RC * (KC * 4 + 4) + (((size_t)NW * RC * (KC + 1) + 3) & ~(size_t)3) + (size_t)KC * MT * kTileWords;
+  constexpr size_t red_words = WK > 1 ? (size_t)WR * WK * NW * MT * 4 * 32 : 0;
+  constexpr size_t smem = sizeof(uint32_t) * (3 * stage_words > red_words ? 3 * stage_words : red_words);
+  static_assert(smem <= 200 * 1024, "stage too large");
+  auto kern = w4_mma_rows_kernel<MT, WR, WK, EPI, KC>;
+  static thread_local bool configured[64] = {false};
+  int dev = 0;
+  TB_CUDA_TRY(cudaGetDevice(&dev));
+  if (smem > 32 * 1024 && (dev >= 64 || !configured[dev])) {
+    TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 64) configured[dev] = true;
+  }
+  kern<<<dim3((unsigned)((p.n + RC - 1) / RC)), 32 * WR * WK, smem, stream>>>(p);
+  TB_CUDA_TRY(cudaGetLastError());
+  return TB_OK;
+}
+
+template <int MT, int EPI, int KC>
+tb_status launch_rows_mt(const MmaParams& p, cudaStream_t stream) {
+  // rows per CTA so that the grid is about one CTA per SM or more; narrow matrices split K over warps
+  const int per_sm = p.n / sm_count();
+  if (per_sm >= 96) return launch_rows_cfg<MT, 6, 1, EPI, KC>(p, stream);
+  if (per_sm >= 40) return launch_rows_cfg<MT, 4, 2, EPI, KC>(p, stream);
+  return launch_rows_cfg<MT, 2, 4, EPI, KC>(p, stream);
+}
+
+template <int EPI>
+tb_status launch_rows_epi(const MmaParams& p, cudaStream_t stream) {
+  if (p.mt_total <= 1) return launch_rows_mt<1, EPI, 8>(p, stream);
+  if (p.mt_total <= 2) return launch_rows_mt<2, EPI, 8>(p, stream);
+  if (p.mt_total <= 4) return launch_rows_mt<4, EPI, 4>(p, stream);
+  return launch_rows_mt<8, EPI, 4>(p, stream);
+}
+
 template <int EPI>
 tb_status launch_mma_epi(const MmaParams& p, cudaStream_t stream) {
   // activation tiles of 8 rows: 1 -> (MT 1, WM 1), 2 -> (1, 2), 3..4 -> (2, 2), 5..8 -> (4, 2)
   if (p.mt_total <= 1) {
     // narrow matrices: 16 rows per CTA with the warps splitting K keeps >= 1 CTA per SM busy
-    if (p.n < 64 * 2 * sm_count()) return launch_mma_cfg<1, 1, EPI, 8, true>(p, stream);
+    static const int e_thr = getenv("TB_MMA_SPLITK_BELOW") ? atoi(getenv("TB_MMA_SPLITK_BELOW")) : 64 * 2 * sm_count();
+    if (p.n < e_thr) return launch_mma_cfg<1, 1, EPI, 8, true>(p, stream);
     return launch_mma_cfg<1, 1, EPI, 8, false>(p, stream);
   }
   if (p.mt_total <= 2) return launch_mma_cfg<1, 2, EPI, 8, false>(p, stream);
@@ -321,7 +520,9 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
     p.ng = (int)(a.k / a.g);
     p.mt_total = mt;
-    tb_status s = a.w2 ? launch_mma_epi<1>(p, stream) : launch_mma_epi<0>(p, stream);
+    static const int e_layout = getenv("TB_MMA_LAYOUT") ? atoi(getenv("TB_MMA_LAYOUT")) : 2;
+    tb_status s = e_layout == 2 ? (a.w2 ? launch_rows_epi<1>(p, stream) : launch_rows_epi<0>(p, stream))
+                                : (a.w2 ? launch_mma_epi<1>(p, stream) : launch_mma_epi<0>(p, stream));
     if (s != TB_OK) return s;
   }
   return TB_OK;
