@@ -56,7 +56,6 @@ struct AttnParams {
   int fixed_per;    // positions per CTA when forced, else 0: divide the current length evenly
   int nc;           // CTAs per (sequence, kv head) = gridDim.x
   int stages;       // ring depth
-  int pre_stages;   // stages requested before the consumers have asked for q (the rest follows their request)
   int region_floats;  // floats of the ring region (also holds the combine / merge buffers)
   int64_t max_seq_len;
   int per_call_tables;
@@ -297,7 +296,6 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
   __shared__ float s_wmax[kCW][kMaxGq], s_wsum[kCW][kMaxGq], s_ml[2][kMaxGq];
   __shared__ int s_abort;
   __shared__ int s_last;
-  __shared__ int s_qreq;
 
   const int gq = p.gq;
   float* q_s = smem;
@@ -311,7 +309,6 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
 
   if (tid == 0) {
     s_abort = 0;
-    s_qreq = 0;
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], kCW);
@@ -369,12 +366,6 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
             const int s = i % p.stages, round = i / p.stages;
             if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) { lost = true; break; }
             if (i == 0) tl_mark(p.tl, cta_lin, 6);
-            if (i == p.pre_stages) {
-              // The consumers' small loads of q must not queue behind the whole K/V stream:
-              // only the first stages go out ahead of them, the rest follows their request.
-              const long long w0 = clock64();
-              while (*reinterpret_cast<volatile int*>(&s_qreq) < kCW && clock64() - w0 < kWaitCycles) {}
-            }
             const int nr = min(kStageRows, crn - t * kStageRows);
             const uint32_t bytes = (uint32_t)nr * D * sizeof(float);
             mbar_expect_tx(&full[s], bytes);
@@ -395,8 +386,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
   if (active) {
     const float* cs = p.cos_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
     const float* sn = p.sin_t + (p.per_call_tables ? (int64_t)b * D : (int64_t)off * D);
-    // q heads of this kv head, rotated, into shared memory.  All loads are issued first; then the
-    // producer is told that it may go on (see pre_stages); then the arithmetic.
+    // q heads of this kv head, rotated, into shared memory.  All loads are issued first, then the
+    // arithmetic: with load and arithmetic interleaved per element the q vector was ready 2 us later.
     constexpr int QIT = kMaxGq * 128 / kCT;
     float xa[QIT], xb[QIT], ca[QIT], sa[QIT];
 #pragma unroll
@@ -411,8 +402,6 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
         sa[k] = sn[e];
       }
     }
-    __syncwarp();
-    if (lane == 0) atomicAdd(&s_qreq, 1);
 #pragma unroll
     for (int k = 0; k < QIT; ++k) {
       const int i = tid + k * kCT;
@@ -842,8 +831,6 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.qkv_rot_out = a.q_rot_out;
   p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.gq = gq;
   p.fixed_per = L.fixed_per; p.nc = L.nc; p.stages = L.stages;
-  static const int e_pre = getenv("TB_ATTN_PRE") ? atoi(getenv("TB_ATTN_PRE")) : 2;
-  p.pre_stages = e_pre;
   // two CTAs per SM when the ring can be cut to make room (wide heads with many q heads per kv head)
   int stages = L.stages;
   while (stages > 3 && 2 * (sizeof(float) * (attn_fixed_floats(D, gq, gqm) + attn_region_floats(D, gq, L.nc, stages)) + 2048) > 227 * 1024)

@@ -87,7 +87,8 @@ struct tb_decoder {
   bool use_graph = true;
   bool pdl = true;
   // Kernels launched with programmatic dependent launch (bit 0 qkv, 1 attention, 2 o_proj,
-  // 3 gate/up, 4 down, 5 lm_head).  Measured on B200: the attention kernel gains from starting
+  // 3 gate/up, 4 down, 5 lm_head; bit 6: every projection of a batched step - measured 3% (batch 8)
+  // to 9% (batch 32) slower than plain stream order, so off).  Measured on B200: the attention kernel gains from starting
   // its K/V tile copies early; the persistent GEMV kernels run slower when they are made
   // resident before their predecessor has finished, so they keep plain stream order.
   int pdl_mask = 2;
@@ -173,7 +174,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.norm_w = W.input_norm_w; a.eps = d->cfg.rms_norm_eps;
       a.x_normed_out = dbg ? d->dbg_normed : nullptr;
       if (sn && l > 0) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
-      a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 1);
+      a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && ((pm & 1) || (b > 1 && (pm & 64)));
       if (l == 0) add_kv(a.prefetch, 0);  // later layers: requested by the previous layer's gate/up
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
@@ -200,7 +201,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     {  // F + G
       GemvArgs a;
       a.x = d->attn; a.w = W.o_w; a.scales = W.o_s; a.m = b; a.n = d->H; a.k = d->q_dim_l; a.g = d->G;
-      a.pdl = pdl && !debug && (pm & 4);
+      a.pdl = pdl && !debug && ((pm & 4) || (b > 1 && (pm & 64)));
       add_mat(a.prefetch, W.down_w, W.down_s, d->H, d->I_l);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
@@ -216,7 +217,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x = d->x; a.w = W.gate_w; a.scales = W.gate_s; a.w2 = W.up_w; a.scales2 = W.up_s; a.out = d->h;
       a.norm_w = W.post_norm_w; a.eps = d->cfg.rms_norm_eps;
       if (sn) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
-      a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 8);
+      a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && ((pm & 8) || (b > 1 && (pm & 64)));
       if (l + 1 < d->L) {
         add_mat(a.prefetch, d->layers[l + 1].qkv_w, d->layers[l + 1].qkv_s, d->tq_l, d->H);
         add_kv(a.prefetch, l + 1);
@@ -233,7 +234,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     {  // I' + J
       GemvArgs a;
       a.x = d->h; a.w = W.down_w; a.scales = W.down_s; a.m = b; a.n = d->H; a.k = d->I_l; a.g = d->G;
-      a.pdl = pdl && !debug && (pm & 16);
+      a.pdl = pdl && !debug && ((pm & 16) || (b > 1 && (pm & 64)));
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
       if (sn) {
@@ -253,7 +254,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     a.x = d->x; a.w = d->lm_w; a.scales = d->lm_s;
     a.norm_w = d->final_norm_w; a.eps = d->cfg.rms_norm_eps;
     if (sn) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
-    a.m = b; a.n = d->V_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && (pm & 32);
+    a.m = b; a.n = d->V_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && ((pm & 32) || (b > 1 && (pm & 64)));
     a.out = d->tp == 1 ? d->logits : d->logits_l;
     a.xq_scratch = d->xq_scratch;
     TB_TRY(launch_w4_gemv(a, st));

@@ -23,6 +23,7 @@ namespace {
 constexpr int kTileWords = 208;  // per (block, 8 activation rows): 6 x 32 digit words + 8 sx + 8 corr
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------
 // x [M, K] fp32 -> xq [K/32][Mt][208] words, Mt = ceil(M/8).  Tile layout: word
@@ -35,6 +36,7 @@ __global__ void __launch_bounds__(128) quantize_x_kernel(const float* __restrict
                                                          int mt_total, float* __restrict__ x_normed_out) {
   __shared__ float s_part[4];
   pdl_wait();
+  pdl_launch_dependents();  // after the own wait: completion stays transitive along the chain
   const int m = blockIdx.x;
   const int nb32 = k >> 5;
   const int mt = m >> 3, g = m & 7;
@@ -115,6 +117,7 @@ struct MmaParams {
   const float* resid;
   float* out;
   int m, n, k, nb32, gshift, ng, mt_total;
+  int pdl;             // launched with programmatic stream serialization (the rows layout only)
 };
 
 // 4 warps = WR row groups (16 weight rows each) x WM groups of MT activation tiles (8 rows
@@ -311,10 +314,10 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
   const int nchunks = (p.nb32 + KC - 1) / KC;
   const int gsh = p.gshift;
 
-  auto issue = [&](int chunk, int stage) {
+  // weights and scales of a stage (static data: may be requested before the dependency wait)
+  auto issue_w = [&](int chunk, int stage) {
     uint32_t* ws = sm + stage * STAGE;
     float* ss = reinterpret_cast<float*>(ws + W_WORDS);
-    uint32_t* xs = ws + W_WORDS + S_WORDS;
     const int b0 = chunk * KC;
     for (int i = tid; i < NW * RC * KC; i += NT) {
       const int q = i / (RC * KC), r = (i / KC) % RC, c = i % KC;
@@ -326,6 +329,11 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
                    "l"(p.scales[q] + (int64_t)row * p.ng + (blk >> gsh))
                    : "memory");
     }
+  };
+  // digit tiles of a stage (written by the kernel ahead); closes the stage's copy group
+  auto issue_x = [&](int chunk, int stage) {
+    uint32_t* xs = sm + stage * STAGE + W_WORDS + S_WORDS;
+    const int b0 = chunk * KC;
     for (int i = tid; i < KC * MT * (kTileWords / 4); i += NT) {
       const int piece = i % (kTileWords / 4), tile = i / (kTileWords / 4);
       const int c = tile / MT, mt = tile % MT;
@@ -334,6 +342,10 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
       cp_async16(xs + (c * MT + mt) * kTileWords + piece * 4, p.xq + ((size_t)blk * p.mt_total + mtg) * kTileWords + piece * 4);
     }
     cp_async_commit();
+  };
+  auto issue = [&](int chunk, int stage) {
+    issue_w(chunk, stage);
+    issue_x(chunk, stage);
   };
 
   float acc[NW][MT][4];
@@ -344,9 +356,12 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[q][nt][i] = 0.f;
 
+  issue_w(0, 0);
+  if (nchunks > 1) issue_w(1, 1);
   pdl_wait();
-  issue(0, 0);
-  if (nchunks > 1) issue(1, 1);
+  pdl_launch_dependents();
+  issue_x(0, 0);
+  if (nchunks > 1) issue_x(1, 1);
   for (int ch = 0; ch < nchunks; ++ch) {
     if (ch + 2 < nchunks) {
       issue(ch + 2, (ch + 2) % NS);
@@ -455,8 +470,17 @@ tb_status launch_rows_cfg(const MmaParams& p, cudaStream_t stream) {
     TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 64) configured[dev] = true;
   }
-  kern<<<dim3((unsigned)((p.n + RC - 1) / RC)), 32 * WR * WK, smem, stream>>>(p);
-  TB_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((p.n + RC - 1) / RC));
+  cfg.blockDim = dim3(32 * WR * WK);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
   return TB_OK;
 }
 
@@ -506,9 +530,22 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
   for (int m0 = 0; m0 < a.m; m0 += 64) {
     const int mc = a.m - m0 < 64 ? a.m - m0 : 64;
     const int mt = (mc + 7) / 8;
-    quantize_x_kernel<<<dim3((unsigned)(mt * 8), (unsigned)((a.k / 32 + 127) / 128)), 128, 0, stream>>>(a.x + (int64_t)m0 * a.k, a.norm_w, a.eps, static_cast<uint32_t*>(scratch), mc,
-                                                  (int)a.k, mt, a.x_normed_out ? a.x_normed_out + (int64_t)m0 * a.k : nullptr);
-    TB_CUDA_TRY(cudaGetLastError());
+    static const int e_layout = getenv("TB_MMA_LAYOUT") ? atoi(getenv("TB_MMA_LAYOUT")) : 2;
+    const bool pdl = a.pdl && e_layout == 2;
+    {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)(mt * 8), (unsigned)((a.k / 32 + 127) / 128));
+      cfg.blockDim = dim3(128);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = pdl ? 1 : 0;
+      TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_x_kernel, a.x + (int64_t)m0 * a.k, a.norm_w, a.eps,
+                                     static_cast<uint32_t*>(scratch), mc, (int)a.k, mt,
+                                     a.x_normed_out ? a.x_normed_out + (int64_t)m0 * a.k : (float*)nullptr));
+    }
     MmaParams p;
     p.xq = static_cast<const uint32_t*>(scratch);
     p.w[0] = a.w; p.w[1] = a.w2;
@@ -520,7 +557,7 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
     p.ng = (int)(a.k / a.g);
     p.mt_total = mt;
-    static const int e_layout = getenv("TB_MMA_LAYOUT") ? atoi(getenv("TB_MMA_LAYOUT")) : 2;
+    p.pdl = pdl ? 1 : 0;
     tb_status s = e_layout == 2 ? (a.w2 ? launch_rows_epi<1>(p, stream) : launch_rows_epi<0>(p, stream))
                                 : (a.w2 ? launch_mma_epi<1>(p, stream) : launch_mma_epi<0>(p, stream));
     if (s != TB_OK) return s;

@@ -53,8 +53,6 @@ struct StreamParams {
   int rounds;        // ceil(n / 8): the unit of work distribution (8 rows)
   PrefetchList prefetch;
   unsigned long long* tl;  // timestamps of this launch or null
-  int x_copies;      // x is stored this many times, k floats apart; CTA c reads copy c % x_copies
-  int hold;          // stages the producer may request before the activations have arrived (-1: no limit)
   int trigger;       // where launch_dependents is signalled: 0 start, 1 after the last stage was requested, 2 end
 };
 
@@ -155,7 +153,6 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   __shared__ float s_ss[16];
   __shared__ int s_abort;
   __shared__ int s_waited;
-  __shared__ int s_xready;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nwarps = p.nwarps, groups = p.groups;
@@ -170,7 +167,6 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   if (tid == 0) {
     s_abort = 0;
     s_waited = 0;
-    s_xready = 0;
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], nwarps);
@@ -192,12 +188,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
       for (int i = 0; i < total_stages; ++i) {
         const int s = i % p.stages, round = i / p.stages;
         if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
-        if (i == p.hold) {
-          // keep the path to L2 clear until the consumers' loads of x have come back
-          const long long t0 = clock64();
-          while (*reinterpret_cast<volatile int*>(&s_xready) == 0 && clock64() - t0 < kWaitCycles) {}
-        }
-        if (i == 0 && p.hold != -2) tl_mark(p.tl, (int)blockIdx.x, 6);
+        if (i == 0) tl_mark(p.tl, (int)blockIdx.x, 6);
         if (i == total_stages - 1) tl_mark(p.tl, (int)blockIdx.x, 7);
         const int row0 = (round0 + i / SPR) * TR + (i % SPR) * RS;
         const int cnt = max(0, min(RS, p.n - row0));
@@ -252,7 +243,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
       for (int j = 0; j < EPL / 4; ++j) nwv[j] = __ldg(nw + j);
     }
     if (has_part) {
-      const float4* xg = reinterpret_cast<const float4*>(p.x + (size_t)(blockIdx.x % p.x_copies) * p.k) + part * (EPL / 4);
+      const float4* xg = reinterpret_cast<const float4*>(p.x) + part * (EPL / 4);
 #pragma unroll
       for (int j = 0; j < EPL / 4; ++j) {
         const float4 t = xg[j];
@@ -288,7 +279,6 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
       }
     }
     float amax = abs_max<EPL>(v);
-    if (p.hold == -2 && tid == 0 && amax >= 0.f) tl_mark(p.tl, (int)blockIdx.x, 6);
     if (EPL == 16) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // the block's other half
     quantize_part<EPL>(v, amax, dig, sx, corr);
     if (!has_part) { sx = 0.f; corr = 0.f; }
@@ -308,7 +298,6 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     inv_rms = 1.0f / sqrtf(ss / (float)p.k + p.eps);
   }
-  if (tid == 0) *reinterpret_cast<volatile int*>(&s_xready) = 1;
   if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 2);
   const int sidx = blk >> p.gshift;
   int buf = 0;
@@ -498,7 +487,7 @@ static int env_int(const char* name, int dflt) {
 
 tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   static const int e_trigger = env_int("TB_STREAM_TRIGGER", 1), e_cps = env_int("TB_STREAM_CPS", 0),
-                   e_ring = env_int("TB_STREAM_RING_KB", 0), e_epl = env_int("TB_STREAM_EPL", 0), e_hold = env_int("TB_STREAM_HOLD", -1), e_xc = env_int("TB_STREAM_XCOPIES", 1);
+                   e_ring = env_int("TB_STREAM_RING_KB", 0), e_epl = env_int("TB_STREAM_EPL", 0);
   StreamParams p;
   p.x = a.x;
   p.w[0] = a.w; p.w[1] = a.w2;
@@ -512,8 +501,6 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   // Dependents may start once this CTA's last HBM request is out (measured: start, that point and
   // the end of the kernel differ by < 1% on the decode step; the early start helps small kernels).
   p.trigger = e_trigger;
-  p.hold = e_hold;
-  p.x_copies = e_xc > 0 ? e_xc : 1;
   p.n = (int)a.n; p.k = (int)a.k; p.nb32 = (int)(a.k / 32);
   p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
   p.ng = (int)(a.k / a.g);
