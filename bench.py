@@ -323,6 +323,31 @@ def time_dominant_kernel(torch, tb, c, layers, device, tp):
     return alg, sec, len(layers)
 
 
+def time_c2_gemm(torch, tb, c, layers, device):
+    """BASELINE config 2: the batched grouped INT4 product at the Llama-3-8B MLP shapes,
+    M in {1, 4, 16, 64}; (K=4096, N=14336) runs over the layers' distinct gate matrices and
+    (K=14336, N=4096) over their down matrices (1.17 GB each, far above L2)."""
+    H, I, G = c["hidden_size"], c["intermediate_size"], c["group_size"]
+    L = tb.lib()
+    out = []
+    for name, n, k, wi, si in (("gate/up shape K=4096 N=14336", I, H, 6, 7), ("down shape K=14336 N=4096", H, I, 10, 11)):
+        for m in (1, 4, 16, 64):
+            x = torch.randn(m, k, device=device)
+            y = torch.empty(m, n, device=device)
+
+            def one_pass():
+                st = torch.cuda.current_stream(device).cuda_stream
+                for lw in layers:
+                    rc = L.tb_gemm_w4a32_grouped(x.data_ptr(), lw[wi].data_ptr(), lw[si].data_ptr(), None, y.data_ptr(), m, n, k, G, st)
+                    assert rc == 0, tb.last_error()
+
+            sec = _graph_time(torch, device, one_pass, len(layers), passes=5)
+            alg = weight_bytes(n, k, G) + m * k * 4 + m * n * 4
+            out.append({"shape": name, "m": m, "us_per_launch": sec * 1e6, "achieved_gbs": alg / sec / 1e9,
+                        "tflops": 2.0 * m * n * k / sec / 1e12, "launches_per_call": 1 if m == 1 else 2})
+    return out
+
+
 def time_c1_gemv(torch, tb, device, copies=64):
     """BASELINE config 1: a single 4096x4096 group-32 GEMV, rotating over `copies` distinct
     weight copies (672 MB, > 5x L2) so every launch streams from HBM."""
@@ -487,6 +512,7 @@ def run_gpu(args):
                          "achieved_gbs": c1_alg / c1_sec / 1e9, "frac_of_measured": c1_alg / c1_sec / 1e9 / peak,
                          "frac_of_nominal_8TBs": c1_alg / c1_sec / 1e9 / NOMINAL_HBM_GBS,
                          "note": "64 rotating weight copies (672 MB), one CUDA graph of 64 launches replayed"},
+        "gemm_config2": (time_c2_gemm(torch, tb, c, layers, device) if tp == 1 else None),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 16 * B, "d2h_bytes_per_step": 4 * B * c["vocab_size"],
                 "ms_per_step": e2e_ms / K, "wall_ms_per_step": wall_ms / K},
         "gpu_launches": (dec.launches_per_step() + 1) * K,
