@@ -57,6 +57,7 @@ struct AttnParams {
   int fixed_per;    // positions per CTA when forced, else 0: divide the current length evenly
   int nc;           // CTAs per (sequence, kv head) = gridDim.x
   int stages;       // ring depth
+  int max_parts;    // upper bound of CTAs of a (sequence, kv head) that take positions
   int cluster;      // CTAs of a (sequence, kv head) form one thread-block cluster and merge through shared memory
   int region_floats;  // floats of the ring region (also holds the combine / merge buffers)
   int64_t max_seq_len;
@@ -339,7 +340,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams 
   const int t_end = seq_ok ? min(off + 1, kSeqCap) : 0;  // attend to [0, t_end)
   int per = p.fixed_per;
   if (per <= 0) {
-    per = (t_end + p.nc - 1) / p.nc;
+    const int parts = min(p.nc, p.max_parts);  // more partials than this cost more in the merge than they save
+    per = (t_end + parts - 1) / parts;
     per = max(kStageRows, (per + kStageRows - 1) & ~(kStageRows - 1));
   }
   const int nvalid = (t_end + per - 1) / per;   // CTAs of this grid row that have positions
@@ -929,6 +931,8 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.qkv_rot_out = a.q_rot_out;
   p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.gq = gq;
   p.fixed_per = L.fixed_per; p.nc = L.nc; p.stages = L.stages;
+  static const int e_max_parts = getenv("TB_ATTN_MAX_PARTS") ? atoi(getenv("TB_ATTN_MAX_PARTS")) : 48;
+  p.max_parts = max(1, e_max_parts);
   // two CTAs per SM when the ring can be cut to make room (wide heads with many q heads per kv head)
   int stages = L.stages;
   while (stages > 3 && 2 * (sizeof(float) * (attn_fixed_floats(D, gq, gqm) + attn_region_floats(D, gq, L.nc, stages)) + 2048) > 227 * 1024)
