@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _rank_main(rank, world, port, q, nccl_only):
+def _rank_main(rank, world, port, q, nccl_only, wide=False):
     sys.path.insert(0, HERE)
     sys.path.insert(0, os.path.dirname(HERE))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -31,6 +31,11 @@ def _rank_main(rank, world, port, q, nccl_only):
 
         cfg = dict(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_layers=3, num_heads=8,
                    num_kv_heads=4, head_dim=64, group_size=32, max_seq_len=64, rms_norm_eps=1e-6, rope_theta=5e5)
+        if wide:
+            # hidden 2048: the projections that consume the residual stream take the persistent kernel and the
+            # low-latency exchange also writes their pre-weighted input and its sums of squares (split RMSNorm)
+            cfg.update(vocab_size=512, hidden_size=2048, intermediate_size=4096, num_layers=2, num_heads=16,
+                       num_kv_heads=4, head_dim=128, tied=False)
         embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 3, o.quantize_int4_grouped, qkv_bias=True)
         layers_r, lw_r, ls_r = shard_model(tb, cfg, layers, lm_w, lm_s, rank, world)
         order = ["input_norm_w", "qkv_w", "qkv_s", "o_w", "o_s", "post_norm_w", "gate_w", "gate_s", "up_w", "up_s",
@@ -44,7 +49,7 @@ def _rank_main(rank, world, port, q, nccl_only):
         init_tensor_parallel(dec, dist, torch.device("cuda", rank), fused=not nccl_only)
         ref = o.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
         worst = 0.0
-        toks = [3, 500, 17, 17, 255, 9, 1000, 1]
+        toks = [3, 500, 17, 17, 255, 9, 1000 % cfg["vocab_size"], 1]
         for off, tok in enumerate(toks):
             worst = max(worst, max_rel_err(dec.step(tok, off), ref.step(tok, off)))
         # batched step: three sequences at once against three oracles
@@ -62,8 +67,8 @@ def _rank_main(rank, world, port, q, nccl_only):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("nccl_only", [False, True])
-def test_tp2_decoder_matches_oracle(nccl_only):
+@pytest.mark.parametrize("nccl_only,wide", [(False, False), (True, False), (False, True)])
+def test_tp2_decoder_matches_oracle(nccl_only, wide):
     import torch
 
     if not torch.cuda.is_available():
@@ -74,8 +79,8 @@ def test_tp2_decoder_matches_oracle(nccl_only):
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29900 + (os.getpid() % 90) + (50 if nccl_only else 0)
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, nccl_only)) for r in range(2)]
+    port = 29900 + (os.getpid() % 40) + (50 if nccl_only else 0) + (100 if wide else 0)
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, nccl_only, wide)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in procs]

@@ -150,7 +150,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
   };
   TB_TRY(snap(d->dbg_embed, d->x, d->H));
   // L2 prefetch chain (see PrefetchList): each kernel requests what the kernels after it read.
-  const bool sn = d->split_norm && b == 1 && !debug;
+  const bool sn = d->split_norm && b == 1 && !debug && (d->tp == 1 || tp_low_latency(d->tpst, b, d->H));
   const bool pfc = d->prefetch_chain && !debug;
   const size_t wq = (size_t)(d->H / 2), sq = sizeof(float) * (size_t)(d->H / d->G);
   auto add_mat = [&](PrefetchList& pf, const uint8_t* w, const float* sc, int64_t n, int64_t k) {
@@ -205,11 +205,14 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       add_mat(a.prefetch, W.down_w, W.down_s, d->H, d->I_l);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
-      if (sn) { a.out_scaled = d->xn; a.out_scale_w = W.post_norm_w; a.out_ss8 = d->ss8; }
+      if (sn && d->tp == 1) { a.out_scaled = d->xn; a.out_scale_w = W.post_norm_w; a.out_ss8 = d->ss8; }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
-      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches)); }
+      if (d->tp > 1) {
+        TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches, sn ? W.post_norm_w : nullptr,
+                                     sn ? d->xn : nullptr, sn ? d->ss8 : nullptr));
+      }
     }
     if (dbg) TB_TRY(snap(d->dbg_x_attn, d->x, d->H));
     {  // H + I: RMSNorm fused into the gate/up projection with the SwiGLU epilogue
@@ -237,14 +240,15 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.pdl = pdl && !debug && ((pm & 16) || (b > 1 && (pm & 64)));
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
-      if (sn) {
-        a.out_scaled = d->xn; a.out_ss8 = d->ss8;
-        a.out_scale_w = l + 1 < d->L ? d->layers[l + 1].input_norm_w : d->final_norm_w;
-      }
+      const float* next_norm_w = l + 1 < d->L ? d->layers[l + 1].input_norm_w : d->final_norm_w;
+      if (sn && d->tp == 1) { a.out_scaled = d->xn; a.out_ss8 = d->ss8; a.out_scale_w = next_norm_w; }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
-      if (d->tp > 1) { TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches)); }
+      if (d->tp > 1) {
+        TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches, sn ? next_norm_w : nullptr,
+                                     sn ? d->xn : nullptr, sn ? d->ss8 : nullptr));
+      }
     }
     if (dbg) TB_TRY(snap(d->dbg_x_out, d->x, d->H));
   }
@@ -389,7 +393,9 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   {
     // Split RMSNorm needs the persistent M = 1 kernel for every projection of a layer.
     auto ok_k = [&](int64_t k) { return k % 32 == 0 && k >= 2048 && k <= 15360 && ((k / d->G) * 4) % 16 == 0; };
-    d->split_norm = tp == 1 && ok_k(d->H) && ok_k(d->q_dim_l) && ok_k(d->I_l);
+    // one GPU: producers are the O / down kernels (all three K must qualify); tensor parallel: the
+    // producer is the low-latency exchange kernel, only the consumers (K = H) must qualify
+    d->split_norm = tp == 1 ? (ok_k(d->H) && ok_k(d->q_dim_l) && ok_k(d->I_l)) : ok_k(d->H);
     if (const char* snv = getenv("TB_SPLIT_NORM")) d->split_norm = d->split_norm && atoi(snv) != 0;
   }
   cudaGetDevice(&d->device);

@@ -84,6 +84,7 @@ NcclApi* nccl() {
   } while (0)
 
 constexpr int kMaxRanks = 8;
+constexpr int kLLLines = 8192;     // float2 lines per rank in the low-latency receive area (16384 floats)
 constexpr long long kPeerWaitCycles = 20000000000ll;  // ~10 s: ranks may be apart by a graph instantiation
 
 struct PeerArgs {
@@ -159,6 +160,96 @@ __global__ void __launch_bounds__(1024) peer_allreduce_residual_kernel(const Pee
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Low-latency form for small exchanges (one decode step of a few sequences): every 16-byte line
+// that crosses NVLink carries two floats and, twice, the number of the exchange.  A rank pushes
+// its partial into a receive area in every peer's memory (posted stores, one way) and then polls
+// its own receive area line by line until both copies of the number have arrived - no fence, no
+// separate flag, no read across the link.  A line is written with one 16-byte store; should the
+// two halves become visible apart, the second copy of the number is still missing and the poll
+// goes on.  Sums are taken in rank order on every rank (bit-identical x everywhere).  Optionally
+// also writes x times the next norm's weights and the sums of squares of x per 8 elements (the
+// split RMSNorm of the decoder).  One CTA; the exchange number lives in device memory so that
+// the launch can be replayed from a CUDA graph.
+// ------------------------------------------------------------------------------------------
+struct LLArgs {
+  const float* partial;             // this rank's partial, [count] floats (local)
+  uint4* my_recv;                   // [size][lines_cap] lines written by the peers
+  uint4* peer_recv[kMaxRanks];      // the same area in every peer's memory
+  uint32_t* epoch;
+  int* err;
+  float* x;
+  const float* scale_w;             // optional: next norm's weights [count]
+  float* out_scaled;                // optional: x * scale_w
+  float* out_ss8;                   // optional: sums of x^2 over 8 consecutive elements
+  int rank, size;
+  int lines, lines_cap;             // float2 lines in use / per rank in the receive area
+};
+
+__global__ void __launch_bounds__(1024) ll_allreduce_residual_kernel(const LLArgs a) {
+  const uint32_t want = *a.epoch + 1;
+  const float2* mine = reinterpret_cast<const float2*>(a.partial);
+  for (int i = threadIdx.x; i < a.lines; i += blockDim.x) {
+    const float2 v = mine[i];
+    const uint4 line = make_uint4(__float_as_uint(v.x), want, __float_as_uint(v.y), want);
+    for (int r = 0; r < a.size; ++r) {
+      if (r == a.rank) continue;
+      uint4* dst = a.peer_recv[r] + (size_t)a.rank * a.lines_cap + i;
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(line.x), "r"(line.y), "r"(line.z), "r"(line.w) : "memory");
+    }
+  }
+  bool ok = true;
+  const long long t0 = clock64();
+  const int rounds = (a.lines + (int)blockDim.x - 1) / (int)blockDim.x;
+  for (int k = 0; k < rounds; ++k) {
+    const int i = k * blockDim.x + threadIdx.x;
+    const bool live = i < a.lines;
+    float2 s = make_float2(0.f, 0.f);
+    if (live) {
+      for (int r = 0; r < a.size; ++r) {
+        float2 v;
+        if (r == a.rank) {
+          v = mine[i];
+        } else {
+          const uint4* src = a.my_recv + (size_t)r * a.lines_cap + i;
+          uint4 line;
+          for (uint32_t spin = 0;; ++spin) {
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(line.x), "=r"(line.y), "=r"(line.z), "=r"(line.w) : "l"(src) : "memory");
+            if (line.y == want && line.w == want) break;
+            if (!ok || ((spin & 1023) == 1023 && clock64() - t0 > kPeerWaitCycles)) {  // the peer never arrived
+              if (ok) atomicExch(a.err, 1);
+              ok = false;
+              break;
+            }
+          }
+          v = make_float2(__uint_as_float(line.x), __uint_as_float(line.z));
+        }
+        s.x += v.x;
+        s.y += v.y;
+      }
+    }
+    float2 xv = make_float2(0.f, 0.f);
+    if (live) {
+      xv = reinterpret_cast<float2*>(a.x)[i];
+      xv.x += s.x;
+      xv.y += s.y;
+      reinterpret_cast<float2*>(a.x)[i] = xv;
+      if (a.out_scaled != nullptr) {
+        const float2 w = reinterpret_cast<const float2*>(a.scale_w)[i];
+        reinterpret_cast<float2*>(a.out_scaled)[i] = make_float2(xv.x * w.x, xv.y * w.y);
+      }
+    }
+    if (a.out_ss8 != nullptr) {  // 8 consecutive elements = 4 consecutive lanes
+      float sq = xv.x * xv.x + xv.y * xv.y;
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      if (live && (threadIdx.x & 3) == 0) a.out_ss8[i >> 2] = sq;
+    }
+  }
+  __syncthreads();  // every thread has read the exchange number
+  if (threadIdx.x == 0) *a.epoch = want;
+}
+
 __global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ y, int n4) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n4) {
@@ -181,6 +272,8 @@ struct TpState {
   char* peer_block[kMaxRanks] = {};
   size_t flags_off = 0;
   int calls = 0;              // host-side call parity selects the buffer a projection writes to
+  size_t ll_off = 0;          // low-latency receive area: [2][size][kLLLines] lines of 16 bytes
+  int ll_calls = 0;
   float* reduced = nullptr;   // NCCL path: the summed partial
 };
 
@@ -189,11 +282,44 @@ float* tp_partial_buffer(TpState* st, float* fallback) {
   return reinterpret_cast<float*>(st->block) + (size_t)(st->calls & 1) * st->max_count;
 }
 
+bool tp_low_latency(const TpState* st, int batch, int64_t hidden) {
+  static const int e_ll = getenv("TB_TP_LL") ? atoi(getenv("TB_TP_LL")) : 1;
+  const size_t count = (size_t)batch * hidden;
+  return st && st->fused && e_ll != 0 && (count & 7) == 0 && count / 2 <= (size_t)kLLLines;
+}
+
 tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int batch, int64_t hidden,
-                                cudaStream_t stream, int* launches) {
+                                cudaStream_t stream, int* launches, const float* scale_w, float* out_scaled,
+                                float* out_ss8) {
   if (!st || !st->comm) return fail(TB_ERR_NCCL, "tensor-parallel decoder used before tb_decoder_tp_init");
   const size_t count = (size_t)batch * hidden;
   if (count > st->max_count || (count & 3)) return fail(TB_ERR_SHAPE, "tp all-reduce: %zu elements", count);
+  if ((out_scaled || out_ss8) && !tp_low_latency(st, batch, hidden))
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: the split RMSNorm outputs need the low-latency exchange");
+  if (tp_low_latency(st, batch, hidden)) {
+    if (partial != reinterpret_cast<const float*>(st->block) + (size_t)(st->calls & 1) * st->max_count)
+      return fail(TB_ERR_ARG, "tp all-reduce: the partial must be written to tp_partial_buffer()");
+    st->calls++;
+    const int slot = st->ll_calls & 1;
+    st->ll_calls++;
+    LLArgs a;
+    a.partial = partial;
+    const size_t slot_lines = (size_t)slot * st->size * kLLLines;
+    for (int r = 0; r < st->size; ++r)
+      a.peer_recv[r] = reinterpret_cast<uint4*>(st->peer_block[r] + st->ll_off) + slot_lines;
+    a.my_recv = reinterpret_cast<uint4*>(st->block + st->ll_off) + slot_lines;
+    uint32_t* words = reinterpret_cast<uint32_t*>(st->block + st->flags_off);
+    a.epoch = words + 20;
+    a.err = reinterpret_cast<int*>(words + 18);
+    a.x = x;
+    a.scale_w = scale_w; a.out_scaled = out_scaled; a.out_ss8 = out_ss8;
+    a.rank = st->rank; a.size = st->size;
+    a.lines = (int)(count / 2); a.lines_cap = kLLLines;
+    ll_allreduce_residual_kernel<<<1, 1024, 0, stream>>>(a);
+    TB_CUDA_TRY(cudaGetLastError());
+    if (launches) ++*launches;
+    return TB_OK;
+  }
   if (st->fused) {
     const int slot = st->calls & 1;
     st->calls++;
@@ -281,7 +407,8 @@ tb_status tp_create(TpState** out, int rank, int size, const uint8_t id[128], si
   if (e != cudaSuccess) return bail(fail(TB_ERR_OOM, "tp: %s", cudaGetErrorString(e)));
   if (allgather && !nccl_only) {
     st->flags_off = 2 * st->max_count * sizeof(float);
-    const size_t bytes = st->flags_off + 256;
+    st->ll_off = st->flags_off + 256;
+    const size_t bytes = st->ll_off + (size_t)2 * size * kLLLines * sizeof(uint4);
     e = cudaMalloc(&st->block, bytes);
     if (e != cudaSuccess) return bail(fail(TB_ERR_OOM, "tp: %s", cudaGetErrorString(e)));
     cudaMemset(st->block, 0, bytes);

@@ -7,8 +7,13 @@ namespace tb {
 struct TpState;
 
 // x[b, :] += sum over ranks of partial[b, :]   (after a row-parallel projection)
+// With scale_w / out_scaled / out_ss8 (low-latency exchange only, see tp_low_latency) the kernel also
+// writes x * scale_w and the sums of squares of x per 8 elements: the split RMSNorm of the decoder.
 tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int batch, int64_t hidden,
-                                cudaStream_t stream, int* launches);
+                                cudaStream_t stream, int* launches, const float* scale_w = nullptr,
+                                float* out_scaled = nullptr, float* out_ss8 = nullptr);
+// True when an exchange of this size takes the low-latency form (small, peer memory available).
+bool tp_low_latency(const TpState* st, int batch, int64_t hidden);
 // logits[b, r*V_l : (r+1)*V_l] = rank r's logits_l[b, :]
 tb_status tp_allgather_logits(TpState* st, const float* logits_l, float* logits, int batch,
                               int64_t v_local, cudaStream_t stream, int* launches);
