@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
 
-N=1 workload: BASELINE config "Llama-3-8B-architecture INT4 decode" - hidden 4096,
+N=1 workload: the headline configuration "Llama-3-8B-architecture INT4 decode" - hidden 4096,
 32 layers, 32 q / 8 kv heads, head_dim 128, intermediate 14336, vocab 128256,
 group 32, random init (std 0.02), fp32 KV cache pre-filled to a context of 4096,
 batch 1.  For N>1 (launched by torchrun, one rank per GPU) the same model is sharded
@@ -324,7 +324,7 @@ def time_dominant_kernel(torch, tb, c, layers, device, tp):
 
 
 def time_c2_gemm(torch, tb, c, layers, device):
-    """BASELINE config 2: the batched grouped INT4 product at the Llama-3-8B MLP shapes,
+    """workload configuration 2: the batched grouped INT4 product at the Llama-3-8B MLP shapes,
     M in {1, 4, 16, 64}; (K=4096, N=14336) runs over the layers' distinct gate matrices and
     (K=14336, N=4096) over their down matrices (1.17 GB each, far above L2)."""
     H, I, G = c["hidden_size"], c["intermediate_size"], c["group_size"]
@@ -349,7 +349,7 @@ def time_c2_gemm(torch, tb, c, layers, device):
 
 
 def time_c1_gemv(torch, tb, device, copies=64):
-    """BASELINE config 1: a single 4096x4096 group-32 GEMV, rotating over `copies` distinct
+    """workload configuration 1: a single 4096x4096 group-32 GEMV, rotating over `copies` distinct
     weight copies (672 MB, > 5x L2) so every launch streams from HBM."""
     n = k = 4096
     g = 32
@@ -391,7 +391,7 @@ def run_gpu(args):
 
     global CONTEXT
     c = dict(LLAMA8B)
-    if args.model == "qwen05b":  # BASELINE config 3 (single GPU, context 1024); not the headline workload
+    if args.model == "qwen05b":  # workload configuration 3 (single GPU, context 1024); not the headline workload
         c, CONTEXT = dict(QWEN05B), 1024
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     max_seq = CONTEXT + 64 * ((K + W + 63) // 64) + 64
@@ -538,7 +538,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--model", default="llama8b", choices=["llama8b", "qwen05b"], help="qwen05b: BASELINE config 3, use with --quick")
+    ap.add_argument("--model", default="llama8b", choices=["llama8b", "qwen05b"], help="qwen05b: workload configuration 3, use with --quick")
     ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: plain ncclAllReduce instead of the fused kernel")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between kernels (A/B of programmatic dependent launch)")

@@ -175,7 +175,9 @@ def v2_cases(quant):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/torchburn")
+    ref_root = sys.argv[1]
     quant, config, model = load_reference(ref_root)
     np.savez_compressed(os.path.join(HERE, "quantizer_golden.npz"), **quantizer_cases(quant))
     np.savez_compressed(os.path.join(HERE, "layout_v2_golden.npz"), **v2_cases(quant))

@@ -143,7 +143,7 @@ def test_linear_int4_rs_known_answer(torch, tb, oracle):
 
 
 def test_linear_config2_shapes_and_linearity(torch, tb, oracle):
-    # BASELINE config 2 (Llama-3-8B MLP shapes).  M=1 and 4 against the oracle on the first
+    # workload configuration 2 (Llama-3-8B MLP shapes).  M=1 and 4 against the oracle on the first
     # 2048 rows; the full sizes through linearity: W(a*x1 + x2) = a*W x1 + W x2.
     rng = np.random.default_rng(2)
     for (k, n) in [(4096, 14336), (14336, 4096)]:
@@ -513,7 +513,7 @@ def test_decoder_batch_matches_single_sequences(torch, tb, oracle):
 
 
 def test_decoder_qwen05b_config3_full_width(torch, tb, oracle):
-    # BASELINE config 3: Qwen2.5-0.5B architecture at full size (24 layers, vocab 151936, tied
+    # workload configuration 3: Qwen2.5-0.5B architecture at full size (24 layers, vocab 151936, tied
     # lm_head = quantized copy of the embedding, qkv bias), int4 group 32, random init std 0.02.
     # The KV cache is produced by sequential steps from random token ids like prefill_tokens;
     # 1024 oracle steps would take minutes on a small host, so the oracle runs the first 96
