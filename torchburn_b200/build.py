@@ -70,9 +70,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
                     print(out)
     if jobs or force or not os.path.exists(LIB):
         # -fvisibility=hidden + explicit export of the extern "C" API keeps the symbol table to the ABI
-        link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs,
+        tmp = LIB + ".tmp"
+        link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp, *objs,
                 "-Xlinker", "--no-undefined", "-ldl", "-lpthread"]
         run(link)
+        os.replace(tmp, LIB)  # atomic: a reader never sees a half-written library
     return LIB
 
 
