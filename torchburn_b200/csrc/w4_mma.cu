@@ -488,8 +488,15 @@ template <int MT, int EPI, int KC>
 tb_status launch_rows_mt(const MmaParams& p, cudaStream_t stream) {
   // rows per CTA so that the grid is about one CTA per SM or more; narrow matrices split K over warps
   const int per_sm = p.n / sm_count();
-  if (per_sm >= 96) return launch_rows_cfg<MT, 6, 1, EPI, KC>(p, stream);
-  if (per_sm >= 40) return launch_rows_cfg<MT, 4, 2, EPI, KC>(p, stream);
+  static const int e_shape = getenv("TB_MMA_ROWS_SHAPE") ? atoi(getenv("TB_MMA_ROWS_SHAPE")) : 0;  // 24, 22: force WR WK
+  if (e_shape == 24) return launch_rows_cfg<MT, 2, 4, EPI, KC>(p, stream);
+  if (e_shape == 22) return launch_rows_cfg<MT, 2, 2, EPI, KC>(p, stream);
+  // Few activation tiles: the digits are small, so many small CTAs (32 rows, 3-4 resident per SM) keep more
+  // warps in flight than one CTA of 96 rows per SM; many tiles: the digit traffic decides, large CTAs.
+  // Measured on the Llama-3-8B shapes (tokens/s of the whole step, 32 rows per CTA in every case):
+  // batch 8 / 16: 4 warps, K split in two, 1466 / 1840 against 965 / 1254 with 96-row CTAs; batch 32: 8 warps,
+  // K split in four, 1980 against 1919; batch 64: 4 warps, 2166 against 1952.
+  if (MT != 4 && per_sm >= 64) return launch_rows_cfg<MT, 2, 2, EPI, KC>(p, stream);
   return launch_rows_cfg<MT, 2, 4, EPI, KC>(p, stream);
 }
 
