@@ -700,11 +700,14 @@ tb_status tb_decoder_generate_greedy(tb_decoder* d, int64_t first_token, int64_t
   if (!out_tokens || n_new < 0 || start_offset < 0) return fail(TB_ERR_ARG, "tb_decoder_generate_greedy: bad arguments");
   if (start_offset + n_new > d->S) return fail(TB_ERR_ARG, "generate exceeds max_seq_len");
   if (n_new > d->hist_cap) {
+    // First use: room for the longest possible run (max_seq_len tokens), so that the graphs, which
+    // hold this pointer, are never rebuilt in the middle of a generation.
     cudaFree(d->d_hist);
     d->d_hist = nullptr;
     d->hist_cap = 0;
-    TB_TRY(dalloc(&d->d_hist, (size_t)n_new));
-    d->hist_cap = n_new;
+    const int64_t cap = n_new > d->S ? n_new : d->S;
+    TB_TRY(dalloc(&d->d_hist, (size_t)cap));
+    d->hist_cap = cap;
     // the graph holds the history pointer: rebuild
     for (int i = 0; i <= kMaxBatch; ++i)
       if (d->graphs_greedy[i]) { cudaGraphExecDestroy(d->graphs_greedy[i]); d->graphs_greedy[i] = nullptr; }
