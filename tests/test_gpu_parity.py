@@ -268,6 +268,10 @@ def _attn_case(rng, nh, nkv, hd, max_seq, batch):
     (14, 2, 64, 1024, [1023], 0), (14, 2, 64, 1024, [0], 0), (32, 8, 128, 4096, [4095], 0),
     (32, 8, 128, 4096, [31, 32, 33, 2000], 0), (8, 8, 32, 96, [95], 64), (8, 1, 128, 300, [257], 64),
     (4, 2, 64, 512, [100, 511, 0], 256), (16, 2, 128, 1500, [1499, 63, 64], 512), (64, 8, 128, 600, [599], 128),
+    # 20 sequences x 8 kv heads exceed the SM count: one CTA per (sequence, kv head) walks the whole sequence in
+    # chunks of 512 positions with the running max / sum / weighted V rescaled in between (offsets around the
+    # chunk boundaries)
+    (16, 8, 64, 2048, [2047, 1500, 513, 512, 511, 1024, 1023, 1025, 0, 31, 32, 1535, 1536, 1537, 2046, 700, 1, 600, 1900, 2047], 0),
 ])
 def test_attention_decode_matches_oracle(torch, tb, oracle, nh, nkv, hd, max_seq, offsets, chunk):
     rng = np.random.default_rng(nh * 100 + hd + max_seq)

@@ -283,8 +283,11 @@ __device__ __forceinline__ void weigh_rows(const float* __restrict__ vb, int nr,
 // maximum and the exponentials of the chunk (a two-pass softmax inside the chunk; the running
 // max / sum / weighted V are rescaled only between chunks), and the V stages are weighted as
 // they land.  No softmax dependency sits inside either streaming loop.
+#ifndef TB_ATTN_MIN_CTAS
+#define TB_ATTN_MIN_CTAS 1
+#endif
 template <int D, int GQM>
-__global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kThreads, TB_ATTN_MIN_CTAS) attn_decode_kernel(const AttnParams p) {
   constexpr int F4 = D / 32;
   constexpr int CPR = D / 4;
   constexpr bool QREG = GQM * F4 <= 16 && kCW == 4;
