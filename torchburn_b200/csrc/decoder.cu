@@ -480,6 +480,7 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
     int64_t kmax = d->H > d->I_l ? d->H : d->I_l;
     if (d->q_dim_l > kmax) kmax = d->q_dim_l;
     CRC(cudaMalloc(&d->xq_scratch, w4_mma_scratch_bytes(B, kmax)));
+    CRC(cudaMemset(d->xq_scratch, 0, 4096));  // the tickets of the K split start at zero
   }
   CRC(cudaMalloc(&d->argmax_scratch, 16 * kMaxBatch));
   CRC(cudaMemset(d->argmax_scratch, 0, 16 * kMaxBatch));

@@ -477,6 +477,7 @@ tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
     if (a.xq_scratch) return launch_w4_mma(a, a.xq_scratch, stream);
     void* tmp = nullptr;
     TB_CUDA_TRY(cudaMallocAsync(&tmp, w4_mma_scratch_bytes(a.m < 64 ? a.m : 64, a.k), stream));
+    TB_CUDA_TRY(cudaMemsetAsync(tmp, 0, 4096, stream));  // the tickets of the K split
     const tb_status s = launch_w4_mma(a, tmp, stream);
     cudaFreeAsync(tmp, stream);
     return s;

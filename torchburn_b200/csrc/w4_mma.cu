@@ -118,6 +118,9 @@ struct MmaParams {
   float* out;
   int m, n, k, nb32, gshift, ng, mt_total;
   int pdl;             // launched with programmatic stream serialization (the rows layout only)
+  int ksplit;          // CTAs that share a row tile and split K (1 = none)
+  float* ksplit_part;  // gridDim.y > 1: partial sums [y][x][row tile][activation tile][4][32]
+  int* ksplit_cnt;     // gridDim.y > 1: one ticket per blockIdx.x, zero before the first launch, left zero
 };
 
 // 4 warps = WR row groups (16 weight rows each) x WM groups of MT activation tiles (8 rows
@@ -311,14 +314,18 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
   const int wr = warp / WK, wk = warp % WK;
   const int row_base = blockIdx.x * RC;
   const int64_t bpr = (int64_t)p.k >> 1;
-  const int nchunks = (p.nb32 + KC - 1) / KC;
+  const int nchunks_all = (p.nb32 + KC - 1) / KC;
+  // gridDim.y CTAs share a row tile and split the chunks of K (narrow matrices at many activation rows)
+  const int ch_lo = (int)(((long long)nchunks_all * blockIdx.y) / gridDim.y);
+  const int ch_hi = (int)(((long long)nchunks_all * (blockIdx.y + 1)) / gridDim.y);
+  const int nchunks = ch_hi - ch_lo;
   const int gsh = p.gshift;
 
   // weights and scales of a stage (static data: may be requested before the dependency wait)
   auto issue_w = [&](int chunk, int stage) {
     uint32_t* ws = sm + stage * STAGE;
     float* ss = reinterpret_cast<float*>(ws + W_WORDS);
-    const int b0 = chunk * KC;
+    const int b0 = (ch_lo + chunk) * KC;
     for (int i = tid; i < NW * RC * KC; i += NT) {
       const int q = i / (RC * KC), r = (i / KC) % RC, c = i % KC;
       const int row = min(row_base + r, p.n - 1);
@@ -333,7 +340,7 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
   // digit tiles of a stage (written by the kernel ahead); closes the stage's copy group
   auto issue_x = [&](int chunk, int stage) {
     uint32_t* xs = sm + stage * STAGE + W_WORDS + S_WORDS;
-    const int b0 = chunk * KC;
+    const int b0 = (ch_lo + chunk) * KC;
     for (int i = tid; i < KC * MT * (kTileWords / 4); i += NT) {
       const int piece = i % (kTileWords / 4), tile = i / (kTileWords / 4);
       const int c = tile / MT, mt = tile % MT;
@@ -378,7 +385,7 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
 #pragma unroll
     for (int cc = 0; cc < KC / WK; ++cc) {
       const int c = cc * WK + wk;          // this warp's blocks of the stage
-      const int blk = ch * KC + c;
+      const int blk = (ch_lo + ch) * KC + c;
       if (blk < p.nb32) {
 #pragma unroll
         for (int q = 0; q < NW; ++q) {
@@ -420,19 +427,52 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
 #pragma unroll
         for (int i = 0; i < 4; ++i) red[(warp * PER + (q * MT + nt) * 4 + i) * 32 + lane] = acc[q][nt][i];
     __syncthreads();
-    if (wk != 0) return;
+    if (wk == 0) {
 #pragma unroll
-    for (int q = 0; q < NW; ++q)
+      for (int q = 0; q < NW; ++q)
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < WK; ++w) v += red[((wr * WK + w) * PER + (q * MT + nt) * 4 + i) * 32 + lane];
+            acc[q][nt][i] = v;
+          }
+    }
+  }
+  if (gridDim.y > 1) {
+    // K split over CTAs (single matrix only): every CTA writes its sums, the last one of the row tile
+    // to arrive (ticket) adds all of them in the order of blockIdx.y - the same order whichever CTA
+    // is last - and goes on to the epilogue.
+    __shared__ int s_last;
+    const size_t slot = ((size_t)blockIdx.x * WR + wr) * MT * 128;
+    const size_t per_y = (size_t)gridDim.x * WR * MT * 128;
+    if (wk == 0) {
+#pragma unroll
+      for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p.ksplit_part[blockIdx.y * per_y + slot + (nt * 4 + i) * 32 + lane] = acc[0][nt][i];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&p.ksplit_cnt[blockIdx.x], 1) == (int)gridDim.y - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) p.ksplit_cnt[blockIdx.x] = 0;  // ready for the next launch
+    if (wk == 0) {
 #pragma unroll
       for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           float v = 0.f;
-#pragma unroll
-          for (int w = 0; w < WK; ++w) v += red[((wr * WK + w) * PER + (q * MT + nt) * 4 + i) * 32 + lane];
-          acc[q][nt][i] = v;
+          for (int y = 0; y < (int)gridDim.y; ++y) v += __ldcg(p.ksplit_part + y * per_y + slot + (nt * 4 + i) * 32 + lane);
+          acc[0][nt][i] = v;
         }
+    }
   }
+  if (wk != 0) return;
   // accumulator i: row (g + 8 * (i >> 1)), activation row (tile * 8 + 2 * t + (i & 1))
 #pragma unroll
   for (int nt = 0; nt < MT; ++nt)
@@ -471,7 +511,7 @@ tb_status launch_rows_cfg(const MmaParams& p, cudaStream_t stream) {
     if (dev < 64) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)((p.n + RC - 1) / RC));
+  cfg.gridDim = dim3((unsigned)((p.n + RC - 1) / RC), (unsigned)(EPI == 0 && p.ksplit > 1 ? p.ksplit : 1));
   cfg.blockDim = dim3(32 * WR * WK);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -524,12 +564,19 @@ tb_status launch_mma_epi(const MmaParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-size_t w4_mma_scratch_bytes(int m, int64_t k) {
+// Scratch layout: [tickets of the K split, 4096 bytes - zero before the first use, left zero] [digit tiles]
+// [partial sums of the K split].
+constexpr size_t kSplitHeader = 4096;
+constexpr int kSplitMaxN = 8192, kSplitMax = 4;
+constexpr size_t kSplitPartBytes = (size_t)kSplitMax * (kSplitMaxN / 16) * 8 * 128 * sizeof(float);
+static size_t digit_bytes(int m, int64_t k) {
   const int mt = (m + 7) / 8;
-  return (size_t)(k / 32) * mt * kTileWords * sizeof(uint32_t);
+  return (((size_t)(k / 32) * mt * kTileWords * sizeof(uint32_t)) + 255) & ~(size_t)255;
 }
+size_t w4_mma_scratch_bytes(int m, int64_t k) { return kSplitHeader + digit_bytes(m, k) + kSplitPartBytes; }
 
-// Up to 64 activation rows per pass; `scratch` holds w4_mma_scratch_bytes(min(m, 64), k).
+// Up to 64 activation rows per pass; `scratch` holds w4_mma_scratch_bytes(min(m, 64), k) and its first
+// 4096 bytes are zero (the decoder clears its block once; a temporary block is cleared per call).
 tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
   if (a.k % 32 != 0 || (reinterpret_cast<uintptr_t>(a.w) & 15) || (a.w2 && (reinterpret_cast<uintptr_t>(a.w2) & 15)) ||
       ((a.k / 2) % 16) != 0)
@@ -550,11 +597,21 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
       cfg.attrs = attr;
       cfg.numAttrs = pdl ? 1 : 0;
       TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_x_kernel, a.x + (int64_t)m0 * a.k, a.norm_w, a.eps,
-                                     static_cast<uint32_t*>(scratch), mc, (int)a.k, mt,
+                                     reinterpret_cast<uint32_t*>(static_cast<char*>(scratch) + kSplitHeader), mc, (int)a.k, mt,
                                      a.x_normed_out ? a.x_normed_out + (int64_t)m0 * a.k : (float*)nullptr));
     }
     MmaParams p;
-    p.xq = static_cast<const uint32_t*>(scratch);
+    p.xq = reinterpret_cast<const uint32_t*>(static_cast<char*>(scratch) + kSplitHeader);
+    // Narrow single matrices at many activation rows: 32-row CTAs alone leave SMs idle, so 2 or 4 CTAs
+    // share a row tile and split K (deterministic sum by the last one to finish).
+    static const int e_ksplit = getenv("TB_MMA_KSPLIT") ? atoi(getenv("TB_MMA_KSPLIT")) : -1;
+    int ksplit = 1;
+    if (!a.w2 && mt >= 2 && a.n <= kSplitMaxN && a.n / 32 < sm_count() && a.k >= 4096) ksplit = a.k >= 8192 ? 4 : 2;
+    if (e_ksplit >= 0 && !a.w2 && a.n <= kSplitMaxN && a.k >= 1024) ksplit = e_ksplit < 1 ? 1 : (e_ksplit > kSplitMax ? kSplitMax : e_ksplit);
+    if (e_layout != 2) ksplit = 1;
+    p.ksplit = ksplit;
+    p.ksplit_cnt = reinterpret_cast<int*>(scratch);
+    p.ksplit_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + kSplitHeader + digit_bytes(mc, a.k));
     p.w[0] = a.w; p.w[1] = a.w2;
     p.scales[0] = a.scales; p.scales[1] = a.scales2;
     p.bias[0] = a.bias; p.bias[1] = a.bias2;
