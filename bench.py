@@ -48,7 +48,7 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu capture summarised under profiles/ (None until a capture exists for this kernel).
-DOMINANT_KERNEL_DRAM_TRAFFIC = 73_467_392 + 1_368_576  # profiles/w4_stream_kernel_gateup_swiglu_14336x4096.md
+DOMINANT_KERNEL_DRAM_TRAFFIC = 73_476_096 + 1_689_088  # profiles/w4_stream_kernel_gateup_swiglu_14336x4096.md
 
 
 def measured_peak():
