@@ -16,8 +16,8 @@ One step = one decode step (all layers + lm_head) for `batch` sequences.
                   step copies the token id in (pinned) and the [vocab] fp32 logits out.
  * roofline     : the dominant kernel (fused RMSNorm + gate/up GEMV + SwiGLU), timed
                   alone over the 32 layers' distinct weights (2.3 GB, far above L2).
- * cpu_baseline : the CPU oracle's SIMD path on this box's host cores, on a bounded
-                  sample (2 of 32 layers + 1/8 of lm_head), scaled to a full step.
+ * cpu_baseline : the CPU oracle's SIMD path on this box's host cores (thread count set
+                  explicitly): full steps, every layer + lm_head, bounded by the step count.
 `--impl reference` prints the CPU arm alone in the same JSON shape.
 
 Synthetic data throughout (no checkpoints or datasets are involved): weights
@@ -46,9 +46,9 @@ QWEN05B = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_l
 CONTEXT = 4096
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
-# ncu capture summarised under profiles/ (None until a capture exists for this kernel).
-DOMINANT_KERNEL_DRAM_TRAFFIC = 73_476_096 + 1_689_088  # profiles/w4_stream_kernel_gateup_swiglu_14336x4096.md
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu
+# capture of that kernel at this shape (None until a capture exists for the kernel).
+DOMINANT_KERNEL_DRAM_TRAFFIC = 73_476_096 + 1_689_088
 
 
 def measured_peak():
@@ -129,60 +129,74 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------- CPU arm
-def cpu_decode_sample(c, ctx, threads=None, seed=0, reps=3):
-    """Times the CPU oracle (the reference's SIMD path restated in C) on a bounded
-    sample of the Llama-3-8B step and scales it to a full step.  Returns a dict."""
+def host_cpu():
+    """(usable hardware threads of this process, CPU model name)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    model = "unknown"
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                model = line.split(":", 1)[1].strip()
+                break
+    except OSError:
+        pass
+    return n, model
+
+
+def cpu_full_step(c, ctx, steps, warmup, seed=0):
+    """Times FULL decode steps (every layer + lm_head, fp32 KV cache at `ctx`) of the CPU oracle -
+    the reference's SIMD path restated in C - on all host threads this process may use.  The
+    thread count is set explicitly (launchers such as torchrun export OMP_NUM_THREADS=1).
+    Weights are random packed nibbles with scales of the magnitude the quantizer produces for
+    N(0, 0.02) weights; timing does not depend on their values."""
     from oracle import oracle as o
 
-    if threads:
-        o.set_threads(threads)
+    threads, cpu_model = host_cpu()
+    o.set_threads(threads)
     rng = np.random.default_rng(seed)
-    H, I, G = c["hidden_size"], c["intermediate_size"], c["group_size"]
-    nh, nkv, hd = c["num_heads"], c["num_kv_heads"], c["head_dim"]
-    n_layers, lm_frac = 2, 8
-    small = dict(c, num_layers=n_layers, vocab_size=64, max_seq_len=ctx)
+    H, I, G, V = c["hidden_size"], c["intermediate_size"], c["group_size"], c["vocab_size"]
+    nh, nkv, hd, L = c["num_heads"], c["num_kv_heads"], c["head_dim"], c["num_layers"]
+    cfg = dict(c, max_seq_len=ctx + 8)
 
-    def qlin(n, k):
-        w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
-        return o.quantize_int4_grouped(w, G)
+    def rlin(n, k):
+        w = np.frombuffer(rng.bytes(n * (k // 2)), dtype=np.uint8).reshape(n, k // 2)
+        s = (rng.random((n, k // G), dtype=np.float32) * np.float32(0.004) + np.float32(0.006))
+        return w, s
 
     layers = []
-    for _ in range(n_layers):
+    for _ in range(L):
         lw = {"input_norm_w": np.ones(H, np.float32), "post_norm_w": np.ones(H, np.float32), "qkv_b": None}
-        lw["qkv_w"], lw["qkv_s"] = qlin((nh + 2 * nkv) * hd, H)
-        lw["o_w"], lw["o_s"] = qlin(H, nh * hd)
-        lw["gate_w"], lw["gate_s"] = qlin(I, H)
-        lw["up_w"], lw["up_s"] = qlin(I, H)
-        lw["down_w"], lw["down_s"] = qlin(H, I)
+        lw["qkv_w"], lw["qkv_s"] = rlin((nh + 2 * nkv) * hd, H)
+        lw["o_w"], lw["o_s"] = rlin(H, nh * hd)
+        lw["gate_w"], lw["gate_s"] = rlin(I, H)
+        lw["up_w"], lw["up_s"] = rlin(I, H)
+        lw["down_w"], lw["down_s"] = rlin(H, I)
         layers.append(lw)
-    embed = rng.standard_normal((64, H), dtype=np.float32) * np.float32(0.02)
-    lm_w, lm_s = qlin(64, H)
-    dec = o.OracleDecoder(small, embed, layers, np.ones(H, np.float32), lm_w, lm_s)
-    for l in range(n_layers):  # context pre-filled with seeded values
+    embed = rng.standard_normal((V, H), dtype=np.float32) * np.float32(0.02)
+    lm_w, lm_s = rlin(V, H)
+    dec = o.OracleDecoder(cfg, embed, layers, np.ones(H, np.float32), lm_w, lm_s)
+    for l in range(L):  # context pre-filled with seeded values
         k, v = dec.kv_cache(l)
-        k[:, : ctx - 1] = rng.standard_normal((nkv, ctx - 1, hd), dtype=np.float32) * np.float32(0.5)
-        v[:, : ctx - 1] = rng.standard_normal((nkv, ctx - 1, hd), dtype=np.float32)
-    dec.set_kv_len(ctx - 1)
-    v_s = c["vocab_size"] // lm_frac
-    hw, hs = qlin(v_s, H)
-    x = rng.standard_normal(H, dtype=np.float32)
-    dec.step(3, ctx - 1)  # warm-up
-    o.gemm_w4a32_grouped(x, hw, hs, None, G)
-    t_layers, t_head = [], []
-    for _ in range(reps):
+        k[:, :ctx] = rng.standard_normal((nkv, ctx, hd), dtype=np.float32) * np.float32(0.5)
+        v[:, :ctx] = rng.standard_normal((nkv, ctx, hd), dtype=np.float32)
+    dec.set_kv_len(ctx)
+    for i in range(warmup):
+        dec.step(3 + i, ctx)
+    times = []
+    for i in range(steps):
         t0 = time.perf_counter()
-        dec.step(5, ctx - 1)
-        t_layers.append(time.perf_counter() - t0)
-        t0 = time.perf_counter()
-        o.gemm_w4a32_grouped(x, hw, hs, None, G)
-        t_head.append(time.perf_counter() - t0)
-    step_s = min(t_layers) * (c["num_layers"] / n_layers) + min(t_head) * lm_frac
+        dec.step(5 + i, ctx)
+        times.append(time.perf_counter() - t0)
+    total = float(np.sum(times))
     return {
-        "value": 1.0 / step_s, "unit": "tokens/s", "cores": o.get_threads(), "kind": "port",
-        "tier": o.TIER_NAMES.get(o.best_tier(), "?"),
-        "sample": (f"{n_layers} of {c['num_layers']} layers at full width with a {ctx}-token fp32 KV cache + 1/{lm_frac} "
-                   f"of lm_head, best of {reps}; scaled linearly to a full step ({step_s * 1e3:.1f} ms/step)"),
-        "ms_per_step": step_s * 1e3,
+        "value": steps / total, "unit": "tokens/s", "cores": threads, "kind": "port",
+        "tier": o.TIER_NAMES.get(o.best_tier(), "?"), "cpu_model": cpu_model,
+        "sample": (f"full step: all {L} layers + lm_head with a {ctx}-token fp32 KV cache, {steps} timed steps after "
+                   f"{warmup} warm-up steps (median {np.median(times) * 1e3:.1f} ms, best {np.min(times) * 1e3:.1f} ms per step)"),
+        "ms_per_step": total / steps * 1e3, "ms_per_step_best": float(np.min(times)) * 1e3,
     }
 
 
@@ -192,21 +206,19 @@ def run_reference(args):
         return
     c = dict(LLAMA8B)
     t0 = time.perf_counter()
-    best = None
-    for _ in range(max(1, min(args.steps, 2))):
-        r = cpu_decode_sample(c, CONTEXT, reps=max(1, min(args.warmup, 2)) + 1)
-        if best is None or r["value"] > best["value"]:
-            best = r
+    steps, warmup = max(1, min(args.steps, 64)), max(1, min(args.warmup, 8))
+    r = cpu_full_step(c, CONTEXT, steps, warmup)
     line = {
-        "impl": "reference", "metric": "decode_tokens_per_s", "value": best["value"] * args.batch / args.batch,
-        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": r["value"],
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": workload_config(c, 1, args.gpus),
-        "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample", "tier")},
-        "e2e": {"value": best["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "tier", "cpu_model")},
+        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
-        "note": "CPU restatement of the reference's SIMD path (the Rust reference cannot be built here); batch 1",
+        "note": "CPU restatement of the reference's SIMD path (the Rust reference cannot be built here); batch 1; "
+                "the same host cores at every --gpus value",
     }
     print(json.dumps(line))
 
@@ -519,7 +531,7 @@ def run_gpu(args):
         "clocks": clocks.summary(),
     }
     if args.cpu_baseline:
-        line["cpu_baseline"] = {k: v for k, v in cpu_decode_sample(c, CONTEXT).items() if k != "ms_per_step"}
+        line["cpu_baseline"] = {k: v for k, v in cpu_full_step(c, CONTEXT, 8, 2).items() if not k.startswith("ms_per_step")}
     print(json.dumps(line), flush=True)
     if tp > 1:
         dist.barrier()

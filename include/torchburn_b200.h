@@ -276,7 +276,8 @@ typedef struct tb_model_config {
 enum {
   TB_DECODER_NO_GRAPH = 1,   /* launch kernels directly instead of replaying a CUDA graph */
   TB_DECODER_NCCL_ONLY = 2,  /* tensor parallel: use ncclAllReduce, not the fused peer-memory kernel */
-  TB_DECODER_NO_PDL = 4      /* chain the kernels with plain stream order instead of programmatic dependent launch */
+  TB_DECODER_NO_PDL = 4,     /* chain the kernels with plain stream order instead of programmatic dependent launch */
+  TB_DECODER_NO_FUSED_STEP = 8 /* batch-1 steps as a chain of single kernels instead of the one persistent step kernel */
 };
 
 /* Per-layer weights in the capsule order of create_rust_qwen_decoder,

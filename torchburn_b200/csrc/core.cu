@@ -239,9 +239,9 @@ void tb_debug_timeline(void* device_buffer, int64_t bytes) { timeline_register(d
 int32_t tb_debug_timeline_blocks(void) { return timeline_blocks_used(); }
 
 int32_t tb_device_fault_flag(void) {
-  const int a = stream_fault_flag(), b = attention_fault_flag();
-  if (a < 0 || b < 0) return -1;
-  return (a | b) ? 1 : 0;
+  const int a = stream_fault_flag(), b = attention_fault_flag(), c = step_fault_flag();
+  if (a < 0 || b < 0 || c < 0) return -1;
+  return (a | b | c) ? 1 : 0;
 }
 
 /* ------------------------------------------------------------ QuantizedLinear */

@@ -66,6 +66,14 @@ struct tb_decoder {
   // norm's weights and the sums of squares of x per 8 elements; the consumers start from those.
   float *xn = nullptr, *ss8 = nullptr;
   bool split_norm = false;
+  // The whole batch-1 step as one persistent kernel (w4_step.cu): phase list, barrier words,
+  // attention partials and a host-mapped word the kernel raises when a bounded wait ran out.
+  bool fused_step = false;
+  StepPhase* d_phases = nullptr;
+  unsigned* d_step_sync = nullptr;
+  float *step_part_o = nullptr, *step_part_ml = nullptr;
+  int* h_step_fault = nullptr;
+  StepProgram prog;
   float* partial = nullptr;  // tensor parallel: this rank's partial sums [B, H]
   float* logits_l = nullptr; // tensor parallel: this rank's logit slice [B, V_l]
   int32_t *d_tokens = nullptr, *d_offsets = nullptr, *d_eff = nullptr;
@@ -140,6 +148,14 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
   const bool pdl = d->pdl;
   const int pm = d->pdl_mask;
   int launches = 0;
+  if (d->fused_step && b == 1 && !debug && before_lm_head == nullptr) {
+    // embedding (+ the first norm's weights and sums of squares), then every layer and lm_head in one kernel
+    TB_TRY(launch_step_embed(d->embed, d->d_tokens, d->d_offsets, d->layers[0].input_norm_w, d->x, d->xn, d->ss8,
+                             d->d_eff, d->V, d->H, d->S, st));
+    TB_TRY(launch_w4_step(d->prog, st));
+    d->launches_per_step = 2;
+    return TB_OK;
+  }
   TB_TRY(launch_embed_gather(d->embed, d->d_tokens, d->d_offsets, d->x, d->d_eff, b, d->V, d->H, d->S,
                              false, st));
   ++launches;
@@ -310,6 +326,100 @@ tb_status run_step(tb_decoder* d, int b, bool greedy) {
   }
   TB_TRY(enqueue_step(d, b, !d->use_graph && (d->cfg.flags & TB_DECODER_NO_GRAPH)));
   if (greedy) TB_TRY(launch_argmax(d->logits, d->V, b, d->d_tokens, d->d_offsets, d->d_hist, d->d_hist_pos, d->argmax_scratch, d->stream));
+  return TB_OK;
+}
+
+// Lays out the batch-1 step for the persistent kernel when every projection fits its rules
+// (otherwise the decoder keeps the chain of single kernels).
+tb_status build_step_program(tb_decoder* d) {
+  d->fused_step = false;
+  if (d->tp != 1 || (d->cfg.flags & (TB_DECODER_NO_FUSED_STEP | TB_DECODER_NO_GRAPH))) return TB_OK;
+  if (d->hd != 64 && d->hd != 128) return TB_OK;
+  const int G = d->G;
+  if (d->H % 32 != 0 || !w4_step_supports(d->tq_l, d->H, G, 1) || !w4_step_supports(d->H, d->q_dim_l, G, 1) ||
+      !w4_step_supports(d->I_l, d->H, G, 2) || !w4_step_supports(d->H, d->I_l, G, 1) || !w4_step_supports(d->V_l, d->H, G, 1))
+    return TB_OK;
+  const int grid = w4_step_grid();
+  const int nc = grid > 0 ? w4_step_attn_split(grid, d->nkv_l) : 0;
+  if (grid <= 0 || nc <= 0) return TB_OK;
+
+  std::vector<StepPhase> ph;
+  int rot = 0;
+  auto gemv = [&](int64_t n, int64_t k, int nw) {
+    StepPhase q;
+    q.kind = 0; q.n = (int)n; q.k = (int)k; q.ng = (int)(k / G); q.gshift = G == 32 ? 0 : (G == 64 ? 1 : 2);
+    q.nw = nw; q.rs = w4_step_rows_per_stage(k, G, nw); q.rot = rot; q.eps = d->cfg.rms_norm_eps;
+    rot = (rot + (int)(((n + 7) / 8) % grid)) % grid;
+    return q;
+  };
+  for (int l = 0; l < d->L; ++l) {
+    const LayerDev& W = d->layers[l];
+    {  // A + B: QKV on the pre-weighted x
+      StepPhase q = gemv(d->tq_l, d->H, 1);
+      q.w[0] = W.qkv_w; q.sc[0] = W.qkv_s; q.bias[0] = W.qkv_b; q.x = d->xn; q.x_ss8 = d->ss8; q.out = d->qkv;
+      ph.push_back(q);
+    }
+    {  // C + D + E: RoPE, append, split-K attention; then the merge of the partials
+      StepPhase q;
+      q.kind = 1;
+      q.k_cache = d->k_cache + (size_t)l * kv_layer_stride(d);
+      q.v_cache = d->v_cache + (size_t)l * kv_layer_stride(d);
+      ph.push_back(q);
+      StepPhase m;
+      m.kind = 2;
+      ph.push_back(m);
+    }
+    {  // F + G
+      StepPhase q = gemv(d->H, d->q_dim_l, 1);
+      q.w[0] = W.o_w; q.sc[0] = W.o_s; q.x = d->attn; q.resid = d->x; q.out = d->x;
+      q.out_scaled = d->xn; q.out_scale_w = W.post_norm_w; q.out_ss8 = d->ss8;
+      ph.push_back(q);
+    }
+    {  // H + I
+      StepPhase q = gemv(d->I_l, d->H, 2);
+      q.w[0] = W.gate_w; q.sc[0] = W.gate_s; q.w[1] = W.up_w; q.sc[1] = W.up_s; q.x = d->xn; q.x_ss8 = d->ss8; q.out = d->h;
+      ph.push_back(q);
+    }
+    {  // I' + J
+      StepPhase q = gemv(d->H, d->I_l, 1);
+      q.w[0] = W.down_w; q.sc[0] = W.down_s; q.x = d->h; q.resid = d->x; q.out = d->x;
+      q.out_scaled = d->xn; q.out_ss8 = d->ss8;
+      q.out_scale_w = l + 1 < d->L ? d->layers[l + 1].input_norm_w : d->final_norm_w;
+      ph.push_back(q);
+    }
+  }
+  {  // 3 + 4: lm_head on the pre-weighted x
+    StepPhase q = gemv(d->V_l, d->H, 1);
+    q.w[0] = d->lm_w; q.sc[0] = d->lm_s; q.x = d->xn; q.x_ss8 = d->ss8; q.out = d->logits;
+    ph.push_back(q);
+  }
+  TB_TRY(dalloc(&d->d_phases, ph.size()));
+  TB_CUDA_TRY(cudaMemcpy(d->d_phases, ph.data(), ph.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
+  TB_TRY(dalloc(&d->d_step_sync, (size_t)4));
+  TB_CUDA_TRY(cudaMemset(d->d_step_sync, 0, 4 * sizeof(unsigned)));
+  TB_TRY(dalloc(&d->step_part_o, (size_t)d->nh_l * nc * d->hd));
+  TB_TRY(dalloc(&d->step_part_ml, (size_t)d->nh_l * nc * 2));
+  TB_CUDA_TRY(cudaHostAlloc((void**)&d->h_step_fault, sizeof(int), cudaHostAllocMapped));
+  *d->h_step_fault = 0;
+  int* dev_fault = nullptr;
+  TB_CUDA_TRY(cudaHostGetDevicePointer((void**)&dev_fault, d->h_step_fault, 0));
+  StepProgram& g = d->prog;
+  g.phases = d->d_phases; g.nphases = (int)ph.size(); g.grid = grid; g.sync = d->d_step_sync;
+  g.host_fault = dev_fault;
+  g.qkv = d->qkv; g.attn = d->attn; g.cos_t = d->cos_t; g.sin_t = d->sin_t; g.offsets = d->d_eff;
+  g.part_o = d->step_part_o; g.part_ml = d->step_part_ml;
+  g.num_heads = d->nh_l; g.num_kv_heads = d->nkv_l; g.head_dim = d->hd; g.nc = nc; g.max_seq_len = d->S;
+  d->fused_step = true;
+  return TB_OK;
+}
+
+// A bounded device-side wait ran out during the last step: the results are invalid and the
+// decoder is unusable from here on (the kernel ended; the context is intact).
+tb_status check_step_fault(tb_decoder* d) {
+  if (d->h_step_fault && *reinterpret_cast<volatile int*>(d->h_step_fault)) {
+    d->device_lost = true;
+    return fail(TB_ERR_TIMEOUT, "a bounded device-side wait of the decode step ran out; the step's results are invalid");
+  }
   return TB_OK;
 }
 
@@ -484,6 +594,7 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   }
   CRC(cudaMalloc(&d->argmax_scratch, 16 * kMaxBatch));
   CRC(cudaMemset(d->argmax_scratch, 0, 16 * kMaxBatch));
+  CR(build_step_program(d));
   if (c.flags & TB_DECODER_NO_GRAPH) {
     CR(dalloc(&d->dbg_embed, (size_t)H)); CR(dalloc(&d->dbg_normed, (size_t)B * H));
     CR(dalloc(&d->dbg_qkv, (size_t)B * d->tq_l)); CR(dalloc(&d->dbg_attn, (size_t)d->q_dim_l));
@@ -526,6 +637,8 @@ void tb_decoder_destroy(tb_decoder* d) {
   }
   cudaFree(d->cos_t); cudaFree(d->sin_t); cudaFree(d->k_cache); cudaFree(d->v_cache);
   cudaFree(d->xn); cudaFree(d->ss8);
+  cudaFree(d->d_phases); cudaFree(d->d_step_sync); cudaFree(d->step_part_o); cudaFree(d->step_part_ml);
+  if (d->h_step_fault) cudaFreeHost(d->h_step_fault);
   cudaFree(d->x); cudaFree(d->qkv); cudaFree(d->attn); cudaFree(d->h); cudaFree(d->logits);
   cudaFree(d->partial); cudaFree(d->logits_l);
   cudaFree(d->d_tokens); cudaFree(d->d_offsets); cudaFree(d->d_eff); cudaFree(d->d_hist); cudaFree(d->d_hist_pos);
@@ -548,7 +661,7 @@ tb_status tb_decoder_step_batch(tb_decoder* d, const int64_t* token_ids, const i
   if (logits_host)
     DEC_CUDA(d, cudaMemcpyAsync(logits_host, d->logits, sizeof(float) * batch * d->V, cudaMemcpyDeviceToHost, d->stream));
   DEC_CUDA(d, cudaStreamSynchronize(d->stream));
-  return TB_OK;
+  return check_step_fault(d);
 }
 
 tb_status tb_decoder_step(tb_decoder* d, int64_t token_id, int64_t offset, float* logits_host) {
@@ -585,7 +698,7 @@ tb_status tb_decoder_prefill_tokens(tb_decoder* d, const int64_t* tokens, int64_
   }
   DEC_CUDA(d, cudaStreamSynchronize(d->stream));
   if (end_offset) *end_offset = start_offset + n;
-  return TB_OK;
+  return check_step_fault(d);
 }
 
 tb_status tb_decoder_prefill(tb_decoder* d, const int64_t* tokens, int64_t n, float* logits_host) {
@@ -723,6 +836,7 @@ tb_status tb_decoder_generate_greedy(tb_decoder* d, int64_t first_token, int64_t
   std::vector<int32_t> hist((size_t)n_new);
   DEC_CUDA(d, cudaMemcpyAsync(hist.data(), d->d_hist, sizeof(int32_t) * n_new, cudaMemcpyDeviceToHost, d->stream));
   DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  TB_TRY(check_step_fault(d));
   int64_t tok = first_token;
   for (int64_t i = 0; i < n_new; ++i) {
     note_kv(d, tok, start_offset + i);

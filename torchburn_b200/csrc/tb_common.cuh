@@ -180,6 +180,70 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream);
 size_t static_attention_scratch_capacity();
 tb_status static_attention_scratch(void** ptr);
 
+// ---- the whole decode step as one persistent kernel (w4_step.cu) ------------------------------
+// A step is a list of phases that every CTA of one cooperative grid walks in order, with a
+// grid-wide barrier after each: projections (kind 0), the split-K attention over one layer's
+// cache (kind 1) and the merge of its partials (kind 2).
+struct StepPhase {
+  int kind = 0;
+  int n = 0;            // projection: output rows (row pairs for the SwiGLU form)
+  int k = 0;            // projection: input features
+  int ng = 0;           // scales per row
+  int gshift = 0;       // log2(group_size / 32)
+  int rs = 8;           // rows per ring stage and matrix (1, 2, 4 or 8)
+  int nw = 1;           // 2 = gate/up pair with the SwiGLU epilogue
+  int rot = 0;          // rotation of the balanced split of the 8-row rounds over the CTAs
+  float eps = 0.f;
+  int pad = 0;
+  const uint8_t* w[2] = {nullptr, nullptr};
+  const float* sc[2] = {nullptr, nullptr};
+  const float* bias[2] = {nullptr, nullptr};
+  const float* x = nullptr;          // [k]
+  const float* x_ss8 = nullptr;      // x is pre-weighted by the norm; sums of squares per 8 elements (null: no norm)
+  const float* resid = nullptr;      // out = resid + y
+  float* out = nullptr;
+  float* out_scaled = nullptr;       // optional out * out_scale_w (the next norm's weights)
+  const float* out_scale_w = nullptr;
+  float* out_ss8 = nullptr;          // optional sums of squares of out per 8 rows
+  float* k_cache = nullptr;          // attention: this layer's [Hkv, max_seq_len, d]
+  float* v_cache = nullptr;
+};
+static_assert(sizeof(StepPhase) == 160, "StepPhase is copied as ten 16-byte words");
+
+struct StepProgram {
+  const StepPhase* phases = nullptr;   // device array
+  int nphases = 0;
+  int grid = 0;                        // CTAs the program was laid out for (rot fields, attention split)
+  unsigned* sync = nullptr;            // device: [0] barrier arrivals, [1] exit tickets; zero before the first launch
+  int* host_fault = nullptr;           // optional host-mapped word, set to 1 when a bounded wait ran out
+  const float* qkv = nullptr;          // [(Hq + 2 Hkv) * d] of the current token, before RoPE
+  float* attn = nullptr;               // [Hq * d]
+  const float* cos_t = nullptr;
+  const float* sin_t = nullptr;
+  const int32_t* offsets = nullptr;    // [1] effective offset (-1: nothing to attend to)
+  float* part_o = nullptr;             // [Hq, nc, d]
+  float* part_ml = nullptr;            // [Hq, nc, 2]
+  int num_heads = 0, num_kv_heads = 0, head_dim = 0;
+  int nc = 0;                          // CTAs per kv head in the attention phases
+  int64_t max_seq_len = 0;
+};
+// CTAs of the step kernel on the current device (0 when it cannot run there).
+int w4_step_grid();
+// Shape rules of one projection phase.
+bool w4_step_supports(int64_t n, int64_t k, int g, int nw);
+int w4_step_rows_per_stage(int64_t k, int g, int nw);
+// Attention split: CTAs per kv head and bytes of the two partial arrays.
+int w4_step_attn_split(int grid, int num_kv_heads);
+tb_status launch_w4_step(const StepProgram& prog, cudaStream_t stream);
+// x = table[token] (zeros and offset -1 when token or offset is out of range), xn = x * norm_w,
+// ss8[i] = sum of x^2 over elements 8i..8i+7: what the first phase of a step starts from.
+tb_status launch_step_embed(const float* table, const int32_t* tokens, const int32_t* offsets, const float* norm_w,
+                            float* x, float* xn, float* ss8, int32_t* eff_offsets, int64_t vocab, int64_t hidden,
+                            int64_t max_seq_len, cudaStream_t stream);
+int step_fault_flag();
+// Test hook: cycles a device-side wait of the step kernel may take before it gives up (0 = default).
+void set_step_wait_limit(long long cycles);
+
 tb_status launch_rms_norm(const float* x, const float* w, float* out, int64_t m, int64_t n,
                           float eps, cudaStream_t stream);
 // x[b] = table[tokens[b]] and eff_offsets[b] = offsets[b] when token and offset are in range,

@@ -61,16 +61,16 @@ __device__ __forceinline__ float idot32(const uint4 wv, const uint32_t (&xq)[24]
 
 // Quantises NE consecutive elements of a 32-element block whose maximum magnitude is
 // `amax` (NE = 32: the whole block; 16: one half, the maximum taken over both halves):
-// digits + sx + the offset term -8 * sx * sum(q) of these elements.
+// digits + sx + S = sum(q) of these elements (the -8 offset of the codes contributes -8 * S).
 template <int NE>
-__device__ __forceinline__ void quantize_part(const float (&v)[NE], float amax, uint32_t (&dig)[NE / 8 * 6],
-                                              float& sx, float& corr) {
+__device__ __forceinline__ void quantize_part_int(const float (&v)[NE], float amax, uint32_t (&dig)[NE / 8 * 6],
+                                                  float& sx, int& S) {
   int e = (__float_as_int(amax) >> 23) & 0xFF;  // biased exponent of the block maximum
   if (e < 24) e = 24;                           // tiny / zero blocks: fixed scale 2^-125
   // Inf or NaN in the block (e == 255): the scale becomes NaN and so does the output.
   sx = (e == 255) ? __int_as_float(0x7FC00000) : __int_as_float((e - 22) << 23);
   const float inv = __int_as_float((276 - (e == 255 ? 254 : e)) << 23);
-  int S = 0;
+  S = 0;
   int q[NE];
 #pragma unroll
   for (int i = 0; i < NE; ++i) {
@@ -79,18 +79,26 @@ __device__ __forceinline__ void quantize_part(const float (&v)[NE], float amax, 
     q[i] = qi;
     S += qi;
   }
+  // byte d of four elements -> one word: two byte permutes pick the byte from each pair, a third joins them
 #pragma unroll
   for (int wd = 0; wd < NE / 8; ++wd)
 #pragma unroll
     for (int par = 0; par < 2; ++par)
 #pragma unroll
       for (int d = 0; d < 3; ++d) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int b = 0; b < 4; ++b)
-          word |= ((uint32_t)(q[wd * 8 + 2 * b + par] >> (8 * d)) & 0xFFu) << (8 * b);
-        dig[wd * 6 + par * 3 + d] = word;
+        const uint32_t sel = (uint32_t)d | ((uint32_t)(4 + d) << 4);
+        const uint32_t lo = __byte_perm((uint32_t)q[wd * 8 + par], (uint32_t)q[wd * 8 + 2 + par], sel);
+        const uint32_t hi = __byte_perm((uint32_t)q[wd * 8 + 4 + par], (uint32_t)q[wd * 8 + 6 + par], sel);
+        dig[wd * 6 + par * 3 + d] = __byte_perm(lo, hi, 0x5410);
       }
+}
+
+// The same with the offset term of the codes as a float: corr = -8 * sx * sum(q).
+template <int NE>
+__device__ __forceinline__ void quantize_part(const float (&v)[NE], float amax, uint32_t (&dig)[NE / 8 * 6],
+                                              float& sx, float& corr) {
+  int S;
+  quantize_part_int<NE>(v, amax, dig, sx, S);
   corr = -8.0f * (float)S * sx;
 }
 
