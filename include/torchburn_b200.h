@@ -161,6 +161,9 @@ tb_status tb_attention_decode_static(const float* qkv, float* k_cache, float* v_
  * tb_debug_timeline_blocks returns how many blocks were handed out. */
 void tb_debug_timeline(void* device_buffer, int64_t bytes);
 int32_t tb_debug_timeline_blocks(void);
+/* Test hook of the persistent step kernel: bit 0 = the projections consume their weight stream
+ * without multiplying (measures the stream alone; results are meaningless).  Process-wide. */
+void tb_debug_step_flags(int32_t flags);
 
 /* Tuning hook: positions of the KV sequence handled per attention CTA (a power
  * of two in [64, 512]; 0 = choose from the shape).  Process-wide; plays the role

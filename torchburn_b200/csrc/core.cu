@@ -236,6 +236,7 @@ void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb,
 }
 
 void tb_debug_timeline(void* device_buffer, int64_t bytes) { timeline_register(device_buffer, bytes); }
+void tb_debug_step_flags(int32_t flags) { set_step_debug(flags); }
 int32_t tb_debug_timeline_blocks(void) { return timeline_blocks_used(); }
 
 int32_t tb_device_fault_flag(void) {

@@ -243,6 +243,7 @@ tb_status launch_step_embed(const float* table, const int32_t* tokens, const int
 int step_fault_flag();
 // Test hook: cycles a device-side wait of the step kernel may take before it gives up (0 = default).
 void set_step_wait_limit(long long cycles);
+void set_step_debug(int flags);
 
 tb_status launch_rms_norm(const float* x, const float* w, float* out, int64_t m, int64_t n,
                           float eps, cudaStream_t stream);

@@ -70,6 +70,7 @@ struct StepParams {
   long long max_seq_len;
   float scale;
   long long wait_cycles;
+  int debug;                // test hook: bit 0 = consume the stages without multiplying
   unsigned long long* tl;   // optional timestamps (step_mark)
 };
 
@@ -245,15 +246,24 @@ __device__ __forceinline__ AttnPlan attn_plan(const StepParams& p, int cta) {
 // ------------------------------------------------------------------------------------------
 template <int D>
 __device__ __forceinline__ void producer_loop(const StepParams& p, unsigned char* ring, uint64_t* full, uint64_t* empty,
-                              volatile int* s_abort) {
-  uint32_t it = 0;
+                                              volatile int* s_abort, const int lane) {
+  // Lane s of the producer warp owns ring slot s: it requests every stage that lands there
+  // (global stage numbers s, s + 8, ...).  Eight lanes work out addresses and wait for their
+  // slots side by side, so one slow slot does not hold back the requests for the others.
+  if (lane >= kStages) return;
   const int cta = (int)blockIdx.x, grid = (int)gridDim.x;
   const long long wait_limit = p.wait_cycles;
   const int nphases = p.nphases;
   const StepPhase* phases = p.phases;
-  auto acquire = [&]() -> bool {  // the slot of stage `it` is free again
-    if (it >= (uint32_t)kStages) return mbar_wait(&empty[it % kStages], ((it / kStages) - 1u) & 1u, s_abort, wait_limit);
-    return !*s_abort;
+  unsigned char* dst = ring + (size_t)lane * kStageBytes;
+  uint64_t* my_full = &full[lane];
+  uint64_t* my_empty = &empty[lane];
+  uint32_t base = 0;    // global number of the first stage of the current phase (or chunk pass)
+  uint32_t uses = 0;    // stages this lane has requested so far
+  auto acquire = [&]() -> bool {  // the slot is free again
+    const bool ok = uses == 0 ? !*s_abort : mbar_wait(my_empty, (uses - 1u) & 1u, s_abort, wait_limit);
+    ++uses;
+    return ok;
   };
   for (int ph = 0; ph < nphases; ++ph) {
     const StepPhase* d = phases + ph;
@@ -267,27 +277,27 @@ __device__ __forceinline__ void producer_loop(const StepParams& p, unsigned char
       const float* s1 = d->sc[1];
       int round0, my_rounds;
       round_share((n + 7) >> 3, grid, cta, __ldg(&d->rot), round0, my_rounds);
-      const int spr = 8 / rs;
-      for (int i = 0; i < my_rounds * spr; ++i, ++it) {
+      const int rs_shift = rs == 8 ? 3 : (rs == 4 ? 2 : 1);
+      const int nst = (my_rounds * 8) >> rs_shift;
+      for (int i = (int)((lane - base) & (kStages - 1)); i < nst; i += kStages) {
         if (!acquire()) return;
-        const int s = (int)(it % kStages);
-        const int row0 = (round0 + i / spr) * 8 + (i % spr) * rs;
+        const int row0 = round0 * 8 + i * rs;
         const int cnt = max(0, min(rs, n - row0));
         if (cnt == 0) {  // nothing to fetch: complete the phase of the barrier by hand
-          mbar_arrive(&full[s]);
+          mbar_arrive(my_full);
           continue;
         }
-        unsigned char* dst = ring + (size_t)s * kStageBytes;
         const uint32_t wb = (uint32_t)cnt * row_bytes, sb = (uint32_t)cnt * srow_bytes;
-        mbar_expect_tx(&full[s], nw * (wb + sb));
-        bulk_g2s(dst, w0 + (int64_t)row0 * row_bytes, wb, &full[s]);
-        bulk_g2s(dst + (size_t)rs * row_bytes, s0 + (int64_t)row0 * ng, sb, &full[s]);
+        mbar_expect_tx(my_full, nw * (wb + sb));
+        bulk_g2s(dst, w0 + (int64_t)row0 * row_bytes, wb, my_full);
+        bulk_g2s(dst + (size_t)rs * row_bytes, s0 + (int64_t)row0 * ng, sb, my_full);
         if (nw == 2) {
           unsigned char* d2 = dst + (size_t)rs * (row_bytes + srow_bytes);
-          bulk_g2s(d2, w1 + (int64_t)row0 * row_bytes, wb, &full[s]);
-          bulk_g2s(d2 + (size_t)rs * row_bytes, s1 + (int64_t)row0 * ng, sb, &full[s]);
+          bulk_g2s(d2, w1 + (int64_t)row0 * row_bytes, wb, my_full);
+          bulk_g2s(d2 + (size_t)rs * row_bytes, s1 + (int64_t)row0 * ng, sb, my_full);
         }
       }
+      base += (uint32_t)nst;
     } else if (kind == 1) {
       const AttnPlan a = attn_plan(p, cta);
       if (!a.active) continue;
@@ -297,17 +307,17 @@ __device__ __forceinline__ void producer_loop(const StepParams& p, unsigned char
         const int cr0 = c * kChunkRows;
         const int crn = min(kChunkRows, a.ring_rows - cr0);
         const int nt = (crn + kAttnRows - 1) / kAttnRows;
-        for (int pass = 0; pass < 2; ++pass) {
-          const float* src = (pass == 0 ? kc : vc) + (int64_t)(a.t0 + cr0) * D;
-          for (int t = 0; t < nt; ++t, ++it) {
-            if (!acquire()) return;
-            const int s = (int)(it % kStages);
-            const int nr = min(kAttnRows, crn - t * kAttnRows);
-            const uint32_t bytes = (uint32_t)nr * D * sizeof(float);
-            mbar_expect_tx(&full[s], bytes);
-            bulk_g2s(ring + (size_t)s * kStageBytes, src + (int64_t)t * kAttnRows * D, bytes, &full[s]);
-          }
+        // the chunk's K tiles, then its V tiles: 2 * nt stages
+        for (int i = (int)((lane - base) & (kStages - 1)); i < 2 * nt; i += kStages) {
+          if (!acquire()) return;
+          const int pass = i >= nt ? 1 : 0, t = i - pass * nt;
+          const float* src = (pass == 0 ? kc : vc) + (int64_t)(a.t0 + cr0 + t * kAttnRows) * D;
+          const int nr = min(kAttnRows, crn - t * kAttnRows);
+          const uint32_t bytes = (uint32_t)nr * D * sizeof(float);
+          mbar_expect_tx(my_full, bytes);
+          bulk_g2s(dst, src, bytes, my_full);
         }
+        base += (uint32_t)(2 * nt);
       }
     }
   }
@@ -402,7 +412,7 @@ __device__ __forceinline__ uint32_t gemv_rounds(const StepPhase& d, const StepPa
       const uint32_t is = it + (uint32_t)ss;
       ok = mbar_wait(&sh.full[is % kStages], (is / kStages) & 1u, sh.s_abort, wait_limit) && ok;
     }
-    if (mine) {
+    if (mine && !(p.debug & 1)) {
 #pragma unroll 1
       for (int q = 0; q < NW; ++q) {
         float pa[8];
@@ -500,7 +510,7 @@ __device__ __forceinline__ uint32_t gemv_phase(const StepPhase& d, const StepPar
 #pragma unroll
     for (int j = 0; j < XIT; ++j) {
       const int f = tid + j * kCT;
-      if (f < nf4) t[j] = __ldcg(xg + f);
+      t[j] = f < nf4 ? __ldcg(xg + f) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int j = 0; j < XIT; ++j) {
@@ -939,7 +949,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
   __syncthreads();
 
   if (warp == kCW) {
-    if ((tid & 31) == 0) producer_loop<D>(p, sh.ring, full, empty, sh.s_abort);
+    producer_loop<D>(p, sh.ring, full, empty, sh.s_abort, tid & 31);
     return;
   }
 
@@ -1010,10 +1020,12 @@ __global__ void __launch_bounds__(1024) step_embed_kernel(const float* __restric
 }
 
 long long g_wait_cycles = 0;
+int g_step_debug = 0;
 
 }  // namespace
 
 void set_step_wait_limit(long long cycles) { g_wait_cycles = cycles; }
+void set_step_debug(int flags) { g_step_debug = flags; }
 
 int step_fault_flag() {
   int v = 0;
@@ -1081,6 +1093,7 @@ tb_status launch_w4_step(const StepProgram& g, cudaStream_t stream) {
   p.max_seq_len = g.max_seq_len;
   p.scale = 1.0f / sqrtf((float)g.head_dim);
   p.wait_cycles = g_wait_cycles > 0 ? g_wait_cycles : kWaitCyclesDefault;
+  p.debug = g_step_debug;
   p.tl = timeline_next_block();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
