@@ -113,7 +113,9 @@ tb_status tb_quantize_weight_int4_grouped(const float* w, int64_t n, int64_t k,
  * k,v into the caches at [seq, kv_h, offset, :] and computes, per q head h
  * (kv_h = h / (Hq/Hkv)), softmax((q.k_t)/sqrt(d)) over t in [0, offset] times V.
  * k_cache, v_cache: [b, Hkv, max_seq_len, d] f32.  offsets [b] int32 DEVICE.
- * out [b, Hq*d].  `scratch` is device memory of tb_attention_scratch_bytes(),
+ * out [b, Hq*d].  max_seq_len above 32768 is refused with TB_ERR_UNSUPPORTED (the reference
+ * attends to at most 32768 positions, src/llm/decoder.rs:1180).  `scratch` is device memory of
+ * tb_attention_scratch_bytes(),
  * zero-filled once before its first use (the kernel leaves its counters zero).
  * Replaces steps C-E of step_internal, src/llm/decoder.rs:1127-1213
  * (src/shaders/rope_append.wgsl + attn_decode.wgsl on the wgpu path). */
@@ -164,6 +166,19 @@ int32_t tb_debug_timeline_blocks(void);
 /* Test hook of the persistent step kernel: bit 0 = the projections consume their weight stream
  * without multiplying (measures the stream alone; results are meaningless).  Process-wide. */
 void tb_debug_step_flags(int32_t flags);
+/* Failure detection without a fault (the role of the reference's device-lost handling,
+ * src/wgpu/decode.rs:1140-1145): launches one warp that waits, with the given limit in clock
+ * cycles, on an mbarrier nobody completes and on a grid barrier that is one arrival short.  Both
+ * waits must give up and raise the fault word.  Returns TB_ERR_TIMEOUT when they did (the word is
+ * cleared again), TB_ERR_CUDA on any other outcome.  Nothing hangs, traps or faults. */
+tb_status tb_debug_wait_probe(int64_t limit_cycles);
+/* One projection through the persistent step kernel's code path (a program of one phase):
+ * out = W x + bias, or silu(W x) * (W2 x) when w2/scales2 are not NULL.  All pointers DEVICE.
+ * For parity tests and profiling of that path at any shape; tb_gemv_w4a32_grouped is the
+ * product entry point.  TB_ERR_UNSUPPORTED for shapes the step kernel does not take. */
+tb_status tb_debug_step_gemv(const float* x, const uint8_t* w, const float* scales, const float* bias,
+                             const uint8_t* w2, const float* scales2, float* out, int64_t n, int64_t k,
+                             int32_t group_size, void* stream);
 
 /* Tuning hook: positions of the KV sequence handled per attention CTA (a power
  * of two in [64, 512]; 0 = choose from the shape).  Process-wide; plays the role

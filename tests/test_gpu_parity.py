@@ -566,7 +566,7 @@ def test_decoder_qwen05b_config3_full_width(torch, tb, oracle):
     dec_ng = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, debug=True)
     dec_ng.copy_kv_cache_from_tensors(list(ks), list(vs), 1023)
     c = dec_ng.step(int(toks[1023]), 1023)
-    assert max_rel_err(c, a) < 1e-6
+    assert max_rel_err(c, a) < 1e-5  # graph path (one persistent kernel) against direct launches: other summation orders
 
 
 def test_decoder_width_2048_persistent_kernels_match_oracle(torch, tb, oracle):
@@ -709,7 +709,7 @@ def test_loader_checkpoint_to_cache_to_decoder(torch, tb, oracle, tmp_path):
     with pytest.raises(KeyError):
         loader.quantize_checkpoint({k: v for k, v in ck.items() if "o_proj" not in k}, 2)
 
-    v1 = loader.save_cache(sd, str(tmp_path / loader.CACHE_V1.format(g=64)))
+    v1 = loader.save_cache(sd, str(tmp_path / loader.CACHE_V1))
     assert loader.find_cache(str(tmp_path)) == v1
     back = loader.load_cache(v1)
     assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)

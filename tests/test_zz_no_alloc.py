@@ -38,6 +38,22 @@ def _case(torch, tb, oracle, nh, nkv, hd, max_seq, offsets, seed):
     torch.cuda.synchronize()
     assert max_rel_err(got.cpu().numpy(), want.cpu().numpy()) < TOL
     assert torch.equal(k1, k2) and torch.equal(v1, v2)  # same cache append
+    # ... and directly against the CPU oracle: rotate q and k, append, attend to [0, offset]
+    g, gk, gv = got.cpu().numpy(), k2.cpu().numpy(), v2.cpu().numpy()
+    qkv_h = qkv.cpu().numpy()
+    for s_, off in enumerate(offsets):
+        q = qkv_h[s_, :nh * hd].reshape(nh, hd).copy()
+        k = qkv_h[s_, nh * hd:(nh + nkv) * hd].reshape(nkv, hd).copy()
+        v = qkv_h[s_, (nh + nkv) * hd:].reshape(nkv, hd)
+        for h in range(nh):
+            q[h] = oracle.rope_apply_head(q[h], cos_t[off], sin_t[off])
+        for h in range(nkv):
+            k[h] = oracle.rope_apply_head(k[h], cos_t[off], sin_t[off])
+        ek, ev = kc[s_].copy(), vc[s_].copy()
+        ek[:, off], ev[:, off] = k, v
+        assert np.array_equal(gk[s_], ek) and np.array_equal(gv[s_], ev)
+        assert max_rel_err(g[s_].reshape(nh, hd), oracle.attention_decode(q, ek, ev, off + 1)) < TOL
+    assert L.tb_device_fault_flag() == 0  # no bounded wait of the kernel ran out
 
 
 def test_static_scratch_attention_matches_regular_entry_point(oracle):

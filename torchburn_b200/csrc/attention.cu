@@ -17,6 +17,8 @@
 // finish - found with a ticket counter - rescales and sums the partials.  The
 // result equals the two-pass softmax up to fp32 rounding.  HBM-bound:
 // algorithmic bytes = 2 * Hkv * (offset+1) * d * 4 per sequence and layer.
+#include <atomic>
+
 #include "tb_common.cuh"
 
 namespace tb {
@@ -906,6 +908,8 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   if (a.head_dim != 32 && a.head_dim != 64 && a.head_dim != 128)
     return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: head_dim %d (supported: 32, 64, 128)", a.head_dim);
   if (a.batch < 1 || a.max_seq_len < 1) return fail(TB_ERR_SHAPE, "attention: empty shape");
+  if (a.max_seq_len > kSeqCap)  // beyond it a new row would neither be appended nor attended to
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: max_seq_len %lld (attention covers at most %d positions)", (long long)a.max_seq_len, kSeqCap);
   if ((reinterpret_cast<uintptr_t>(a.k_cache) | reinterpret_cast<uintptr_t>(a.v_cache)) & 15)
     return fail(TB_ERR_ARG, "attention: the KV caches must be 16-byte aligned");
 
@@ -1013,18 +1017,21 @@ size_t static_attention_scratch_capacity() { return kStaticScratchBytes; }
 // In host code the array's name is only a handle for the runtime, not an address a kernel
 // could use; the device address is looked up once per device, with that device current.
 tb_status static_attention_scratch(void** ptr) {
-  static void* cached[64] = {nullptr};
+  static std::atomic<void*> cached[64];   // several host threads may make their first call at once
   int dev = 0;
   TB_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && cached[dev]) {
-    *ptr = cached[dev];
-    return TB_OK;
+  if (dev >= 0 && dev < 64) {
+    void* c = cached[dev].load(std::memory_order_relaxed);
+    if (c) {
+      *ptr = c;
+      return TB_OK;
+    }
   }
   void* p = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&p, g_static_attn_scratch);
   if (e != cudaSuccess || p == nullptr)
     return fail(TB_ERR_CUDA, "cudaGetSymbolAddress(static attention scratch) failed: %s", cudaGetErrorString(e));
-  if (dev >= 0 && dev < 64) cached[dev] = p;
+  if (dev >= 0 && dev < 64) cached[dev].store(p, std::memory_order_relaxed);
   *ptr = p;
   return TB_OK;
 }

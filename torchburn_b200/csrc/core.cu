@@ -237,6 +237,15 @@ void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb,
 
 void tb_debug_timeline(void* device_buffer, int64_t bytes) { timeline_register(device_buffer, bytes); }
 void tb_debug_step_flags(int32_t flags) { set_step_debug(flags); }
+tb_status tb_debug_wait_probe(int64_t limit_cycles) { return step_wait_probe((long long)limit_cycles); }
+
+tb_status tb_debug_step_gemv(const float* x, const uint8_t* w, const float* scales, const float* bias, const uint8_t* w2,
+                             const float* scales2, float* out, int64_t n, int64_t k, int32_t group_size, void* stream) {
+  GemvArgs a;
+  a.x = x; a.w = w; a.scales = scales; a.bias = bias; a.w2 = w2; a.scales2 = scales2; a.out = out;
+  a.m = 1; a.n = n; a.k = k; a.g = group_size;
+  return launch_w4_step_gemv(a, as_stream(stream));
+}
 int32_t tb_debug_timeline_blocks(void) { return timeline_blocks_used(); }
 
 int32_t tb_device_fault_flag(void) {

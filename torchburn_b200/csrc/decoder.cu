@@ -395,8 +395,8 @@ tb_status build_step_program(tb_decoder* d) {
   }
   TB_TRY(dalloc(&d->d_phases, ph.size()));
   TB_CUDA_TRY(cudaMemcpy(d->d_phases, ph.data(), ph.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
-  TB_TRY(dalloc(&d->d_step_sync, (size_t)4));
-  TB_CUDA_TRY(cudaMemset(d->d_step_sync, 0, 4 * sizeof(unsigned)));
+  TB_TRY(dalloc(&d->d_step_sync, (size_t)8));
+  TB_CUDA_TRY(cudaMemset(d->d_step_sync, 0, 8 * sizeof(unsigned)));
   TB_TRY(dalloc(&d->step_part_o, (size_t)d->nh_l * nc * d->hd));
   TB_TRY(dalloc(&d->step_part_ml, (size_t)d->nh_l * nc * 2));
   TB_CUDA_TRY(cudaHostAlloc((void**)&d->h_step_fault, sizeof(int), cudaHostAllocMapped));

@@ -214,7 +214,7 @@ struct StepProgram {
   const StepPhase* phases = nullptr;   // device array
   int nphases = 0;
   int grid = 0;                        // CTAs the program was laid out for (rot fields, attention split)
-  unsigned* sync = nullptr;            // device: [0] barrier arrivals, [1] exit tickets; zero before the first launch
+  unsigned* sync = nullptr;            // device, 16-byte aligned: [0..3] barrier arrivals, [4] exit tickets; zero before the first launch
   int* host_fault = nullptr;           // optional host-mapped word, set to 1 when a bounded wait ran out
   const float* qkv = nullptr;          // [(Hq + 2 Hkv) * d] of the current token, before RoPE
   float* attn = nullptr;               // [Hq * d]
@@ -235,6 +235,7 @@ int w4_step_rows_per_stage(int64_t k, int g, int nw);
 // Attention split: CTAs per kv head and bytes of the two partial arrays.
 int w4_step_attn_split(int grid, int num_kv_heads);
 tb_status launch_w4_step(const StepProgram& prog, cudaStream_t stream);
+tb_status launch_w4_step_gemv(const GemvArgs& a, cudaStream_t stream);
 // x = table[token] (zeros and offset -1 when token or offset is out of range), xn = x * norm_w,
 // ss8[i] = sum of x^2 over elements 8i..8i+7: what the first phase of a step starts from.
 tb_status launch_step_embed(const float* table, const int32_t* tokens, const int32_t* offsets, const float* norm_w,
@@ -244,6 +245,7 @@ int step_fault_flag();
 // Test hook: cycles a device-side wait of the step kernel may take before it gives up (0 = default).
 void set_step_wait_limit(long long cycles);
 void set_step_debug(int flags);
+tb_status step_wait_probe(long long limit_cycles);
 
 tb_status launch_rms_norm(const float* x, const float* w, float* out, int64_t m, int64_t n,
                           float eps, cudaStream_t stream);

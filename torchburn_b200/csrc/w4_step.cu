@@ -46,6 +46,10 @@ constexpr int kXBufBytes = kMaxK * 4;
 constexpr int kPartFloats = 2 * 2 * kCW * 33;   // [buffer][matrix][warp][row]
 constexpr int kSmemBytes = kStages * kStageBytes + kXBufBytes + kPartFloats * 4;   // + kBarBytes of barriers
 constexpr int kBarBytes = 2 * kStages * 8 + 16;
+#ifndef TB_STEP_BATCH
+#define TB_STEP_BATCH 8
+#endif
+constexpr int kBatch = TB_STEP_BATCH;     // rows of a round whose loads a lane issues before the products
 constexpr int kAttnRows = 32;             // K (or V) rows per ring stage
 constexpr int kChunkRows = 512;           // positions whose scores are held in shared memory at a time
 constexpr int kMaxSplits = 64;            // partials per head the merge reads with two loads per lane
@@ -128,16 +132,22 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
 // All consumer threads of all CTAs.  Writes made before it by any consumer thread of the grid are
 // visible after it to every consumer thread (bar.sync orders the CTA's threads before thread 0's
 // release; thread 0's acquire is ordered before the CTA's threads by the second bar.sync).
-__device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned target, volatile int* s_abort, long long limit,
+// The arrivals are spread over four counters (CTA number mod 4) so that they do not queue on one
+// address; a waiter reads all four with one 16-byte load.  `round` counts the barriers so far.
+__device__ __forceinline__ void grid_barrier(unsigned* counters, unsigned round, volatile int* s_abort, long long limit,
                                              int tid) {
   consumer_sync();
   if (tid == 0) {
-    __threadfence();
-    atomicAdd(counter, 1u);
+    // release: the CTA's writes (ordered before this by the bar.sync) become visible before the count
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counters + (blockIdx.x & 3)) : "memory");
     if (!*s_abort) {
+      const unsigned g = gridDim.x;
+      const unsigned t0c = round * ((g + 3) >> 2), t1c = round * ((g + 2) >> 2), t2c = round * ((g + 1) >> 2), t3c = round * (g >> 2);
       long long t0 = 0;
       for (uint32_t i = 0;; ++i) {
-        if (ld_acquire_gpu(counter) >= target) break;
+        unsigned c0, c1, c2, c3;
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3) : "l"(counters) : "memory");
+        if (c0 >= t0c && c1 >= t1c && c2 >= t2c && c3 >= t3c) break;
         if ((i & 31) == 31) {
           if (t0 == 0) t0 = clock64();
           else if (clock64() - t0 > limit || *reinterpret_cast<volatile int*>(&g_step_fault)) {
@@ -188,8 +198,9 @@ __device__ __forceinline__ float transpose_reduce8(float (&p)[8], int lane) {
 // S = sum_i q_i), so no large terms cancel in floating point.
 __device__ __forceinline__ float idot_block(const uint4 wv, const uint32_t (&xq)[24], int s8hi, int s8lo) {
   const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
-  uint32_t d0 = 0, d1 = 0, e0 = 0, e1 = 0;
-  int d2 = 0, e2 = 0;
+  // the accumulators start at the offset term; d0 and d1 wrap modulo 2^32, their combination is exact
+  uint32_t d0 = (uint32_t)(-s8lo), d1 = 0;
+  int d2 = -s8hi;
 #pragma unroll
   for (int wd = 0; wd < 4; ++wd) {
     const uint32_t t = w[wd] & 0x0F0F0F0Fu;
@@ -197,14 +208,12 @@ __device__ __forceinline__ float idot_block(const uint4 wv, const uint32_t (&xq)
     d0 = dp4a_uu(t, xq[wd * 6 + 0], d0);
     d1 = dp4a_uu(t, xq[wd * 6 + 1], d1);
     d2 = dp4a_us(t, xq[wd * 6 + 2], d2);
-    e0 = dp4a_uu(u, xq[wd * 6 + 3], e0);
-    e1 = dp4a_uu(u, xq[wd * 6 + 4], e1);
-    e2 = dp4a_us(u, xq[wd * 6 + 5], e2);
+    d0 = dp4a_uu(u, xq[wd * 6 + 3], d0);
+    d1 = dp4a_uu(u, xq[wd * 6 + 4], d1);
+    d2 = dp4a_us(u, xq[wd * 6 + 5], d2);
   }
-  d0 += e0; d1 += e1; d2 += e2;
-  const int lo = (int)(d0 + (d1 << 8)) - s8lo;   // |lo| < 2^26
-  const int hi = d2 - s8hi;
-  return fmaf(65536.0f, (float)hi, (float)lo);
+  const int lo = (int)(d0 + (d1 << 8));   // |lo| < 2^26
+  return fmaf(65536.0f, (float)d2, (float)lo);
 }
 
 // Balanced, contiguous share of `rounds` 8-row rounds for CTA `cta` of `grid`; the CTAs that take
@@ -360,8 +369,8 @@ struct LaneX {
 };
 
 // The rounds of one projection phase.  One code path for every stage shape: a round is 8 rows of
-// each matrix, spread over 8 / rs consecutive stages; a lane takes them as two batches of 4 rows
-// (loads first, then the products: four independent rows in flight).
+// each matrix, spread over 8 / rs consecutive stages; a lane takes them in batches of kBatch rows
+// (loads first, then the products: that many independent rows in flight).
 __device__ __forceinline__ uint32_t gemv_rounds(const StepPhase& d, const StepParams& p, uint32_t it,
                                                 const int tid, const int ph, const LaneX& X) {
   const Shared sh = shared_layout();
@@ -417,12 +426,12 @@ __device__ __forceinline__ uint32_t gemv_rounds(const StepPhase& d, const StepPa
       for (int q = 0; q < NW; ++q) {
         float pa[8];
 #pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-          uint4 wv[4];
-          float sc[4];
+        for (int hb = 0; hb < 8 / kBatch; ++hb) {
+          uint4 wv[kBatch];
+          float sc[kBatch];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int row = hb * 4 + j;                       // row of the round
+          for (int j = 0; j < kBatch; ++j) {
+            const int row = hb * kBatch + j;                       // row of the round
             const uint32_t is = it + (uint32_t)(row >> rs_shift);
             const unsigned char* base = sh.ring + (size_t)(is % kStages) * kStageBytes + q * mat_bytes;
             const int r = row & (RS - 1);                     // row inside its stage
@@ -430,9 +439,9 @@ __device__ __forceinline__ uint32_t gemv_rounds(const StepPhase& d, const StepPa
             sc[j] = *reinterpret_cast<const float*>(base + r * srow_bytes + sofs);
           }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < kBatch; ++j) {
             const float val = (sc[j] * sx) * idot_block(wv[j], X.dig, s8hi, s8lo);
-            pa[hb * 4 + j] = (has_part && ok) ? val : 0.f;
+            pa[hb * kBatch + j] = (has_part && ok) ? val : 0.f;
           }
         }
         const float v = transpose_reduce8(pa, lane);
@@ -954,7 +963,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
   }
 
   uint32_t it = 0;
-  unsigned target = 0;
+  unsigned round = 0;
 #pragma unroll 1
   for (int ph = 0; ph < p.nphases; ++ph) {
     const StepPhase& d = s_desc[ph & 1];
@@ -970,8 +979,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
     }
     step_mark(p, ph, 2, tid);
     if (ph + 1 < p.nphases) {
-      target += gridDim.x;
-      grid_barrier(p.sync, target, sh.s_abort, p.wait_cycles, tid);
+      ++round;
+      grid_barrier(p.sync, round, sh.s_abort, p.wait_cycles, tid);
     }
   }
   // The last CTA to leave puts the barrier words back to zero for the next launch (every CTA has
@@ -982,11 +991,38 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
       *reinterpret_cast<volatile int*>(p.host_fault) = 1;
       __threadfence_system();
     }
-    if (atomicAdd(p.sync + 1, 1u) == gridDim.x - 1) {
-      p.sync[0] = 0u;
-      p.sync[1] = 0u;
+    if (atomicAdd(p.sync + 4, 1u) == gridDim.x - 1) {
+      p.sync[0] = 0u; p.sync[1] = 0u; p.sync[2] = 0u; p.sync[3] = 0u;
+      p.sync[4] = 0u;
       __threadfence();
     }
+  }
+}
+
+// The two bounded waits of the step kernel on conditions that nothing fulfils: an mbarrier phase
+// nobody completes and a grid barrier one arrival short.  With a short limit both must give up,
+// raise the fault word and let the kernel end (one CTA of one warp; nothing else is touched).
+__global__ void __launch_bounds__(32) wait_probe_kernel(unsigned* counters, long long limit, int* out) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const bool a = mbar_wait(&bar, 0u, &s_abort, limit);            // nobody arrives on `bar`
+    out[0] = a ? 0 : 1;
+    s_abort = 0;
+    // a lone CTA waits for a second arrival that never comes (round 1 of a grid of "2")
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counters) : "memory");
+    long long t0 = clock64();
+    bool gave_up = false;
+    while (ld_acquire_gpu(counters) < 2u) {
+      if (clock64() - t0 > limit) { gave_up = true; atomicExch(&g_step_fault, 1); break; }
+    }
+    out[1] = gave_up ? 1 : 0;
   }
 }
 
@@ -1031,6 +1067,31 @@ int step_fault_flag() {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_step_fault, sizeof(int)) != cudaSuccess) return -1;
   return v;
+}
+
+// Test hook: see wait_probe_kernel.  Returns TB_ERR_TIMEOUT when both waits gave up as they
+// must (and clears the fault word they raised), TB_ERR_CUDA on any other outcome.
+tb_status step_wait_probe(long long limit_cycles) {
+  if (limit_cycles < 1000 || limit_cycles > 2000000000ll) return fail(TB_ERR_ARG, "wait probe: limit of %lld cycles is outside [1e3, 2e9]", limit_cycles);
+  unsigned* ctr = nullptr;
+  int* out = nullptr;
+  TB_CUDA_TRY(cudaMalloc((void**)&ctr, 64));
+  cudaError_t e = cudaMalloc((void**)&out, 64);
+  if (e != cudaSuccess) { cudaFree(ctr); return fail(TB_ERR_OOM, "wait probe: %s", cudaGetErrorString(e)); }
+  cudaMemset(ctr, 0, 64);
+  cudaMemset(out, 0xff, 64);
+  wait_probe_kernel<<<1, 32>>>(ctr, limit_cycles, out);
+  int h[2] = {-1, -1};
+  e = cudaMemcpy(h, out, sizeof(h), cudaMemcpyDeviceToHost);
+  const int flag = step_fault_flag();
+  const int zero = 0;
+  cudaMemcpyToSymbol(g_step_fault, &zero, sizeof(int));
+  cudaFree(ctr);
+  cudaFree(out);
+  if (e != cudaSuccess) return fail(TB_ERR_CUDA, "wait probe: %s", cudaGetErrorString(e));
+  if (h[0] == 1 && h[1] == 1 && flag == 1)
+    return fail(TB_ERR_TIMEOUT, "a bounded device-side wait ran out (probe: both waits gave up after %lld cycles)", limit_cycles);
+  return fail(TB_ERR_CUDA, "wait probe: unexpected outcome (mbarrier %d, grid barrier %d, fault word %d)", h[0], h[1], flag);
 }
 
 int w4_step_rows_per_stage(int64_t k, int g, int nw) {
@@ -1108,6 +1169,34 @@ tb_status launch_w4_step(const StepProgram& g, cudaStream_t stream) {
   if (g.head_dim == 128) TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4_step_kernel<128>, p));
   else TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4_step_kernel<64>, p));
   return TB_OK;
+}
+
+// One projection through the step kernel's code path (a program of a single phase): out = W x,
+// or silu(W x) * (W2 x) when w2 is given.  For tests and profiling of that path at any shape.
+tb_status launch_w4_step_gemv(const GemvArgs& a, cudaStream_t stream) {
+  const int nw = a.w2 ? 2 : 1;
+  if (a.m != 1 || !w4_step_supports(a.n, a.k, a.g, nw)) return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: step kernel projection [%lld, %lld] group %d", (long long)a.n, (long long)a.k, a.g);
+  if (a.norm_w) return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: step kernel projection takes pre-weighted activations (x_ss8), not norm weights");
+  const int grid = w4_step_grid();
+  if (grid <= 0) return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: the step kernel cannot run on this device");
+  StepPhase q;
+  q.kind = 0; q.n = (int)a.n; q.k = (int)a.k; q.ng = (int)(a.k / a.g); q.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
+  q.nw = nw; q.rs = w4_step_rows_per_stage(a.k, a.g, nw); q.rot = 0; q.eps = a.eps;
+  q.w[0] = a.w; q.sc[0] = a.scales; q.bias[0] = a.bias; q.w[1] = a.w2; q.sc[1] = a.scales2; q.bias[1] = a.bias2;
+  q.x = a.x; q.x_ss8 = a.x_ss8; q.resid = a.resid; q.out = a.out;
+  q.out_scaled = a.out_scaled; q.out_scale_w = a.out_scale_w; q.out_ss8 = a.out_ss8;
+  // the phase descriptor and the barrier words live in one small allocation of the stream's pool
+  char* blk = nullptr;
+  TB_CUDA_TRY(cudaMallocAsync((void**)&blk, 512, stream));
+  TB_CUDA_TRY(cudaMemsetAsync(blk + 256, 0, 64, stream));
+  TB_CUDA_TRY(cudaMemcpyAsync(blk, &q, sizeof(q), cudaMemcpyHostToDevice, stream));
+  StepProgram g;
+  g.phases = reinterpret_cast<const StepPhase*>(blk); g.nphases = 1; g.grid = grid;
+  g.sync = reinterpret_cast<unsigned*>(blk + 256);
+  g.head_dim = 128; g.num_heads = 1; g.num_kv_heads = 1; g.nc = 1; g.max_seq_len = 1;
+  const tb_status st = launch_w4_step(g, stream);
+  cudaFreeAsync(blk, stream);
+  return st;
 }
 
 tb_status launch_step_embed(const float* table, const int32_t* tokens, const int32_t* offsets, const float* norm_w,

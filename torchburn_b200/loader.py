@@ -25,7 +25,10 @@ import torch
 from ._lib import check, lib
 from .quantization import quantize_weight_int4_grouped
 
-CACHE_V1 = "torchburn_int4_g{g}.safetensors"
+# The reference's literal file names: "g64" is part of the name whatever the group size of the
+# file's contents (python/torchburn/llm/loader.py:92-95, 150-153), so that a cache written by
+# either side is found by the other; the group size is read from the shape of the scales.
+CACHE_V1 = "torchburn_int4_g64.safetensors"
 CACHE_V2 = "torchburn_int4_g64_v2.safetensors"
 
 # Names under which the pieces of a layer appear in checkpoints (loader.py:236-330).
@@ -149,7 +152,7 @@ def save_cache(sd: Mapping[str, torch.Tensor], path: str) -> str:
 
 def find_cache(model_dir: str, group_size: int = 64) -> Optional[str]:
     """The cache the reference would pick for this directory: v2 first, then v1 (loader.py:92-112)."""
-    for name in ([CACHE_V2] if group_size == 64 else []) + [CACHE_V1.format(g=group_size)]:
+    for name in ([CACHE_V2] if group_size == 64 else []) + [CACHE_V1]:
         for cand in (os.path.join(model_dir, name),
                      os.path.join(os.path.expanduser("~/.cache/torchburn"), f"{os.path.basename(os.path.normpath(model_dir))}_{name}")):
             if os.path.isfile(cand):
