@@ -69,6 +69,7 @@ struct tb_decoder {
   // The whole batch-1 step as one persistent kernel (w4_step.cu): phase list, barrier words,
   // attention partials and a host-mapped word the kernel raises when a bounded wait ran out.
   bool fused_step = false;
+  bool logits_shared = false;   // tensor parallel: d->logits points into the peer-mapped block
   StepPhase* d_phases = nullptr;
   unsigned* d_step_sync = nullptr;
   float *step_part_o = nullptr, *step_part_ml = nullptr;
@@ -333,7 +334,10 @@ tb_status run_step(tb_decoder* d, int b, bool greedy) {
 // (otherwise the decoder keeps the chain of single kernels).
 tb_status build_step_program(tb_decoder* d) {
   d->fused_step = false;
-  if (d->tp != 1 || (d->cfg.flags & (TB_DECODER_NO_FUSED_STEP | TB_DECODER_NO_GRAPH))) return TB_OK;
+  if (d->cfg.flags & (TB_DECODER_NO_FUSED_STEP | TB_DECODER_NO_GRAPH)) return TB_OK;
+  StepTp tpa;
+  if (d->tp > 1 && !tp_step_areas(d->tpst, &tpa)) return TB_OK;   // no peer memory: the chain of kernels with NCCL
+  if (d->d_phases) return TB_OK;
   if (d->hd != 64 && d->hd != 128) return TB_OK;
   const int G = d->G;
   if (d->H % 32 != 0 || !w4_step_supports(d->tq_l, d->H, G, 1) || !w4_step_supports(d->H, d->q_dim_l, G, 1) ||
@@ -344,7 +348,15 @@ tb_status build_step_program(tb_decoder* d) {
   if (grid <= 0 || nc <= 0) return TB_OK;
 
   std::vector<StepPhase> ph;
-  int rot = 0;
+  int rot = 0, n_exch = 0;
+  const bool tpm = d->tp > 1;
+  // tensor parallel: the sum over the ranks of a row-parallel projection's rows, with the residual
+  auto exchange = [&](const float* next_norm_w) {
+    StepPhase q;
+    q.kind = 3; q.n = (int)d->H; q.xi = n_exch++;
+    q.resid = d->x; q.out = d->x; q.out_scaled = d->xn; q.out_scale_w = next_norm_w; q.out_ss8 = d->ss8;
+    return q;
+  };
   auto gemv = [&](int64_t n, int64_t k, int nw) {
     StepPhase q;
     q.kind = 0; q.n = (int)n; q.k = (int)k; q.ng = (int)(k / G); q.gshift = G == 32 ? 0 : (G == 64 ? 1 : 2);
@@ -371,9 +383,15 @@ tb_status build_step_program(tb_decoder* d) {
     }
     {  // F + G
       StepPhase q = gemv(d->H, d->q_dim_l, 1);
-      q.w[0] = W.o_w; q.sc[0] = W.o_s; q.x = d->attn; q.resid = d->x; q.out = d->x;
-      q.out_scaled = d->xn; q.out_scale_w = W.post_norm_w; q.out_ss8 = d->ss8;
-      ph.push_back(q);
+      q.w[0] = W.o_w; q.sc[0] = W.o_s; q.x = d->attn;
+      if (!tpm) {
+        q.resid = d->x; q.out = d->x; q.out_scaled = d->xn; q.out_scale_w = W.post_norm_w; q.out_ss8 = d->ss8;
+        ph.push_back(q);
+      } else {
+        q.tp_mode = 1; q.xi = n_exch;
+        ph.push_back(q);
+        ph.push_back(exchange(W.post_norm_w));
+      }
     }
     {  // H + I
       StepPhase q = gemv(d->I_l, d->H, 2);
@@ -382,15 +400,22 @@ tb_status build_step_program(tb_decoder* d) {
     }
     {  // I' + J
       StepPhase q = gemv(d->H, d->I_l, 1);
-      q.w[0] = W.down_w; q.sc[0] = W.down_s; q.x = d->h; q.resid = d->x; q.out = d->x;
-      q.out_scaled = d->xn; q.out_ss8 = d->ss8;
-      q.out_scale_w = l + 1 < d->L ? d->layers[l + 1].input_norm_w : d->final_norm_w;
-      ph.push_back(q);
+      q.w[0] = W.down_w; q.sc[0] = W.down_s; q.x = d->h;
+      const float* next_norm_w = l + 1 < d->L ? d->layers[l + 1].input_norm_w : d->final_norm_w;
+      if (!tpm) {
+        q.resid = d->x; q.out = d->x; q.out_scaled = d->xn; q.out_ss8 = d->ss8; q.out_scale_w = next_norm_w;
+        ph.push_back(q);
+      } else {
+        q.tp_mode = 1; q.xi = n_exch;
+        ph.push_back(q);
+        ph.push_back(exchange(next_norm_w));
+      }
     }
   }
   {  // 3 + 4: lm_head on the pre-weighted x
     StepPhase q = gemv(d->V_l, d->H, 1);
     q.w[0] = d->lm_w; q.sc[0] = d->lm_s; q.x = d->xn; q.x_ss8 = d->ss8; q.out = d->logits;
+    if (tpm) { q.tp_mode = 2; q.xi = (int)(d->rank * d->V_l); }   // this rank's slice into every rank's logits
     ph.push_back(q);
   }
   TB_TRY(dalloc(&d->d_phases, ph.size()));
@@ -409,6 +434,7 @@ tb_status build_step_program(tb_decoder* d) {
   g.qkv = d->qkv; g.attn = d->attn; g.cos_t = d->cos_t; g.sin_t = d->sin_t; g.offsets = d->d_eff;
   g.part_o = d->step_part_o; g.part_ml = d->step_part_ml;
   g.num_heads = d->nh_l; g.num_kv_heads = d->nkv_l; g.head_dim = d->hd; g.nc = nc; g.max_seq_len = d->S;
+  if (tpm) { g.tp = tpa; g.n_exchanges = n_exch; }
   d->fused_step = true;
   return TB_OK;
 }
@@ -639,7 +665,8 @@ void tb_decoder_destroy(tb_decoder* d) {
   cudaFree(d->xn); cudaFree(d->ss8);
   cudaFree(d->d_phases); cudaFree(d->d_step_sync); cudaFree(d->step_part_o); cudaFree(d->step_part_ml);
   if (d->h_step_fault) cudaFreeHost(d->h_step_fault);
-  cudaFree(d->x); cudaFree(d->qkv); cudaFree(d->attn); cudaFree(d->h); cudaFree(d->logits);
+  cudaFree(d->x); cudaFree(d->qkv); cudaFree(d->attn); cudaFree(d->h);
+  if (!d->logits_shared) cudaFree(d->logits);
   cudaFree(d->partial); cudaFree(d->logits_l);
   cudaFree(d->d_tokens); cudaFree(d->d_offsets); cudaFree(d->d_eff); cudaFree(d->d_hist); cudaFree(d->d_hist_pos);
   cudaFreeHost(d->h_io); cudaFreeHost(d->h_feed);
@@ -964,7 +991,15 @@ tb_status tb_decoder_tp_init(tb_decoder* d, const uint8_t id[128], tb_allgather_
   if (d->tp < 2) return fail(TB_ERR_ARG, "tb_decoder_tp_init: the decoder was created with tp_size 1");
   if (d->tpst) return fail(TB_ERR_ARG, "tb_decoder_tp_init: already initialised");
   TB_TRY(tp_create(&d->tpst, d->rank, d->tp, id, (size_t)d->B * d->H, allgather, user,
-                   (d->cfg.flags & TB_DECODER_NCCL_ONLY) != 0));
+                   (d->cfg.flags & TB_DECODER_NCCL_ONLY) != 0, (size_t)d->H, (size_t)d->B * d->V));
+  if (float* shared_logits = tp_step_logits(d->tpst)) {
+    // the gathered logits live in the block every rank has mapped: the step kernel of each rank
+    // stores its vocabulary slice straight into every rank's copy
+    cudaFree(d->logits);
+    d->logits = shared_logits;
+    d->logits_shared = true;
+  }
+  TB_TRY(build_step_program(d));
   // warm-up with an out-of-range token (collective: every rank runs it)
   int64_t tok = -1, off = 0;
   const bool g = d->use_graph;

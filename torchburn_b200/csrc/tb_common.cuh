@@ -183,7 +183,8 @@ tb_status static_attention_scratch(void** ptr);
 // ---- the whole decode step as one persistent kernel (w4_step.cu) ------------------------------
 // A step is a list of phases that every CTA of one cooperative grid walks in order, with a
 // grid-wide barrier after each: projections (kind 0), the split-K attention over one layer's
-// cache (kind 1) and the merge of its partials (kind 2).
+// cache (kind 1), the merge of its partials (kind 2) and, tensor parallel, the sum of the ranks'
+// partial rows with the residual (kind 3; n rows, exchange number xi, no barrier in front of it).
 struct StepPhase {
   int kind = 0;
   int n = 0;            // projection: output rows (row pairs for the SwiGLU form)
@@ -194,6 +195,9 @@ struct StepPhase {
   int nw = 1;           // 2 = gate/up pair with the SwiGLU epilogue
   int rot = 0;          // rotation of the balanced split of the 8-row rounds over the CTAs
   float eps = 0.f;
+  int tp_mode = 0;      // tensor parallel: 1 = push the rows to every rank's receive area (exchange number xi),
+                        // 2 = store them into every rank's logits at column offset xi
+  int xi = 0;
   int pad = 0;
   const uint8_t* w[2] = {nullptr, nullptr};
   const float* sc[2] = {nullptr, nullptr};
@@ -207,8 +211,20 @@ struct StepPhase {
   float* out_ss8 = nullptr;          // optional sums of squares of out per 8 rows
   float* k_cache = nullptr;          // attention: this layer's [Hkv, max_seq_len, d]
   float* v_cache = nullptr;
+  const void* reserved = nullptr;
 };
-static_assert(sizeof(StepPhase) == 160, "StepPhase is copied as ten 16-byte words");
+constexpr int kStepPhaseWords = 11;
+static_assert(sizeof(StepPhase) == 16 * kStepPhaseWords, "StepPhase is copied as 16-byte words");
+
+// Tensor-parallel side of the step kernel: pointers into every rank's shared block (peer memory).
+struct StepTp {
+  int rank = 0, size = 1, hidden = 0;
+  uint2* recv[8] = {};          // [2][size][hidden] {partial, exchange number}: rank r's receive area
+  float* logits[8] = {};        // rank r's copy of the gathered logits
+  uint32_t* flags[8] = {};      // rank r's words [size]: source s stores the exchange number at [s]
+  uint32_t* epoch = nullptr;    // this rank: exchanges completed by earlier launches
+  int* err = nullptr;
+};
 
 struct StepProgram {
   const StepPhase* phases = nullptr;   // device array
@@ -226,6 +242,8 @@ struct StepProgram {
   int num_heads = 0, num_kv_heads = 0, head_dim = 0;
   int nc = 0;                          // CTAs per kv head in the attention phases
   int64_t max_seq_len = 0;
+  StepTp tp;                           // size 1: one GPU
+  int n_exchanges = 0;                 // in-kernel exchanges per launch (tensor parallel)
 };
 // CTAs of the step kernel on the current device (0 when it cannot run there).
 int w4_step_grid();

@@ -274,6 +274,10 @@ struct TpState {
   int calls = 0;              // host-side call parity selects the buffer a projection writes to
   size_t ll_off = 0;          // low-latency receive area: [2][size][kLLLines] lines of 16 bytes
   int ll_calls = 0;
+  // areas of the persistent step kernel (one launch per token, exchanges inside the kernel)
+  size_t step_recv_off = 0;   // [2][size][hidden] entries of 8 bytes {partial, exchange number}
+  size_t step_logits_off = 0; // [logit_floats] floats: every rank stores its slice into every peer's copy
+  size_t hidden = 0, logit_floats = 0;
   float* reduced = nullptr;   // NCCL path: the summed partial
 };
 
@@ -367,6 +371,26 @@ tb_status tp_allgather_logits(TpState* st, const float* logits_l, float* logits,
   return TB_OK;
 }
 
+// Peer-visible areas of the persistent step kernel: for every rank the receive area of the
+// in-kernel exchanges, the gathered logits and the word where peers announce their logit slices;
+// this rank's exchange counter and error word.
+bool tp_step_areas(TpState* st, StepTp* t) {
+  if (!st || !st->fused || st->hidden == 0) return false;
+  t->rank = st->rank; t->size = st->size; t->hidden = (int)st->hidden;
+  for (int r = 0; r < st->size; ++r) {
+    t->recv[r] = reinterpret_cast<uint2*>(st->peer_block[r] + st->step_recv_off);
+    t->logits[r] = reinterpret_cast<float*>(st->peer_block[r] + st->step_logits_off);
+    t->flags[r] = reinterpret_cast<uint32_t*>(st->peer_block[r] + st->flags_off) + 32;   // words 32..39: one per source rank
+  }
+  uint32_t* words = reinterpret_cast<uint32_t*>(st->block + st->flags_off);
+  t->epoch = words + 24;
+  t->err = reinterpret_cast<int*>(words + 18);
+  return true;
+}
+float* tp_step_logits(TpState* st) {
+  return st && st->fused && st->logit_floats ? reinterpret_cast<float*>(st->block + st->step_logits_off) : nullptr;
+}
+
 int tp_error_flag(TpState* st) {
   if (!st || !st->fused) return 0;
   int v = 0;
@@ -388,7 +412,7 @@ void tp_destroy(TpState* st) {
 }
 
 tb_status tp_create(TpState** out, int rank, int size, const uint8_t id[128], size_t max_count,
-                    tb_allgather_fn allgather, void* user, bool nccl_only) {
+                    tb_allgather_fn allgather, void* user, bool nccl_only, size_t hidden, size_t logit_floats) {
   *out = nullptr;
   if (size < 2 || size > kMaxRanks || rank < 0 || rank >= size) return fail(TB_ERR_ARG, "tensor parallel size %d / rank %d (supported: 2..%d ranks)", size, rank, kMaxRanks);
   NcclApi* api = nccl();
@@ -408,7 +432,10 @@ tb_status tp_create(TpState** out, int rank, int size, const uint8_t id[128], si
   if (allgather && !nccl_only) {
     st->flags_off = 2 * st->max_count * sizeof(float);
     st->ll_off = st->flags_off + 256;
-    const size_t bytes = st->ll_off + (size_t)2 * size * kLLLines * sizeof(uint4);
+    st->hidden = hidden; st->logit_floats = logit_floats;
+    st->step_recv_off = st->ll_off + (size_t)2 * size * kLLLines * sizeof(uint4);
+    st->step_logits_off = st->step_recv_off + (((size_t)2 * size * hidden * 8 + 255) & ~(size_t)255);
+    const size_t bytes = st->step_logits_off + ((logit_floats * sizeof(float) + 255) & ~(size_t)255);
     e = cudaMalloc(&st->block, bytes);
     if (e != cudaSuccess) return bail(fail(TB_ERR_OOM, "tp: %s", cudaGetErrorString(e)));
     cudaMemset(st->block, 0, bytes);

@@ -20,8 +20,13 @@ tb_status tp_allgather_logits(TpState* st, const float* logits_l, float* logits,
 void tp_destroy(TpState* st);
 // Communicator (NCCL) and, when `allgather` is given and nccl_only is false, the peer-memory
 // exchange buffers.  Collective: every rank calls it.  max_count = floats per partial.
+// hidden / logit_floats size the areas of the persistent step kernel (0: none).
 tb_status tp_create(TpState** out, int rank, int size, const uint8_t id[128], size_t max_count,
-                    tb_allgather_fn allgather, void* user, bool nccl_only);
+                    tb_allgather_fn allgather, void* user, bool nccl_only, size_t hidden = 0, size_t logit_floats = 0);
+// Fills `t` with the peer-visible areas of the step kernel; false when there are none.
+bool tp_step_areas(TpState* st, StepTp* t);
+// This rank's copy of the gathered logits inside the shared block (null when there is none).
+float* tp_step_logits(TpState* st);
 // Where the row-parallel projection of the NEXT tp_allreduce_residual call must write its
 // partial (the peer-visible buffer on the fused path, `fallback` otherwise).
 float* tp_partial_buffer(TpState* st, float* fallback);

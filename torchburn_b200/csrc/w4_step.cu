@@ -75,6 +75,13 @@ struct StepParams {
   float scale;
   long long wait_cycles;
   int debug;                // test hook: bit 0 = consume the stages without multiplying
+  // tensor parallel (tp_size 1: none of it is used)
+  int tp_rank, tp_size, tp_hidden, n_exchanges;
+  uint2* tp_recv[8];
+  float* tp_logits[8];
+  uint32_t* tp_flags[8];
+  uint32_t* tp_epoch;
+  uint32_t epoch_base;      // copy of *tp_epoch taken when the kernel starts (in the shared copy of the parameters)
   unsigned long long* tl;   // optional timestamps (step_mark)
 };
 
@@ -480,8 +487,18 @@ __device__ __forceinline__ uint32_t gemv_rounds(const StepPhase& d, const StepPa
           v = a0 * inv_rms + pre_b0;
           if (d.resid) v = pre_res + v;
         }
-        d.out[row] = v;
-        if (d.out_scaled != nullptr) d.out_scaled[row] = v * pre_sw;
+        if (d.tp_mode == 0) {
+          d.out[row] = v;
+          if (d.out_scaled != nullptr) d.out_scaled[row] = v * pre_sw;
+        } else if (d.tp_mode == 1) {
+          // this rank's partial row into every rank's receive area, tagged with the exchange number
+          const uint32_t e = p.epoch_base + (uint32_t)d.xi;
+          const size_t at = ((size_t)(e & 1u) * p.tp_size + p.tp_rank) * p.tp_hidden + row;
+          for (int q = 0; q < p.tp_size; ++q)
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.tp_recv[q] + at), "r"(__float_as_uint(v)), "r"(e + 1u) : "memory");
+        } else {
+          for (int q = 0; q < p.tp_size; ++q) p.tp_logits[q][(size_t)d.xi + row] = v;
+        }
         v_out = v;
       }
       if (d.out_ss8 != nullptr) {
@@ -935,6 +952,58 @@ __device__ __forceinline__ void merge_phase(const StepParams& p, const int tid) 
   }
 }
 
+// Exchange phase (tensor parallel): x[r] += sum over the ranks of their partial row r, plus the
+// next norm's pre-weighted copy and the sums of squares.  A warp takes 8 rows; lane (s, r) polls
+// the entries of sources s, s + 4 for row r until they carry this exchange's number (the
+// producing projection stored them straight into this rank's receive area), the four lanes of a
+// row are added in a fixed order - the same on every rank, so every rank holds the same x.
+__device__ __forceinline__ void exch_phase(const StepPhase& d, const StepParams& p, const int tid, volatile int* s_abort) {
+  const int lane = tid & 31, warp = tid >> 5;
+  const int H = d.n, size = p.tp_size;
+  const uint32_t e = p.epoch_base + (uint32_t)d.xi;
+  const uint2* base = p.tp_recv[p.tp_rank] + (size_t)(e & 1u) * size * p.tp_hidden;
+  const long long limit = p.wait_cycles;
+  for (int o = (int)blockIdx.x + warp * (int)gridDim.x; o < (H >> 3); o += (int)gridDim.x * kCW) {
+    const int row = o * 8 + (lane & 7);
+    float sum = 0.f;
+    for (int src = lane >> 3; src < size; src += 4) {
+      const uint2* at = base + (size_t)src * p.tp_hidden + row;
+      uint32_t v0, v1;
+      long long t0 = 0;
+      for (uint32_t spin = 0;; ++spin) {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1) : "l"(at) : "memory");
+        if (v1 == e + 1u) break;
+        if ((spin & 63) == 63) {
+          if (*s_abort) { v0 = 0u; break; }
+          if (t0 == 0) t0 = clock64();
+          else if (clock64() - t0 > limit || *reinterpret_cast<volatile int*>(&g_step_fault)) {
+            *s_abort = 1;
+            atomicExch(&g_step_fault, 1);
+            v0 = 0u;
+            break;
+          }
+        }
+      }
+      sum += __uint_as_float(v0);
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+    float xv = 0.f;
+    if (lane < 8) {
+      xv = __ldcg(d.resid + row) + sum;
+      d.out[row] = xv;
+      if (d.out_scaled != nullptr) d.out_scaled[row] = xv * __ldg(d.out_scale_w + row);
+    }
+    if (d.out_ss8 != nullptr) {
+      float sq = xv * xv;
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      if (lane == 0) d.out_ss8[o] = sq;
+    }
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams kp) {
   __shared__ __align__(16) StepPhase s_desc[2];
@@ -947,6 +1016,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
   const int tid = threadIdx.x, warp = tid >> 5;
   if (tid == 0) {
     s_params = kp;
+    if (kp.tp_size > 1) s_params.epoch_base = *kp.tp_epoch;
     *sh.s_abort = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
@@ -954,7 +1024,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (tid < 10) reinterpret_cast<int4*>(&s_desc[0])[tid] = __ldg(reinterpret_cast<const int4*>(kp.phases) + tid);
+  if (tid < kStepPhaseWords) reinterpret_cast<int4*>(&s_desc[0])[tid] = __ldg(reinterpret_cast<const int4*>(kp.phases) + tid);
   __syncthreads();
 
   if (warp == kCW) {
@@ -968,23 +1038,52 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
   for (int ph = 0; ph < p.nphases; ++ph) {
     const StepPhase& d = s_desc[ph & 1];
     step_mark(p, ph, 0, tid);
-    if (ph + 1 < p.nphases && tid < 10)   // the next descriptor travels while this phase runs
+    if (ph + 1 < p.nphases && tid < kStepPhaseWords)   // the next descriptor travels while this phase runs
       reinterpret_cast<int4*>(&s_desc[(ph + 1) & 1])[tid] = __ldg(reinterpret_cast<const int4*>(p.phases + ph + 1) + tid);
     if (d.kind == 0) {
       it = gemv_phase(d, p, it, tid, ph);
     } else if (d.kind == 1) {
       it = attn_phase<D>(d, p, it, tid, ph);
-    } else {
+    } else if (d.kind == 2) {
       merge_phase<D>(p, tid);
+    } else {
+      exch_phase(d, p, tid, sh.s_abort);
     }
     step_mark(p, ph, 2, tid);
-    if (ph + 1 < p.nphases) {
+    // (a projection whose rows go to the ranks' receive areas is followed by the exchange phase,
+    // which waits on those rows themselves: no barrier in between)
+    if ((ph + 1 < p.nphases || p.tp_size > 1) && !(d.kind == 0 && d.tp_mode == 1)) {
       ++round;
       grid_barrier(p.sync, round, sh.s_abort, p.wait_cycles, tid);
     }
   }
   // The last CTA to leave puts the barrier words back to zero for the next launch (every CTA has
   // passed its last barrier by the time it takes an exit ticket).
+  if (p.tp_size > 1 && blockIdx.x == 0 && tid == 0) {
+    // Every CTA of this rank has stored its logit rows into every rank's copy (the barrier above).
+    // Tell the peers, then wait until every peer has told us: the logits are complete everywhere.
+    const uint32_t fin = p.epoch_base + (uint32_t)p.n_exchanges + 1u;
+    __threadfence_system();
+    for (int q = 0; q < p.tp_size; ++q)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[q] + p.tp_rank), "r"(fin) : "memory");
+    const long long limit = p.wait_cycles;
+    for (int src = 0; src < p.tp_size && !*sh.s_abort; ++src) {
+      long long t0 = 0;
+      for (uint32_t spin = 0;; ++spin) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.tp_flags[p.tp_rank] + src) : "memory");
+        if (v == fin) break;
+        if ((spin & 63) == 63) {
+          if (t0 == 0) t0 = clock64();
+          else if (clock64() - t0 > limit || *reinterpret_cast<volatile int*>(&g_step_fault)) {
+            *sh.s_abort = 1;
+            atomicExch(&g_step_fault, 1);
+            break;
+          }
+        }
+      }
+    }
+  }
   consumer_sync();
   if (tid == 0) {
     if (*sh.s_abort && p.host_fault != nullptr) {
@@ -994,6 +1093,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
     if (atomicAdd(p.sync + 4, 1u) == gridDim.x - 1) {
       p.sync[0] = 0u; p.sync[1] = 0u; p.sync[2] = 0u; p.sync[3] = 0u;
       p.sync[4] = 0u;
+      if (p.tp_size > 1) *p.tp_epoch = p.epoch_base + (uint32_t)p.n_exchanges + 1u;
       __threadfence();
     }
   }
@@ -1155,6 +1255,9 @@ tb_status launch_w4_step(const StepProgram& g, cudaStream_t stream) {
   p.scale = 1.0f / sqrtf((float)g.head_dim);
   p.wait_cycles = g_wait_cycles > 0 ? g_wait_cycles : kWaitCyclesDefault;
   p.debug = g_step_debug;
+  p.tp_rank = g.tp.rank; p.tp_size = g.tp.size; p.tp_hidden = g.tp.hidden; p.n_exchanges = g.n_exchanges;
+  for (int r = 0; r < 8; ++r) { p.tp_recv[r] = g.tp.recv[r]; p.tp_logits[r] = g.tp.logits[r]; p.tp_flags[r] = g.tp.flags[r]; }
+  p.tp_epoch = g.tp.epoch; p.epoch_base = 0;
   p.tl = timeline_next_block();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
