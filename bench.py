@@ -411,7 +411,8 @@ def run_gpu(args):
     dec = tb.B200QwenDecoder(embed, layers, fnorm, lm_p, lm_s, c["num_layers"], c["hidden_size"],
                              c["intermediate_size"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["group_size"],
                              c["rms_norm_eps"], max_seq, c["rope_theta"], max_batch=B, tp_size=tp, tp_rank=rank,
-                             vocab_size=c["vocab_size"], nccl_only=args.nccl_only, pdl=not args.no_pdl, debug=args.no_graph)
+                             vocab_size=c["vocab_size"], nccl_only=args.nccl_only, pdl=not args.no_pdl, debug=args.no_graph,
+                             fused_step=not args.chain)
     if tp > 1:
         from torchburn_b200.tp import init_tensor_parallel
 
@@ -555,6 +556,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between kernels (A/B of programmatic dependent launch)")
     ap.add_argument("--no-graph", action="store_true", help="direct launches instead of CUDA-graph replay")
+    ap.add_argument("--chain", action="store_true", help="batch-1 steps as a chain of single kernels instead of the persistent step kernel")
     ap.add_argument("--quick", action="store_true", help="skip the kernel-alone and CPU measurements")
     args = ap.parse_args()
     if args.impl == "reference":

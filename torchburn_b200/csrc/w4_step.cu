@@ -1055,6 +1055,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4_step_kernel(const StepParams k
     if ((ph + 1 < p.nphases || p.tp_size > 1) && !(d.kind == 0 && d.tp_mode == 1)) {
       ++round;
       grid_barrier(p.sync, round, sh.s_abort, p.wait_cycles, tid);
+    } else {
+      // no grid barrier here, but the CTA's warps must all be done with this phase's descriptor
+      // before the next phase's first threads overwrite the other descriptor slot
+      consumer_sync();
     }
   }
   // The last CTA to leave puts the barrier words back to zero for the next launch (every CTA has
