@@ -41,6 +41,8 @@ import numpy as np
 
 LLAMA8B = dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_layers=32, num_heads=32,
                num_kv_heads=8, head_dim=128, group_size=32, rms_norm_eps=1e-6, rope_theta=500000.0)
+LLAMA70B = dict(vocab_size=128256, hidden_size=8192, intermediate_size=28672, num_layers=80, num_heads=64,
+                num_kv_heads=8, head_dim=128, group_size=32, rms_norm_eps=1e-6, rope_theta=500000.0)
 QWEN05B = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_layers=24, num_heads=14,
                num_kv_heads=2, head_dim=64, group_size=32, rms_norm_eps=1e-6, rope_theta=1000000.0)
 CONTEXT = 4096
@@ -225,7 +227,7 @@ def run_reference(args):
 
 def workload_config(c, batch, n_gpus):
     return {
-        "workload": f"{'llama-3-8b' if c['hidden_size'] == 4096 else 'qwen2.5-0.5b'}-shaped INT4 (group {c['group_size']}) W4A32 decode, batch {batch}, fp32 KV at context {CONTEXT}",
+        "workload": f"{ {4096: 'llama-3-8b', 8192: 'llama-3-70b'}.get(c['hidden_size'], 'qwen2.5-0.5b')}-shaped INT4 (group {c['group_size']}) W4A32 decode, batch {batch}, fp32 KV at context {CONTEXT}",
         "hidden": c["hidden_size"], "layers": c["num_layers"], "heads": f"{c['num_heads']}q/{c['num_kv_heads']}kv",
         "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
         "batch": batch, "context": CONTEXT, "parallelism": f"tp{n_gpus}",
@@ -234,9 +236,13 @@ def workload_config(c, batch, n_gpus):
 
 
 # ----------------------------------------------------------------- GPU arm
-def build_model(torch, tb, c, device, tp, rank, seed=1234):
+def build_model(torch, tb, c, device, tp, rank, seed=1234, direct_shards=False):
     """Random-init Llama-shaped weights generated and quantized on the GPU; under
-    tensor parallelism every rank generates the same full matrix and keeps its shard."""
+    tensor parallelism every rank generates the same full matrix and keeps its shard.
+    direct_shards (throughput-only runs of models too large for that): every rank generates
+    matrices of its shard's shape; the ranks' shards are then not slices of one model."""
+    if direct_shards:
+        return build_model_direct(torch, tb, c, device, tp, rank, seed)
     gen = torch.Generator(device).manual_seed(seed)
     H, I, V, G = c["hidden_size"], c["intermediate_size"], c["vocab_size"], c["group_size"]
     nh, nkv, hd = c["num_heads"], c["num_kv_heads"], c["head_dim"]
@@ -277,6 +283,25 @@ def build_model(torch, tb, c, device, tp, rank, seed=1234):
     return embed, layers, torch.ones(H, device=device), lm_p, lm_s
 
 
+def build_model_direct(torch, tb, c, device, tp, rank, seed):
+    gen = torch.Generator(device).manual_seed(seed + rank)
+    H, I, V, G = c["hidden_size"], c["intermediate_size"], c["vocab_size"], c["group_size"]
+    q_dim, kv_dim = c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
+
+    def qlin(n, k):
+        w = torch.randn(n, k, device=device, generator=gen) * 0.02
+        return tb.quantize_weight_int4_grouped(w, group_size=G)
+
+    ones = torch.ones(H, device=device)
+    layers = []
+    for _ in range(c["num_layers"]):
+        layers.append([ones, *qlin((q_dim + 2 * kv_dim) // tp, H), *qlin(H, q_dim // tp), ones, *qlin(I // tp, H), *qlin(I // tp, H),
+                       *qlin(H, I // tp)])
+    embed = torch.randn(V, H, device=device, generator=torch.Generator(device).manual_seed(seed)) * 0.02
+    lm_p, lm_s = qlin(V // tp, H)
+    return embed, layers, ones, lm_p, lm_s
+
+
 def prefill_kv(torch, dec, c, device, ctx, batch, tp, rank, seed=99):
     gen = torch.Generator(device).manual_seed(seed)
     nkv_l = c["num_kv_heads"] // tp
@@ -288,6 +313,81 @@ def prefill_kv(torch, dec, c, device, ctx, batch, tp, rank, seed=99):
             ks.append(k[rank * nkv_l:(rank + 1) * nkv_l].contiguous())
             vs.append(v[rank * nkv_l:(rank + 1) * nkv_l].contiguous())
         dec.copy_kv_cache_from_tensors(ks, vs, ctx, seq=b)
+
+
+def make_decoder(tb, c, model, max_seq, batch, tp, rank, args, **kw):
+    embed, layers, fnorm, lm_p, lm_s = model
+    return tb.B200QwenDecoder(embed, layers, fnorm, lm_p, lm_s, c["num_layers"], c["hidden_size"],
+                              c["intermediate_size"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["group_size"],
+                              c["rms_norm_eps"], max_seq, c["rope_theta"], max_batch=batch, tp_size=tp, tp_rank=rank,
+                              vocab_size=c["vocab_size"], nccl_only=args.nccl_only, pdl=not args.no_pdl, debug=args.no_graph,
+                              fused_step=not args.chain, **kw)
+
+
+def timed_steps(torch, dist, tb, dec, device, tp, batch, ctx, steps, warmup, repeats):
+    """`repeats` timed regions of exactly `steps` decode steps each (CUDA events on the decoder's
+    stream, a barrier and a device synchronisation on both sides, max over ranks); returns the
+    list of milliseconds per region."""
+    L = tb.lib()
+    stream = torch.cuda.ExternalStream(L.tb_decoder_stream(dec.handle), device=device)
+    out_tokens = np.empty(max(steps, warmup), np.int64)
+
+    def barrier():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def generate(first, start, n):
+        if batch == 1:
+            tb._lib.check(L.tb_decoder_generate_greedy(dec.handle, first, start, n, out_tokens.ctypes.data))
+        else:
+            toks = np.full(batch, first, np.int64)
+            for i in range(n):
+                offs = np.full(batch, start + i, np.int64)
+                tb._lib.check(L.tb_decoder_step_batch(dec.handle, toks.ctypes.data, offs.ctypes.data, batch, None))
+
+    generate(11, ctx, warmup)
+    barrier()
+    out = []
+    for r in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        generate(12 + r, ctx + warmup, steps)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if tp > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        out.append(ms)
+    return out
+
+
+def tp_correctness_check(torch, dist, tb, c, device, tp, rank, args):
+    """Outside every timed region: a two-layer model of the benchmark's true widths, sharded over the
+    `tp` ranks, against the same model unsharded on rank 0's GPU - the logits of three steps."""
+    small = dict(c, num_layers=2, vocab_size=8192)
+    full = build_model(torch, tb, small, device, 1, 0, seed=4321)
+    shard = build_model(torch, tb, small, device, tp, rank, seed=4321)
+    dec = make_decoder(tb, small, shard, 64, 1, tp, rank, args)
+    from torchburn_b200.tp import init_tensor_parallel
+
+    init_tensor_parallel(dec, dist, device)
+    ref = make_decoder(tb, small, full, 64, 1, 1, 0, args) if rank == 0 else None
+    worst = 0.0
+    for off, tok in enumerate((17, 4000, 911)):
+        got = dec.step(tok, off)
+        if rank == 0:
+            want = ref.step(tok, off)
+            worst = max(worst, float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-6)))
+    fault = int(tb.lib().tb_device_fault_flag())
+    dist.barrier()
+    dec.close()
+    if ref is not None:
+        ref.close()
+    return {"max_rel_err": worst, "ranks": tp, "fault_flag": fault,
+            "what": "2 layers at the benchmark's widths, vocabulary 8192: sharded decoder against the unsharded one on rank 0, logits of 3 steps"}
 
 
 def _graph_time(torch, device, one_pass, launches_per_pass, passes=10):
@@ -403,16 +503,17 @@ def run_gpu(args):
 
     global CONTEXT
     c = dict(LLAMA8B)
+    direct = False
     if args.model == "qwen05b":  # workload configuration 3 (single GPU, context 1024); not the headline workload
         c, CONTEXT = dict(QWEN05B), 1024
+    elif args.model == "llama70b":  # workload configuration 5: tensor parallel 8, batch 16, context 8192; throughput only
+        c, CONTEXT, direct = dict(LLAMA70B), 8192, True
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    R = 1 if args.quick else max(1, args.repeats)
     max_seq = CONTEXT + 64 * ((K + W + 63) // 64) + 64
-    embed, layers, fnorm, lm_p, lm_s = build_model(torch, tb, c, device, tp, rank)
-    dec = tb.B200QwenDecoder(embed, layers, fnorm, lm_p, lm_s, c["num_layers"], c["hidden_size"],
-                             c["intermediate_size"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["group_size"],
-                             c["rms_norm_eps"], max_seq, c["rope_theta"], max_batch=B, tp_size=tp, tp_rank=rank,
-                             vocab_size=c["vocab_size"], nccl_only=args.nccl_only, pdl=not args.no_pdl, debug=args.no_graph,
-                             fused_step=not args.chain)
+    model = build_model(torch, tb, c, device, tp, rank, direct_shards=direct)
+    layers = model[1]
+    dec = make_decoder(tb, c, model, max_seq, B, tp, rank, args)
     if tp > 1:
         from torchburn_b200.tp import init_tensor_parallel
 
@@ -420,38 +521,16 @@ def run_gpu(args):
     prefill_kv(torch, dec, c, device, CONTEXT, B, tp, rank)
     stream = torch.cuda.ExternalStream(lib_stream(tb, dec), device=device)
     L = tb.lib()
-    import ctypes as C
 
     def barrier():
         if tp > 1:
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    # ---- device-resident: greedy generate loop, K steps enqueued back to back ----
-    out_tokens = np.empty(max(K, W), np.int64)
-
-    def generate(first, start, n):
-        if B == 1:
-            tb._lib.check(L.tb_decoder_generate_greedy(dec.handle, first, start, n, out_tokens.ctypes.data))
-        else:
-            toks = np.full(B, first, np.int64)
-            for i in range(n):
-                offs = np.full(B, start + i, np.int64)
-                tb._lib.check(L.tb_decoder_step_batch(dec.handle, toks.ctypes.data, offs.ctypes.data, B, None))
-
-    generate(11, CONTEXT, W)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # ---- device-resident: greedy generate loop, K steps enqueued back to back, R regions ----
     with ClockSampler(local) as clocks:
-        e0.record(stream)
-        generate(12, CONTEXT + W, K)
-        e1.record(stream)
-        barrier()
-    ms = e0.elapsed_time(e1)
-    if tp > 1:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        regions = timed_steps(torch, dist, tb, dec, device, tp, B, CONTEXT, K, W, R)
+    ms = float(np.median(regions))
     ms_per_step = ms / K
     value = B * 1e3 / ms_per_step
 
@@ -468,36 +547,67 @@ def run_gpu(args):
     for i in range(W):
         e2e_step(i)
     barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    e2.record(stream)
-    for i in range(K):
-        e2e_step(i)
-    e3.record(stream)
-    barrier()
-    wall_ms = (time.perf_counter() - t0) * 1e3
-    e2e_ms = max(e2.elapsed_time(e3), 0.0)
-    if tp > 1:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_regions, wall_regions = [], []
+    for _ in range(R):
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e2.record(stream)
+        for i in range(K):
+            e2e_step(i)
+        e3.record(stream)
+        barrier()
+        wall_regions.append((time.perf_counter() - t0) * 1e3)
+        e2e_ms = max(e2.elapsed_time(e3), 0.0)
+        if tp > 1:
+            t = torch.tensor([e2e_ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e_regions.append(e2e_ms)
+    e2e_ms, wall_ms = float(np.median(e2e_regions)), float(np.median(wall_regions))
     e2e_value = B * 1e3 / (e2e_ms / K)
+    launches_per_step = dec.launches_per_step()
 
-    if rank != 0:
+    def finish():
         if tp > 1:
             dist.barrier()
-            dec.close()
             dist.destroy_process_group()
-        return
+
     if args.quick:
-        print(json.dumps({"value": value, "ms_per_step": ms_per_step, "e2e": e2e_value, "n_gpus": tp, "batch": B, "model": args.model,
-                          "weights_only_frac_of_measured": step_weight_bytes(c) / tp / (ms_per_step * 1e-3) / 1e9 / measured_peak()[0]}), flush=True)
-        if tp > 1:
-            dist.barrier()
-            dec.close()
-            dist.destroy_process_group()
+        dec.close()
+        if rank == 0:
+            print(json.dumps({"value": value, "ms_per_step": ms_per_step, "e2e": e2e_value, "n_gpus": tp, "batch": B, "model": args.model,
+                              "launches_per_step": launches_per_step,
+                              "weights_only_frac_of_measured": step_weight_bytes(c) / tp / (ms_per_step * 1e-3) / 1e9 / measured_peak()[0],
+                              "weights_plus_kv_frac_of_measured": (step_weight_bytes(c) + B * kv_bytes_per_seq(c, CONTEXT)) / tp / (ms_per_step * 1e-3) / 1e9 / measured_peak()[0]}), flush=True)
+        finish()
         return
-    # ---- rank 0: roofline of the dominant kernel, config-1 GEMV, CPU baseline ----
+
+    # ---- outside the headline region (every rank takes part where the model is sharded) ----
+    # correctness of the sharded path at this N
+    tp_check = tp_correctness_check(torch, dist, tb, c, device, tp, rank, args) if tp > 1 else None
+    # the other batch sizes of the workload configuration: tokens/s at batch 8 and 32
+    batch_sweep = None
+    if args.model == "llama8b" and B == 1 and args.batch_sweep:
+        dec.close()
+        dec = None
+        big = make_decoder(tb, c, model, CONTEXT + 192, 32, tp, rank, args)
+        if tp > 1:
+            init_tensor_parallel(big, dist, device)
+        prefill_kv(torch, big, c, device, CONTEXT, 32, tp, rank)
+        batch_sweep = {"1": {"tokens_per_s": value, "ms_per_step": ms_per_step}}
+        for bb in (8, 32):
+            r_ms = timed_steps(torch, dist, tb, big, device, tp, bb, CONTEXT, 8, 3, 3)
+            m = float(np.median(r_ms)) / 8
+            batch_sweep[str(bb)] = {"tokens_per_s": bb * 1e3 / m, "ms_per_step": m,
+                                    "weights_plus_kv_frac": (step_weight_bytes(c) + bb * kv_bytes_per_seq(c, CONTEXT)) / tp / (m * 1e-3) / 1e9 / measured_peak()[0]}
+        big.close()
+    if rank != 0:
+        if dec is not None:
+            dec.close()
+        finish()
+        return
+
+    # ---- rank 0: roofline of the dominant kernel, config-1 GEMV, config 2, config 3, CPU baseline ----
     peak, peak_kind = measured_peak()
     alg, sec, _ = time_dominant_kernel(torch, tb, c, layers, device, tp)
     achieved = alg / sec / 1e9
@@ -516,28 +626,55 @@ def run_gpu(args):
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": tp, "steps": K, "warmup": W,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": workload_config(c, B, tp),
+        "repeats": {"regions": R, "steps_per_region": K, "ms_per_step_median": ms_per_step, "ms_per_step_min": min(regions) / K,
+                    "ms_per_step_max": max(regions) / K},
         "roofline": roofline,
         "step_roofline": {
             "weight_bytes_per_step_per_gpu": wb, "kv_bytes_per_step_per_gpu": kvb * B,
             "weights_only_frac": wb / step_s / 1e9 / peak, "weights_plus_kv_frac": (wb + kvb * B) / step_s / 1e9 / peak,
-            "peak_kind": f"of {peak_kind}"},
+            "peak_kind": f"of {peak_kind}", "launches_per_step": launches_per_step},
         "gemv_config1": {"shape": "4096x4096 group 32, M=1", "algorithmic_bytes": c1_alg, "us_per_launch": c1_sec * 1e6,
                          "achieved_gbs": c1_alg / c1_sec / 1e9, "frac_of_measured": c1_alg / c1_sec / 1e9 / peak,
                          "frac_of_nominal_8TBs": c1_alg / c1_sec / 1e9 / NOMINAL_HBM_GBS,
                          "note": "64 rotating weight copies (672 MB), one CUDA graph of 64 launches replayed"},
         "gemm_config2": (time_c2_gemm(torch, tb, c, layers, device) if tp == 1 else None),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 16 * B, "d2h_bytes_per_step": 4 * B * c["vocab_size"],
-                "ms_per_step": e2e_ms / K, "wall_ms_per_step": wall_ms / K},
-        "gpu_launches": (dec.launches_per_step() + 1) * K,
+                "ms_per_step": e2e_ms / K, "wall_ms_per_step": wall_ms / K, "regions": R},
+        "gpu_launches": (launches_per_step + 1) * K,
         "clocks": clocks.summary(),
     }
+    if tp_check is not None:
+        line["tp_check"] = tp_check
+    if batch_sweep is not None:
+        line["batch_sweep"] = batch_sweep
+    if dec is not None:
+        dec.close()
+    del model, layers
+    torch.cuda.empty_cache()
+    if tp == 1 and args.model == "llama8b" and args.config3:
+        line["qwen05b_config3"] = time_config3(torch, tb, device, args)
     if args.cpu_baseline:
         line["cpu_baseline"] = {k: v for k, v in cpu_full_step(c, CONTEXT, 8, 2).items() if not k.startswith("ms_per_step")}
     print(json.dumps(line), flush=True)
-    if tp > 1:
-        dist.barrier()
-        dec.close()
-        dist.destroy_process_group()
+    finish()
+
+
+def time_config3(torch, tb, device, args):
+    """Workload configuration 3: Qwen2.5-0.5B-shaped decode, batch 1, fp32 KV pre-filled to 1024."""
+    c, ctx = dict(QWEN05B), 1024
+    model = build_model(torch, tb, c, device, 1, 0, seed=77)
+    dec = make_decoder(tb, c, model, ctx + 256, 1, 1, 0, args)
+    prefill_kv(torch, dec, c, device, ctx, 1, 1, 0)
+    r_ms = timed_steps(torch, None, tb, dec, device, 1, 1, ctx, 64, 8, 3)
+    m = float(np.median(r_ms)) / 64
+    peak, kind = measured_peak()
+    wb = step_weight_bytes(c)
+    out = {"workload": "qwen2.5-0.5b-shaped INT4 (group 32) decode, batch 1, fp32 KV at context 1024",
+           "tokens_per_s": 1e3 / m, "ms_per_step": m, "launches_per_step": dec.launches_per_step(),
+           "weights_only_frac": wb / (m * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}",
+           "weight_streaming_roofline_tokens_per_s": peak * 1e9 / wb}
+    dec.close()
+    return out
 
 
 def lib_stream(tb, dec):
@@ -551,7 +688,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--model", default="llama8b", choices=["llama8b", "qwen05b"], help="qwen05b: workload configuration 3, use with --quick")
+    ap.add_argument("--model", default="llama8b", choices=["llama8b", "qwen05b", "llama70b"],
+                    help="qwen05b: workload configuration 3; llama70b: configuration 5 (8 GPUs, --batch 16); both with --quick")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--no-batch-sweep", dest="batch_sweep", action="store_false", help="skip the batch 8 / 32 measurements")
+    ap.add_argument("--no-config3", dest="config3", action="store_false", help="skip the Qwen2.5-0.5B-shaped measurement")
     ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: plain ncclAllReduce instead of the fused kernel")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between kernels (A/B of programmatic dependent launch)")

@@ -265,6 +265,43 @@ tb_status tb_fused_attention_step(tb_linear* qkv, tb_linear* o, const float* x, 
                                   int32_t head_dim, int64_t max_seq_len, float* out,
                                   tb_space io_space, void* stream);
 
+/* fused_transformer_layer_step_w4a32 (src/ffi/quantization_ffi.rs:406-438,
+ * src/quantization/fused_transformer.rs:16-376): one decoder layer for one token, IN PLACE on x:
+ *   x += O(attention(rope(QKV(rms_norm(x, input_norm_w))))); x += down(silu(gate(n)) * up(n)),
+ *   n = rms_norm(x, post_norm_w).
+ * The 17 weight / bias tensors of the reference's positional arguments travel in one struct, all
+ * DEVICE pointers in the layouts of tb_gemv_w4a32_grouped; the four biases after qkv_b may be NULL
+ * like the reference's Option arguments.  k_cache / v_cache: [1, Hkv, max_seq_len, d] f32, DEVICE,
+ * mutated at `offset` (the reference writes through its const capsules, fused_transformer.rs:172-187).
+ * cos_p / sin_p: the rotation of THIS position, length head_dim.  x [hidden], cos_p and sin_p live
+ * in io_space.  hidden_size and intermediate_size are explicit (the reference reads them from the
+ * tensor shapes).  Errors: TB_ERR_ARG for null tensors or an offset outside the cache,
+ * TB_ERR_SHAPE with the "TB_UNSUPPORTED:" marker for shapes the linears refuse. */
+typedef struct tb_layer_step_weights {
+  const float* input_norm_w;
+  const uint8_t* qkv_w;
+  const float* qkv_s;
+  const float* qkv_b;
+  const uint8_t* o_w;
+  const float* o_s;
+  const float* o_b;
+  const float* post_norm_w;
+  const uint8_t* gate_w;
+  const float* gate_s;
+  const float* gate_b;
+  const uint8_t* up_w;
+  const float* up_s;
+  const float* up_b;
+  const uint8_t* down_w;
+  const float* down_s;
+  const float* down_b;
+} tb_layer_step_weights;
+tb_status tb_fused_transformer_layer_step(float* x, const tb_layer_step_weights* w, float* k_cache, float* v_cache,
+                                          const float* cos_p, const float* sin_p, int64_t offset,
+                                          int64_t hidden_size, int64_t intermediate_size, int32_t num_heads,
+                                          int32_t num_kv_heads, int32_t head_dim, int64_t max_seq_len,
+                                          int32_t group_size, float eps, tb_space io_space, void* stream);
+
 /* ------------------------------------------------------------------------
  * Decoder: RustQwenDecoder / WgpuQwenDecoder (src/llm/decoder.rs:111-171,
  * src/wgpu/decode.rs:297-334) as a handle.

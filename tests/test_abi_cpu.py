@@ -35,6 +35,36 @@ def test_header_symbols_all_exported(tb):
     assert tb.abi_version() == 1
 
 
+def test_rust_sys_crate_declares_exactly_the_header(tb):
+    """rust/torchburn-b200-sys/src/lib.rs (sources only: no Rust toolchain here) must declare every
+    function of the header, no other, with the same number of arguments, and the same struct fields."""
+    hdr = open(os.path.join(ROOT, "include", "torchburn_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    rs = open(os.path.join(ROOT, "rust", "torchburn-b200-sys", "src", "lib.rs")).read()
+    rs_code = re.sub(r"//.*", "", rs)
+
+    def argc(args):
+        args = " ".join(args.split())
+        return 0 if args in ("", "void") else args.count(",") + 1
+
+    c_fns = {name: argc(args) for name, args in re.findall(r"\b(tb_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", hdr, flags=re.S)
+             if name != "tb_allgather_fn"}
+    r_fns = {name: argc(args) for name, args in re.findall(r"pub fn (tb_[a-z0-9_]+)\(([^;]*?)\)(?:\s*->\s*[^;]+)?;", rs_code, flags=re.S)}
+    assert set(c_fns) == set(r_fns), (sorted(set(c_fns) - set(r_fns)), sorted(set(r_fns) - set(c_fns)))
+    assert c_fns == r_fns, {k: (c_fns[k], r_fns[k]) for k in c_fns if c_fns[k] != r_fns[k]}
+    # struct fields, in order
+    for name in ("tb_model_config", "tb_layer_weights", "tb_layer_step_weights"):
+        c_body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), hdr, flags=re.S).group(1)
+        c_fields = re.findall(r"(\w+)\s*;", c_body)
+        r_body = re.search(r"pub struct %s \{(.*?)\n\}" % name, rs_code, flags=re.S).group(1)
+        r_fields = re.findall(r"pub (\w+)\s*:", r_body)
+        assert c_fields == r_fields, name
+    # status codes
+    for code, val in re.findall(r"\b(TB_(?:OK|ERR_\w+))\s*=\s*(\d+)", hdr):
+        assert re.search(r"pub const %s: tb_status = %s;" % (code, val), rs_code), code
+    assert rs.startswith("// UNCOMPILED")
+
+
 def test_no_oracle_in_product():
     # the product package must not import, load or link the oracle
     for dirpath, _, files in os.walk(os.path.join(ROOT, "torchburn_b200")):

@@ -291,6 +291,63 @@ def test_step_kernel_projection_path_matches_oracle(torch, tb, oracle, n, k, g, 
     assert L.tb_device_fault_flag() == 0
 
 
+@pytest.mark.parametrize("H,I,nh,nkv,hd,g,host_io", [(896, 4864, 14, 2, 64, 32, True), (2048, 4096, 16, 4, 128, 64, False)])
+def test_fused_transformer_layer_step_in_place(torch, tb, oracle, H, I, nh, nkv, hd, g, host_io):
+    """fused_transformer_layer_step_w4a32 (src/quantization/fused_transformer.rs:16-376): one layer in
+    place on x, every optional bias present, against the same ten steps composed from oracle pieces;
+    the caches change in the one slot [kv_h, offset, :] only."""
+    rng = np.random.default_rng(H + I)
+    S, off = 96, 57
+    tq = (nh + 2 * nkv) * hd
+    W = {}
+    for name, (n, k) in {"qkv": (tq, H), "o": (H, nh * hd), "gate": (I, H), "up": (I, H), "down": (H, I)}.items():
+        W[name + "_w"], W[name + "_s"] = _quantized(torch, tb, n, k, g, H + n + k)
+        W[name + "_b"] = (0.05 * rng.standard_normal(n)).astype(np.float32)
+    W["input_norm_w"] = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    W["post_norm_w"] = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    x0 = rng.standard_normal(H).astype(np.float32)
+    kc = (rng.standard_normal((1, nkv, S, hd)) * 0.5).astype(np.float32)
+    vc = rng.standard_normal((1, nkv, S, hd)).astype(np.float32)
+    cos_t, sin_t = oracle.rope_tables(S, hd, 1e6)
+    eps = 1e-6
+    # the oracle's ten steps
+    n1 = oracle.rms_norm(x0, W["input_norm_w"], eps)
+    qkv = np.asarray(oracle.gemm_w4a32_grouped(n1, W["qkv_w"], W["qkv_s"], W["qkv_b"], g)).reshape(-1)
+    q = qkv[:nh * hd].reshape(nh, hd).copy()
+    k = qkv[nh * hd:(nh + nkv) * hd].reshape(nkv, hd).copy()
+    v = qkv[(nh + nkv) * hd:].reshape(nkv, hd)
+    for h in range(nh):
+        q[h] = oracle.rope_apply_head(q[h], cos_t[off], sin_t[off])
+    for h in range(nkv):
+        k[h] = oracle.rope_apply_head(k[h], cos_t[off], sin_t[off])
+    ek, ev = kc[0].copy(), vc[0].copy()
+    ek[:, off], ev[:, off] = k, v
+    attn = oracle.attention_decode(q, ek, ev, off + 1).reshape(-1)
+    x1 = x0 + np.asarray(oracle.gemm_w4a32_grouped(attn, W["o_w"], W["o_s"], W["o_b"], g)).reshape(-1)
+    n2 = oracle.rms_norm(x1, W["post_norm_w"], eps)
+    hmid = np.asarray(oracle.swiglu_gemv(n2, W["gate_w"], W["gate_s"], W["gate_b"], W["up_w"], W["up_s"], W["up_b"], g)).reshape(-1)
+    want = x1 + np.asarray(oracle.gemm_w4a32_grouped(hmid, W["down_w"], W["down_s"], W["down_b"], g)).reshape(-1)
+    # the library, in place
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    d_k, d_v = t(kc), t(vc)
+    x = torch.from_numpy(x0.copy()) if host_io else t(x0)
+    tb.fused_transformer_layer_step(x, t(W["input_norm_w"]), t(W["qkv_w"]), t(W["qkv_s"]), t(W["qkv_b"]), t(W["o_w"]), t(W["o_s"]),
+                                    t(W["o_b"]), t(W["post_norm_w"]), t(W["gate_w"]), t(W["gate_s"]), t(W["gate_b"]), t(W["up_w"]),
+                                    t(W["up_s"]), t(W["up_b"]), t(W["down_w"]), t(W["down_s"]), t(W["down_b"]), d_k, d_v,
+                                    torch.from_numpy(cos_t[off]), torch.from_numpy(sin_t[off]), off, nh, nkv, hd, g, eps)
+    assert max_rel_err(x.cpu().numpy(), want) < STAGE_TOL
+    gk, gv = d_k.cpu().numpy()[0], d_v.cpu().numpy()[0]
+    assert max_rel_err(gk[:, off], k) < 1e-6 and max_rel_err(gv[:, off], v) < 1e-6
+    mask = np.ones(S, bool); mask[off] = False
+    assert np.array_equal(gk[:, mask], kc[0][:, mask]) and np.array_equal(gv[:, mask], vc[0][:, mask])
+    # errors of the reference's entry point: an offset outside the cache
+    with pytest.raises(ValueError):
+        tb.fused_transformer_layer_step(x, t(W["input_norm_w"]), t(W["qkv_w"]), t(W["qkv_s"]), None, t(W["o_w"]), t(W["o_s"]), None,
+                                        t(W["post_norm_w"]), t(W["gate_w"]), t(W["gate_s"]), None, t(W["up_w"]), t(W["up_s"]), None,
+                                        t(W["down_w"]), t(W["down_s"]), None, d_k, d_v, torch.from_numpy(cos_t[off]),
+                                        torch.from_numpy(sin_t[off]), S, nh, nkv, hd, g, eps)
+
+
 def test_fp32_product_mode_is_selectable_and_matches_oracle(torch, tb, oracle):
     """tb_set_gemv_tuning(0, ...): the M = 1 kernels multiply in fp32 (the reference's own W4A32
     arithmetic) instead of block fixed point; same tolerance, tighter distance from float64."""

@@ -15,6 +15,7 @@ from .quantization import (
     fused_attention_step,
     fused_swiglu_mlp,
     fused_swiglu_mlp_batched,
+    fused_transformer_layer_step,
     quantize_weight_int4_grouped,
     quantize_weight_int4_grouped_v2,
     w4a32_grouped_linear,
@@ -24,6 +25,6 @@ from .quantization import (
 __all__ = [
     "TorchBurnB200Error", "abi_version", "device_report", "lib", "last_error",
     "B200QwenDecoder", "create_b200_qwen_decoder", "QuantizedLinear", "fused_attention_step",
-    "fused_swiglu_mlp", "fused_swiglu_mlp_batched", "quantize_weight_int4_grouped",
+    "fused_swiglu_mlp", "fused_swiglu_mlp_batched", "fused_transformer_layer_step", "quantize_weight_int4_grouped",
     "w4a32_grouped_linear", "quantize_weight_int4_grouped_v2", "dequantize_int4_grouped_v2", "w4a32_grouped_linear_v2",
 ]

@@ -39,6 +39,12 @@ class LayerWeights(C.Structure):
         "up_s", "down_w", "down_s", "qkv_b")]
 
 
+class LayerStepWeights(C.Structure):
+    _fields_ = [(k, C.c_void_p) for k in (
+        "input_norm_w", "qkv_w", "qkv_s", "qkv_b", "o_w", "o_s", "o_b", "post_norm_w", "gate_w", "gate_s", "gate_b",
+        "up_w", "up_s", "up_b", "down_w", "down_s", "down_b")]
+
+
 ALLGATHER_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t)
 
 _p, _i64, _i32, _f32, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_size_t
@@ -79,6 +85,7 @@ SIGNATURES = {
     "tb_linear_device_ptrs": (_i32, [_p, _PP, _PP, _PP]),
     "tb_fused_swiglu_mlp": (_i32, [_p, _p, _p, _p, _i64, _p, _i32, _p]),
     "tb_fused_attention_step": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _p, _i32, _p]),
+    "tb_fused_transformer_layer_step": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i32, _i32, _i32, _i64, _i32, _f32, _i32, _p]),
     "tb_decoder_create": (_i32, [_PP, C.POINTER(ModelConfig), _p, _p, _p, _p, _p, _i32]),
     "tb_decoder_destroy": (None, [_p]),
     "tb_decoder_step": (_i32, [_p, _i64, _i64, _p]),

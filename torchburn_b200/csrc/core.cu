@@ -407,4 +407,87 @@ tb_status tb_fused_attention_step(tb_linear* qkv, tb_linear* o, const float* x, 
   return s;
 }
 
+/* fused_transformer_layer_step_w4a32: steps 1-10 of one layer, in place on x. */
+tb_status tb_fused_transformer_layer_step(float* x, const tb_layer_step_weights* w, float* k_cache, float* v_cache,
+                                          const float* cos_p, const float* sin_p, int64_t offset, int64_t hidden_size,
+                                          int64_t intermediate_size, int32_t num_heads, int32_t num_kv_heads,
+                                          int32_t head_dim, int64_t max_seq_len, int32_t group_size, float eps,
+                                          tb_space io_space, void* stream) {
+  if (!x || !w || !k_cache || !v_cache || !cos_p || !sin_p) return fail(TB_ERR_ARG, "tb_fused_transformer_layer_step: null argument");
+  if (!w->input_norm_w || !w->qkv_w || !w->qkv_s || !w->o_w || !w->o_s || !w->post_norm_w || !w->gate_w || !w->gate_s ||
+      !w->up_w || !w->up_s || !w->down_w || !w->down_s)
+    return fail(TB_ERR_ARG, "tb_fused_transformer_layer_step: a weight tensor is missing");
+  if (num_heads < 1 || num_kv_heads < 1 || head_dim < 2 || hidden_size < 1 || intermediate_size < 1)
+    return fail(TB_ERR_SHAPE, "TB_UNSUPPORTED: fused_transformer_layer_step: empty shape");
+  const int64_t H = hidden_size, I = intermediate_size, q_dim = (int64_t)num_heads * head_dim;
+  const int64_t total = q_dim + 2ll * num_kv_heads * head_dim;
+  TB_TRY(check_linear_shape(total, H, group_size));
+  TB_TRY(check_linear_shape(H, q_dim, group_size));
+  TB_TRY(check_linear_shape(I, H, group_size));
+  TB_TRY(check_linear_shape(H, I, group_size));
+  if (offset < 0 || offset >= max_seq_len)
+    return fail(TB_ERR_ARG, "fused_transformer_layer_step: offset %lld outside the cache (max_seq_len %lld)", (long long)offset, (long long)max_seq_len);
+  cudaStream_t st = as_stream(stream);
+  const size_t sbytes = attention_scratch_bytes(1, num_heads, num_kv_heads, head_dim, max_seq_len);
+  // one device block: x | cos | sin | qkv | attn | h | offset | attention scratch
+  const size_t fl = (size_t)H + 2 * head_dim + total + q_dim + I;
+  const size_t hdr = ((fl * sizeof(float) + sizeof(int32_t)) + 255) & ~(size_t)255;
+  char* blk = nullptr;
+  cudaError_t e = cudaMalloc(&blk, hdr + sbytes);
+  if (e != cudaSuccess) return fail(TB_ERR_OOM, "fused_transformer_layer_step: %s", cudaGetErrorString(e));
+  float* d_x = reinterpret_cast<float*>(blk);
+  float* d_cos = d_x + H;
+  float* d_sin = d_cos + head_dim;
+  float* d_qkv = d_sin + head_dim;
+  float* d_attn = d_qkv + total;
+  float* d_h = d_attn + q_dim;
+  int32_t* d_off = reinterpret_cast<int32_t*>(d_h + I);
+  tb_status s = TB_OK;
+  const cudaMemcpyKind kin = io_space == TB_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+  const int32_t off32 = (int32_t)offset;
+  auto chk = [&](cudaError_t err) { if (err != cudaSuccess && s == TB_OK) s = fail(TB_ERR_CUDA, "fused_transformer_layer_step: %s", cudaGetErrorString(err)); };
+  chk(cudaMemsetAsync(blk + hdr, 0, sbytes, st));
+  chk(cudaMemcpyAsync(d_x, x, sizeof(float) * H, kin, st));
+  chk(cudaMemcpyAsync(d_cos, cos_p, sizeof(float) * head_dim, kin, st));
+  chk(cudaMemcpyAsync(d_sin, sin_p, sizeof(float) * head_dim, kin, st));
+  chk(cudaMemcpyAsync(d_off, &off32, sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  if (s == TB_OK) {  // 1 + 2: RMSNorm fused into the QKV projection
+    GemvArgs a;
+    a.x = d_x; a.w = w->qkv_w; a.scales = w->qkv_s; a.bias = w->qkv_b; a.norm_w = w->input_norm_w; a.eps = eps;
+    a.out = d_qkv; a.m = 1; a.n = total; a.k = H; a.g = group_size;
+    s = launch_w4_gemv(a, st);
+  }
+  if (s == TB_OK) {  // 3 + 4 + 5: RoPE, cache write, attention
+    AttnArgs a;
+    a.qkv = d_qkv; a.k_cache = k_cache; a.v_cache = v_cache; a.cos_t = d_cos; a.sin_t = d_sin;
+    a.offsets = d_off; a.out = d_attn; a.scratch = blk + hdr; a.batch = 1; a.num_heads = num_heads;
+    a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.max_seq_len = max_seq_len;
+    a.per_call_tables = true;
+    s = launch_attention_decode(a, st);
+  }
+  if (s == TB_OK) {  // 6 + 7: O projection, x += o_out
+    GemvArgs a;
+    a.x = d_attn; a.w = w->o_w; a.scales = w->o_s; a.bias = w->o_b; a.resid = d_x; a.out = d_x;
+    a.m = 1; a.n = H; a.k = q_dim; a.g = group_size;
+    s = launch_w4_gemv(a, st);
+  }
+  if (s == TB_OK) {  // 8 + 9a: RMSNorm fused into gate/up with the SwiGLU epilogue
+    GemvArgs a;
+    a.x = d_x; a.w = w->gate_w; a.scales = w->gate_s; a.bias = w->gate_b; a.w2 = w->up_w; a.scales2 = w->up_s; a.bias2 = w->up_b;
+    a.norm_w = w->post_norm_w; a.eps = eps; a.out = d_h; a.m = 1; a.n = I; a.k = H; a.g = group_size;
+    s = launch_w4_gemv(a, st);
+  }
+  if (s == TB_OK) {  // 9b + 10: down projection, x += mlp_out
+    GemvArgs a;
+    a.x = d_h; a.w = w->down_w; a.scales = w->down_s; a.bias = w->down_b; a.resid = d_x; a.out = d_x;
+    a.m = 1; a.n = H; a.k = I; a.g = group_size;
+    s = launch_w4_gemv(a, st);
+  }
+  if (s == TB_OK)
+    chk(cudaMemcpyAsync(x, d_x, sizeof(float) * H, io_space == TB_HOST ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice, st));
+  chk(cudaStreamSynchronize(st));
+  cudaFree(blk);
+  return s;
+}
+
 }  // extern "C"

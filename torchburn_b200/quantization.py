@@ -286,3 +286,40 @@ def fused_attention_step(x, qkv_proj, o_proj, k_cache, v_cache, cos, sin, offset
                                             head_dim, max_seq_len, out.data_ptr(),
                                             TB_DEVICE if on_cuda else TB_HOST, _stream_ptr(dev)))
     return out.reshape(1, 1, -1)
+
+
+def fused_transformer_layer_step(x, input_norm_w, qkv_w, qkv_s, qkv_b, o_w, o_s, o_b, post_norm_w, gate_w, gate_s, gate_b,
+                                 up_w, up_s, up_b, down_w, down_s, down_b, k_cache, v_cache, cos, sin, offset: int,
+                                 num_heads: int, num_kv_heads: int, head_dim: int, group_size: int, eps: float = 1e-6) -> None:
+    """fused_transformer_layer_step_w4a32 (src/ffi/quantization_ffi.rs:406-438): one decoder layer
+    for one token IN PLACE on ``x`` (a contiguous float32 tensor whose last dimension is the hidden
+    size, on the host or on the GPU); same positional arguments as the reference.  Weights and the
+    KV caches [1, Hkv, max_seq_len, d] are CUDA tensors; the caches are updated at ``offset``."""
+    if k_cache.device.type != "cuda" or v_cache.device.type != "cuda":
+        raise _lib.TorchBurnB200Error(1, "fused_transformer_layer_step: the KV caches must be CUDA tensors (they are updated in place)")
+    if not (x.is_contiguous() and x.dtype == torch.float32):
+        raise _lib.TorchBurnB200Error(3, "TB_UNSUPPORTED: fused_transformer_layer_step: x must be contiguous float32 (it is updated in place)")
+    dev = k_cache.device
+    w = _lib.LayerStepWeights()
+    keep = []
+    for name, t, dt in (("input_norm_w", input_norm_w, torch.float32), ("qkv_w", qkv_w, torch.uint8), ("qkv_s", qkv_s, torch.float32),
+                        ("qkv_b", qkv_b, torch.float32), ("o_w", o_w, torch.uint8), ("o_s", o_s, torch.float32), ("o_b", o_b, torch.float32),
+                        ("post_norm_w", post_norm_w, torch.float32), ("gate_w", gate_w, torch.uint8), ("gate_s", gate_s, torch.float32),
+                        ("gate_b", gate_b, torch.float32), ("up_w", up_w, torch.uint8), ("up_s", up_s, torch.float32),
+                        ("up_b", up_b, torch.float32), ("down_w", down_w, torch.uint8), ("down_s", down_s, torch.float32),
+                        ("down_b", down_b, torch.float32)):
+        if t is None:
+            setattr(w, name, None)
+            continue
+        td = t.detach().to(device=dev, dtype=dt).contiguous()
+        keep.append(td)
+        setattr(w, name, td.data_ptr())
+    hidden, inter = x.shape[-1], gate_w.shape[0]
+    on_cuda = x.device.type == "cuda"
+    cs = cos.reshape(-1)[-head_dim:].contiguous().float().to(x.device)
+    sn = sin.reshape(-1)[-head_dim:].contiguous().float().to(x.device)
+    with torch.cuda.device(dev):
+        check(lib().tb_fused_transformer_layer_step(x.data_ptr(), C.byref(w), k_cache.data_ptr(), v_cache.data_ptr(), cs.data_ptr(),
+                                                    sn.data_ptr(), int(offset), hidden, inter, num_heads, num_kv_heads, head_dim,
+                                                    k_cache.shape[2], group_size, float(eps), TB_DEVICE if on_cuda else TB_HOST,
+                                                    _stream_ptr(dev)))
