@@ -190,8 +190,10 @@ void tb_set_attention_chunk(int32_t positions);
 void tb_set_attention_tuning(int32_t ctas_per_sm, int32_t ring_stages);
 /* Tuning hook for the M = 1 GEMV kernels.  product_mode 1 (default): activations are
  * rounded per 32-element block to 24-bit fixed point and multiplied with integer dot
- * products (M >= 2 on the tensor cores); 0: fp32 products for M = 1; 2: integer products on
- * CUDA cores for every M (no tensor cores).  rows_per_warp in {0,1,2,4} and warps in {0,4,8} force
+ * products (2 <= M < 16 with integer mma.sync; 16 <= M on tcgen05 with exact bf16 codes and the
+ * activations as three bf16 pieces); 0: fp32 products for M = 1; 2: integer products on
+ * CUDA cores for every M (no tensor cores); 3: like 1 but the integer mma.sync kernel for every
+ * M >= 2 (no tcgen05).  rows_per_warp in {0,1,2,4} and warps in {0,4,8} force
  * the launch shape (0 = choose from the matrix size).  Process-wide. */
 void tb_set_gemv_tuning(int32_t product_mode, int32_t rows_per_warp, int32_t warps);
 /* Tuning hook for the persistent M = 1 kernel (one long-lived CTA per SM fed by a ring of

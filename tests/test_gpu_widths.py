@@ -369,6 +369,60 @@ def test_fp32_product_mode_is_selectable_and_matches_oracle(torch, tb, oracle):
     assert max_rel_err(got_int, want) < STAGE_TOL
 
 
+@pytest.mark.parametrize("n,k,g,m,bias,pair", [
+    (640, 1024, 32, 16, True, False),      # K split over several CTAs (atomic partial sums), bias
+    (300, 512, 64, 19, False, False),      # rows past n inside the only tile, padded activation rows
+    (1001, 2048, 128, 33, True, False),    # a group spans two 64-element stages
+    (4096, 4096, 32, 64, False, False),    # o_proj of configuration 4
+    (512, 14336, 32, 100, False, False),   # two passes (64 + 36 rows), K = 14336
+    (777, 1024, 32, 17, False, True),      # SwiGLU pair, ragged n
+    (4864, 896, 32, 48, True, True),       # Qwen gate/up with bias
+    (14336, 4096, 32, 64, False, True),    # Llama gate/up at M = 64
+])
+def test_tcgen05_batched_product_matches_oracle(torch, tb, oracle, n, k, g, m, bias, pair):
+    """16 and more activation rows take the tcgen05 kernel (bf16 codes from tensor memory, three
+    bf16 pieces of every activation, the scale applied per group outside the tensor core).  It
+    must stay as close to the float64 result as the reference's own fp32 kernel, and agree with
+    the integer mma.sync kernel it replaces (tb_set_gemv_tuning(3, ..) keeps that one selectable)."""
+    L = tb.lib()
+    rng = np.random.default_rng(n * 3 + k + m)
+    p, s = _quantized(torch, tb, n, k, g, n + k + m, std=0.05)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32) if bias else None
+    d = lambda a: dev(torch, a) if a is not None else None
+    if pair:
+        p2, s2 = _quantized(torch, tb, n, k, g, n + k + m + 1, std=0.05)
+        b2 = rng.standard_normal(n).astype(np.float32) if bias else None
+        t = [d(a) for a in (x, p, s, b, p2, s2, b2)]
+        ptr = lambda a: a.data_ptr() if a is not None else None
+
+        def run():
+            h = torch.full((m, n), float("nan"), device="cuda")
+            assert L.tb_swiglu_gemv_w4a32(ptr(t[0]), ptr(t[1]), ptr(t[2]), ptr(t[3]), ptr(t[4]), ptr(t[5]), ptr(t[6]),
+                                          h.data_ptr(), m, n, k, g, None) == 0, tb.last_error()
+            torch.cuda.synchronize()
+            return h.cpu().numpy()
+        want = np.stack([oracle.swiglu_gemv(x[i], p, s, b, p2, s2, b2, g) for i in range(m)])
+    else:
+        def run():
+            return tb.w4a32_grouped_linear(d(x), d(p), d(s), d(b), g).cpu().numpy()
+        want = oracle.gemm_w4a32_grouped(x, p, s, b, g).reshape(m, n)
+    got = run()
+    assert got.shape == (m, n)
+    assert max_rel_err(got, want) < STAGE_TOL
+    try:
+        L.tb_set_gemv_tuning(3, 0, 0)
+        old = run()
+    finally:
+        L.tb_set_gemv_tuning(1, 0, 0)
+    assert max_rel_err(old, want) < STAGE_TOL
+    assert max_rel_err(got, old) < 1e-5
+    if not pair:
+        exact = oracle.gemm_w4a32_f64(x, p, s, b, g)
+        assert max_rel_err(got, exact) <= max(4 * max_rel_err(want, exact), 2e-6)
+    assert L.tb_device_fault_flag() == 0
+
+
 def test_bounded_device_wait_runs_out_and_reports_timeout(torch, tb):
     """Failure detection without a fault: a wait of the step kernel on a barrier that nothing
     completes, with a limit of a millisecond.  The kernel must return, raise the fault word and

@@ -249,9 +249,9 @@ tb_status tb_debug_step_gemv(const float* x, const uint8_t* w, const float* scal
 int32_t tb_debug_timeline_blocks(void) { return timeline_blocks_used(); }
 
 int32_t tb_device_fault_flag(void) {
-  const int a = stream_fault_flag(), b = attention_fault_flag(), c = step_fault_flag();
-  if (a < 0 || b < 0 || c < 0) return -1;
-  return (a | b | c) ? 1 : 0;
+  const int a = stream_fault_flag(), b = attention_fault_flag(), c = step_fault_flag(), e = tc5_fault_flag();
+  if (a < 0 || b < 0 || c < 0 || e < 0) return -1;
+  return (a | b | c | e) ? 1 : 0;
 }
 
 /* ------------------------------------------------------------ QuantizedLinear */

@@ -140,6 +140,12 @@ void set_gemv_tuning(int xmode, int rows_per_warp, int warps);
 // Tensor-core kernel for 2 <= M (w4_mma.cu).
 size_t w4_mma_scratch_bytes(int m, int64_t k);
 tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream);
+// tcgen05 kernel for 16 <= M (w4_tc5.cu); its operand images live behind the first 4096 bytes of the same scratch.
+size_t w4_tc5_scratch_bytes(int m, int64_t k);
+bool w4_tc5_supported(const GemvArgs& a);
+tb_status launch_w4_tc5(const GemvArgs& a, void* scratch, cudaStream_t stream);
+void set_tc5_enabled(int on);
+int tc5_fault_flag();
 
 // Persistent TMA-ring kernel for M = 1 (w4_stream.cu).
 bool w4_stream_supported(const GemvArgs& a);

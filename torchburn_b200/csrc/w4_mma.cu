@@ -573,7 +573,10 @@ static size_t digit_bytes(int m, int64_t k) {
   const int mt = (m + 7) / 8;
   return (((size_t)(k / 32) * mt * kTileWords * sizeof(uint32_t)) + 255) & ~(size_t)255;
 }
-size_t w4_mma_scratch_bytes(int m, int64_t k) { return kSplitHeader + digit_bytes(m, k) + kSplitPartBytes; }
+size_t w4_mma_scratch_bytes(int m, int64_t k) {
+  const size_t own = digit_bytes(m, k) + kSplitPartBytes, tc5 = w4_tc5_scratch_bytes(m, k);
+  return kSplitHeader + (own > tc5 ? own : tc5);
+}
 
 // Up to 64 activation rows per pass; `scratch` holds w4_mma_scratch_bytes(min(m, 64), k) and its first
 // 4096 bytes are zero (the decoder clears its block once; a temporary block is cleared per call).
