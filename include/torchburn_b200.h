@@ -190,7 +190,7 @@ void tb_set_attention_chunk(int32_t positions);
 void tb_set_attention_tuning(int32_t ctas_per_sm, int32_t ring_stages);
 /* Tuning hook for the M = 1 GEMV kernels.  product_mode 1 (default): activations are
  * rounded per 32-element block to 24-bit fixed point and multiplied with integer dot
- * products (2 <= M < 16 with integer mma.sync; 16 <= M on tcgen05 with exact bf16 codes and the
+ * products (2 <= M <= 16 with integer mma.sync; 16 < M on tcgen05 with exact bf16 codes and the
  * activations as three bf16 pieces); 0: fp32 products for M = 1; 2: integer products on
  * CUDA cores for every M (no tensor cores); 3: like 1 but the integer mma.sync kernel for every
  * M >= 2 (no tcgen05).  rows_per_warp in {0,1,2,4} and warps in {0,4,8} force

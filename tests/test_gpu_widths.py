@@ -370,7 +370,7 @@ def test_fp32_product_mode_is_selectable_and_matches_oracle(torch, tb, oracle):
 
 
 @pytest.mark.parametrize("n,k,g,m,bias,pair", [
-    (640, 1024, 32, 16, True, False),      # K split over several CTAs (atomic partial sums), bias
+    (640, 1024, 32, 24, True, False),      # K split over several CTAs (atomic partial sums), bias
     (300, 512, 64, 19, False, False),      # rows past n inside the only tile, padded activation rows
     (1001, 2048, 128, 33, True, False),    # a group spans two 64-element stages
     (4096, 4096, 32, 64, False, False),    # o_proj of configuration 4
@@ -380,7 +380,7 @@ def test_fp32_product_mode_is_selectable_and_matches_oracle(torch, tb, oracle):
     (14336, 4096, 32, 64, False, True),    # Llama gate/up at M = 64
 ])
 def test_tcgen05_batched_product_matches_oracle(torch, tb, oracle, n, k, g, m, bias, pair):
-    """16 and more activation rows take the tcgen05 kernel (bf16 codes from tensor memory, three
+    """More than 16 activation rows take the tcgen05 kernel (bf16 codes from tensor memory, three
     bf16 pieces of every activation, the scale applied per group outside the tensor core).  It
     must stay as close to the float64 result as the reference's own fp32 kernel, and agree with
     the integer mma.sync kernel it replaces (tb_set_gemv_tuning(3, ..) keeps that one selectable)."""

@@ -36,7 +36,6 @@ constexpr int kWR = kStageRows / kCW;  // rows of a stage that one consumer warp
 constexpr int kRG = kWR / 4;           // groups of 4 rows per warp and stage (2)
 constexpr int kMaxGq = 8;              // q heads per kv head
 constexpr int kMaxStages = 8;
-constexpr int kClusterCtas = 16;       // cluster form: CTAs per (sequence, kv head)
 constexpr int kChunkRows = 512;        // positions whose scores are held in shared memory at a time
 constexpr int kSeqCap = 32768;         // src/llm/decoder.rs:1180
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: a wait that long means a lost copy
@@ -60,12 +59,10 @@ struct AttnParams {
   int nc;           // CTAs per (sequence, kv head) = gridDim.x
   int stages;       // ring depth
   int max_parts;    // upper bound of CTAs of a (sequence, kv head) that take positions
-  int cluster;      // CTAs of a (sequence, kv head) form one thread-block cluster and merge through shared memory
   int region_floats;  // floats of the ring region (also holds the combine / merge buffers)
   int64_t max_seq_len;
   int per_call_tables;
   float scale;
-  PrefetchList prefetch;
   unsigned long long* tl;  // timestamps of this launch or null
 };
 
@@ -367,8 +364,6 @@ __global__ void TB_ATTN_BOUNDS attn_decode_kernel(const AttnParams p) {
 
   if (warp == kCW) {
     // ---------------- producer: one lane feeds the ring ----------------
-    if (lane == 1)
-      prefetch_l2_slice(p.prefetch, cta_lin, (int)(gridDim.x * gridDim.y * gridDim.z));
     if (lane == 0) {
       int i = 0;
       bool lost = false;
@@ -581,10 +576,6 @@ __global__ void TB_ATTN_BOUNDS attn_decode_kernel(const AttnParams p) {
       float o = 0.f;
 #pragma unroll
       for (int w = 0; w < kCW; ++w) o += w_acc[((size_t)w * gq + g) * D + e];
-      if (p.cluster) {
-        region[(size_t)kCW * gq * D + i] = o;  // behind the warps' buffers; read by the whole cluster below
-        continue;
-      }
       const int h = kvh * gq + g;
       p.part_o[(((int64_t)b * p.num_heads + h) * p.nc + split) * D + e] = o;
       if (e == 0) {
@@ -593,56 +584,6 @@ __global__ void TB_ATTN_BOUNDS attn_decode_kernel(const AttnParams p) {
         dst[1] = s_ml[1][g];
       }
     }
-  }
-
-  if (p.cluster) {
-    // ---- merge inside the cluster: no scratch memory, no fence, no ticket ----
-    // Every CTA holds its partial (weighted V in `region`, max and sum in s_ml) in its own
-    // shared memory.  After a cluster barrier CTA r normalises elements [r*S, (r+1)*S) of the
-    // gq*D outputs, reading the nr partials of those elements from its peers (distributed shared
-    // memory); a second barrier keeps every CTA's memory alive until all peers have read it.
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    const int nr = (int)gridDim.x;   // the cluster spans the grid's x dimension
-    const int total = gq * D;
-    const int S_ = (total + nr - 1) / nr;
-    const int e = split * S_ + tid;
-    if (tid < S_ && e < total) {
-      const int g = e / D;
-      const uint32_t a_o = smem_u32(region + (size_t)kCW * gq * D + e);
-      const uint32_t a_m = smem_u32(&s_ml[0][g]), a_l = smem_u32(&s_ml[1][g]);
-      float mx = -INFINITY;
-      float mv[16], lv[16], ov[16];
-#pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        mv[r] = -INFINITY; lv[r] = 0.f; ov[r] = 0.f;
-        if (r < nr) {
-          uint32_t ra;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a_m), "r"(r));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mv[r]) : "r"(ra) : "memory");
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a_l), "r"(r));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lv[r]) : "r"(ra) : "memory");
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a_o), "r"(r));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ov[r]) : "r"(ra) : "memory");
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < 16; ++r) mx = fmaxf(mx, mv[r]);
-      float tot = 0.f, acc_o = 0.f;
-#pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        if (mv[r] != -INFINITY) {  // CTAs without positions hold no partial
-          const float w = expf(mv[r] - mx);
-          tot = fmaf(lv[r], w, tot);
-          acc_o = fmaf(ov[r], w, acc_o);
-        }
-      }
-      // no position at all (invalid offset): zeros, like the other path
-      p.out[((int64_t)b * p.num_heads + kvh * gq) * D + e] = mx == -INFINITY ? 0.f : acc_o * (1.0f / fmaxf(tot, 1e-30f));
-    }
-    if (tid == 0 && s_abort) atomicExch(&g_attn_fault, 1);
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (tid == 0) tl_mark(p.tl, cta_lin, 5);
-    return;
   }
 
   // ---- ticket: the last CTA of this (sequence, kv head) merges the partials ----
@@ -791,13 +732,10 @@ AttnLayout attn_layout(int batch, int num_heads, int num_kv_heads, int head_dim,
   const int64_t cap = max_seq_len < kSeqCap ? max_seq_len : kSeqCap;
   const int64_t cols = (int64_t)batch * num_kv_heads;
   // Ring depth: 96 KB of stages for head_dim 128 (two CTAs per SM), fewer bytes for narrower heads.
-  static const int e_cps = getenv("TB_ATTN_CPS") ? atoi(getenv("TB_ATTN_CPS")) : 0;
-  static const int e_stages = getenv("TB_ATTN_STAGES") ? atoi(getenv("TB_ATTN_STAGES")) : 0;
-  const int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (e_cps > 0 ? e_cps : 2);
+  const int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : 2;
   L.stages = head_dim == 128 ? 6 : 8;
   if (cps == 1 && L.stages < 8) L.stages = 8;
   if (g_ring_stages > 0) L.stages = g_ring_stages;
-  else if (e_stages > 0) L.stages = e_stages;
   if (L.stages > kMaxStages) L.stages = kMaxStages;
   if (g_chunk_override > 0) {
     L.fixed_per = g_chunk_override;
@@ -856,36 +794,8 @@ static tb_status launch_attn(const AttnParams& p, const cudaLaunchConfig_t& cfg)
   if (cfg.dynamicSmemBytes > 32 * 1024)
     TB_CUDA_TRY(cudaFuncSetAttribute(attn_decode_kernel<D, GQM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)cfg.dynamicSmemBytes));
-  if (p.cluster)
-    TB_CUDA_TRY(cudaFuncSetAttribute(attn_decode_kernel<D, GQM>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
   TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<D, GQM>, p));
   return TB_OK;
-}
-
-// How many clusters of `cfg`'s shape can be resident at once (0 when the shape cannot launch).
-template <int D, int GQM>
-static int max_clusters(const cudaLaunchConfig_t& cfg) {
-  auto kern = attn_decode_kernel<D, GQM>;
-  if (cfg.dynamicSmemBytes > 32 * 1024 &&
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes) != cudaSuccess)
-    return 0;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) return 0;
-  int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
-    cudaGetLastError();
-    return 0;
-  }
-  return n;
-}
-
-template <int D>
-static int max_clusters_d(const cudaLaunchConfig_t& cfg, int gqm) {
-  switch (gqm) {
-    case 1: return max_clusters<D, 1>(cfg);
-    case 2: return max_clusters<D, 2>(cfg);
-    case 4: return max_clusters<D, 4>(cfg);
-    default: return max_clusters<D, 8>(cfg);
-  }
 }
 
 template <int D>
@@ -914,16 +824,6 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
     return fail(TB_ERR_ARG, "attention: the KV caches must be 16-byte aligned");
 
   AttnLayout L = attn_layout(a.batch, a.num_heads, a.num_kv_heads, a.head_dim, a.max_seq_len);
-  // Cluster form: the 16 CTAs of a (sequence, kv head) are one thread-block cluster (one CTA per SM)
-  // and merge through distributed shared memory.  Only when every cluster can be resident at once.
-  static const int e_cluster = getenv("TB_ATTN_CLUSTER") ? atoi(getenv("TB_ATTN_CLUSTER")) : 0;
-  const int64_t cols = (int64_t)a.batch * a.num_kv_heads;
-  bool want_cluster = e_cluster != 0 && g_chunk_override == 0 && g_ctas_per_sm == 0 && cols * kClusterCtas <= 2 * sm_count() &&
-                      max_splits(a.max_seq_len) >= kClusterCtas;
-  if (want_cluster) {  // ring sized for two CTAs per SM as in the ticket form: a GPC then holds a cluster on 8 SMs
-    L.nc = kClusterCtas;
-    L.fixed_per = 0;
-  }
   if (L.fixed_per && (L.fixed_per < 64 || L.fixed_per > 512 || (L.fixed_per & (L.fixed_per - 1))))
     return fail(TB_ERR_ARG, "attention: chunk %d is not a power of two in [64, 512]", L.fixed_per);
   if (L.nc > max_splits(a.max_seq_len)) return fail(TB_ERR_SHAPE, "attention: %d splits exceed the scratch layout", L.nc);
@@ -941,8 +841,7 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.qkv_rot_out = a.q_rot_out;
   p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.gq = gq;
   p.fixed_per = L.fixed_per; p.nc = L.nc; p.stages = L.stages;
-  static const int e_max_parts = getenv("TB_ATTN_MAX_PARTS") ? atoi(getenv("TB_ATTN_MAX_PARTS")) : 48;
-  p.max_parts = max(1, e_max_parts);
+  p.max_parts = 48;
   // two CTAs per SM when the ring can be cut to make room (wide heads with many q heads per kv head)
   int stages = L.stages;
   while (stages > 3 && 2 * (sizeof(float) * (attn_fixed_floats(D, gq, gqm) + attn_region_floats(D, gq, L.nc, stages)) + 2048) > 227 * 1024)
@@ -953,7 +852,6 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.max_seq_len = a.max_seq_len;
   p.per_call_tables = a.per_call_tables ? 1 : 0;
   p.scale = 1.0f / sqrtf((float)a.head_dim);
-  p.prefetch = a.prefetch;
   p.tl = timeline_next_block();
 
   const size_t smem = sizeof(float) * (attn_fixed_floats(D, gq, gqm) + region);
@@ -969,29 +867,6 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
-  }
-  p.cluster = 0;
-  if (want_cluster) {
-    attr[na].id = cudaLaunchAttributeClusterDimension;
-    attr[na].val.clusterDim.x = kClusterCtas;
-    attr[na].val.clusterDim.y = 1;
-    attr[na].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = na + 1;
-    // ask once per shape whether that many clusters fit; otherwise keep the ticket form
-    static thread_local int ok_key = -1, ok_val = 0;
-    const int key = D * 1000000 + gqm * 10000 + (int)(smem >> 10);
-    if (ok_key != key) {
-      ok_val = D == 128 ? max_clusters_d<128>(cfg, gqm) : (D == 64 ? max_clusters_d<64>(cfg, gqm) : max_clusters_d<32>(cfg, gqm));
-      ok_key = key;
-    }
-    if (ok_val >= cols) {
-      p.cluster = 1;
-      ++na;
-    } else {
-      return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: attention cluster form: %d clusters of %d CTAs fit, %lld needed", ok_val,
-                  kClusterCtas, (long long)cols);
-    }
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;

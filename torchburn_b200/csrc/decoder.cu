@@ -101,9 +101,6 @@ struct tb_decoder {
   // its K/V tile copies early; the persistent GEMV kernels run slower when they are made
   // resident before their predecessor has finished, so they keep plain stream order.
   int pdl_mask = 2;
-  // L2 prefetch chain (PrefetchList): measured on B200 it does not pay - the kernels are bound by
-  // their own latency chains, not by HBM - so it is off unless TB_L2_PREFETCH=1.
-  bool prefetch_chain = false;
   int64_t kv_used = 0;
   int last_batch = 1;
   bool device_lost = false;
@@ -166,22 +163,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     return TB_OK;
   };
   TB_TRY(snap(d->dbg_embed, d->x, d->H));
-  // L2 prefetch chain (see PrefetchList): each kernel requests what the kernels after it read.
   const bool sn = d->split_norm && b == 1 && !debug && (d->tp == 1 || tp_low_latency(d->tpst, b, d->H));
-  const bool pfc = d->prefetch_chain && !debug;
-  const size_t wq = (size_t)(d->H / 2), sq = sizeof(float) * (size_t)(d->H / d->G);
-  auto add_mat = [&](PrefetchList& pf, const uint8_t* w, const float* sc, int64_t n, int64_t k) {
-    if (!pfc) return;
-    pf.add(w, (size_t)n * (k / 2));
-    pf.add(sc, sizeof(float) * (size_t)n * (k / d->G));
-  };
-  auto add_kv = [&](PrefetchList& pf, int layer) {
-    if (!pfc || layer >= d->L) return;
-    const size_t bytes = sizeof(float) * (size_t)b * d->nkv_l * d->S * d->hd;
-    pf.add(d->k_cache + (size_t)layer * kv_layer_stride(d), bytes);
-    pf.add(d->v_cache + (size_t)layer * kv_layer_stride(d), bytes);
-  };
-  (void)wq; (void)sq;
   for (int l = 0; l < d->L; ++l) {
     const LayerDev& W = d->layers[l];
     const bool dbg = debug && l == 0;
@@ -192,7 +174,6 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.x_normed_out = dbg ? d->dbg_normed : nullptr;
       if (sn && l > 0) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
       a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && ((pm & 1) || (b > 1 && (pm & 64)));
-      if (l == 0) add_kv(a.prefetch, 0);  // later layers: requested by the previous layer's gate/up
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
       ++launches;
@@ -206,9 +187,6 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.scratch = d->attn_scratch; a.q_rot_out = dbg ? d->dbg_qkv : nullptr;
       a.batch = b; a.num_heads = d->nh_l; a.num_kv_heads = d->nkv_l; a.head_dim = d->hd;
       a.max_seq_len = d->S; a.pdl = pdl && !debug && (pm & 2);
-      add_mat(a.prefetch, W.o_w, W.o_s, d->H, d->q_dim_l);
-      add_mat(a.prefetch, W.gate_w, W.gate_s, d->I_l, d->H);
-      add_mat(a.prefetch, W.up_w, W.up_s, d->I_l, d->H);
       // The kernel strides sequences by [Hkv, S, d]; with batch > 1 that is the layout of
       // one layer's block [B][Hkv][S][d].
       TB_TRY(launch_attention_decode(a, st));
@@ -219,7 +197,6 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       GemvArgs a;
       a.x = d->attn; a.w = W.o_w; a.scales = W.o_s; a.m = b; a.n = d->H; a.k = d->q_dim_l; a.g = d->G;
       a.pdl = pdl && !debug && ((pm & 4) || (b > 1 && (pm & 64)));
-      add_mat(a.prefetch, W.down_w, W.down_s, d->H, d->I_l);
       if (d->tp == 1) { a.out = d->x; a.resid = d->x; }
       else { a.out = tp_partial_buffer(d->tpst, d->partial); }
       if (sn && d->tp == 1) { a.out_scaled = d->xn; a.out_scale_w = W.post_norm_w; a.out_ss8 = d->ss8; }
@@ -239,12 +216,9 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       if (sn) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
       a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && ((pm & 8) || (b > 1 && (pm & 64)));
       if (l + 1 < d->L) {
-        add_mat(a.prefetch, d->layers[l + 1].qkv_w, d->layers[l + 1].qkv_s, d->tq_l, d->H);
-        add_kv(a.prefetch, l + 1);
       } else {
         // the head of lm_head that fits next to what is still in flight
         const int64_t rows = d->V_l < 24576 ? d->V_l : 24576;
-        add_mat(a.prefetch, d->lm_w, d->lm_s, rows, d->H);
       }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
@@ -524,15 +498,12 @@ tb_status tb_decoder_create(tb_decoder** out, const tb_model_config* cfg,
   d->tq_l = d->q_dim_l + 2ll * d->nkv_l * d->hd;
   d->use_graph = !(c.flags & TB_DECODER_NO_GRAPH);
   d->pdl = !(c.flags & TB_DECODER_NO_PDL);
-  if (const char* pmv = getenv("TB_PDL_MASK")) d->pdl_mask = atoi(pmv);
-  if (const char* pfv = getenv("TB_L2_PREFETCH")) d->prefetch_chain = atoi(pfv) != 0;
   {
     // Split RMSNorm needs the persistent M = 1 kernel for every projection of a layer.
     auto ok_k = [&](int64_t k) { return k % 32 == 0 && k >= 2048 && k <= 15360 && ((k / d->G) * 4) % 16 == 0; };
     // one GPU: producers are the O / down kernels (all three K must qualify); tensor parallel: the
     // producer is the low-latency exchange kernel, only the consumers (K = H) must qualify
     d->split_norm = tp == 1 ? (ok_k(d->H) && ok_k(d->q_dim_l) && ok_k(d->I_l)) : ok_k(d->H);
-    if (const char* snv = getenv("TB_SPLIT_NORM")) d->split_norm = d->split_norm && atoi(snv) != 0;
   }
   cudaGetDevice(&d->device);
 

@@ -38,40 +38,6 @@ int sm_count();
 // Copies `bytes` from host or device memory into a fresh device allocation.
 tb_status upload(void** dst, const void* src, size_t bytes, tb_space space);
 
-// Operands of kernels that run LATER in the same stream.  A kernel that is given such a list
-// asks the L2 (126 MB on B200) to fetch them while it works on its own data: every CTA issues
-// cp.async.bulk.prefetch.L2 for its slice.  The requests are hints: nothing waits for them and
-// nothing depends on them, they only keep HBM busy during the latency-bound parts of a step.
-struct PrefetchList {
-  const void* ptr[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-  unsigned long long bytes[6] = {0, 0, 0, 0, 0, 0};
-  void add(const void* p, size_t b) {
-    for (int i = 0; i < 6; ++i)
-      if (bytes[i] == 0) { ptr[i] = p; bytes[i] = b; return; }
-  }
-};
-
-#ifdef __CUDACC__
-// Called by ONE thread of CTA `cta` of `nctas`: requests this CTA's share of every entry.
-__device__ __forceinline__ void prefetch_l2_slice(const PrefetchList& pf, int cta, int nctas) {
-  constexpr unsigned long long kPiece = 16384;
-#pragma unroll 1
-  for (int i = 0; i < 6; ++i) {
-    const unsigned long long total = pf.bytes[i] & ~15ull;
-    if (total == 0) continue;
-    const unsigned long long pieces = (total + kPiece - 1) / kPiece;
-    const unsigned long long per = (pieces + nctas - 1) / nctas;
-    const unsigned long long p0 = (unsigned long long)cta * per;
-#pragma unroll 1
-    for (unsigned long long q = p0; q < p0 + per && q < pieces; ++q) {
-      const unsigned long long off = q * kPiece;
-      const unsigned int sz = (unsigned int)(total - off < kPiece ? total - off : kPiece);
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(pf.ptr[i]) + off), "r"(sz) : "memory");
-    }
-  }
-}
-#endif
-
 // ---- per-CTA timestamps of the hot kernels (off unless a buffer was registered) -------------
 // The role of the reference's timestamp queries (src/wgpu/profiler.rs).  Every launch of an
 // instrumented kernel gets the next block of kTlBlock 64-bit words of the registered device
@@ -127,7 +93,6 @@ struct GemvArgs {
   int64_t n = 0, k = 0;
   int g = 32;
   bool pdl = false;                // launch with programmatic stream serialization
-  PrefetchList prefetch;           // operands of later kernels to pull into L2 meanwhile
   void* xq_scratch = nullptr;      // m > 1: room for the digit form of x (w4_mma_scratch_bytes);
                                    // null = allocate on the stream for the duration of the call
 };
@@ -140,7 +105,7 @@ void set_gemv_tuning(int xmode, int rows_per_warp, int warps);
 // Tensor-core kernel for 2 <= M (w4_mma.cu).
 size_t w4_mma_scratch_bytes(int m, int64_t k);
 tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream);
-// tcgen05 kernel for 16 <= M (w4_tc5.cu); its operand images live behind the first 4096 bytes of the same scratch.
+// tcgen05 kernel for 16 < M (w4_tc5.cu); its operand images live behind the first 4096 bytes of the same scratch.
 size_t w4_tc5_scratch_bytes(int m, int64_t k);
 bool w4_tc5_supported(const GemvArgs& a);
 tb_status launch_w4_tc5(const GemvArgs& a, void* scratch, cudaStream_t stream);
@@ -167,7 +132,6 @@ struct AttnArgs {
   int64_t max_seq_len = 0;
   bool per_call_tables = false; // cos/sin hold one row per sequence instead of a table
   bool pdl = false;
-  PrefetchList prefetch;        // operands of later kernels to pull into L2 meanwhile
 };
 size_t attention_scratch_bytes(int batch, int num_heads, int num_kv_heads, int head_dim,
                                int64_t max_seq_len);

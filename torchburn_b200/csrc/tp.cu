@@ -287,9 +287,8 @@ float* tp_partial_buffer(TpState* st, float* fallback) {
 }
 
 bool tp_low_latency(const TpState* st, int batch, int64_t hidden) {
-  static const int e_ll = getenv("TB_TP_LL") ? atoi(getenv("TB_TP_LL")) : 1;
   const size_t count = (size_t)batch * hidden;
-  return st && st->fused && e_ll != 0 && (count & 7) == 0 && count / 2 <= (size_t)kLLLines;
+  return st && st->fused && (count & 7) == 0 && count / 2 <= (size_t)kLLLines;
 }
 
 tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int batch, int64_t hidden,

@@ -436,7 +436,7 @@ tb_status launch_epi(int m, const GemvParams& p, bool pdl, cudaStream_t stream) 
 
 void set_gemv_tuning(int xmode, int rows_per_warp, int warps) {
   g_mma_enabled = xmode == 2 ? 0 : 1;  // 2: integer products on CUDA cores for every M
-  set_tc5_enabled(xmode == 3 ? 0 : 1);  // 3: the mma.sync integer kernel also for M >= 16
+  set_tc5_enabled(xmode == 3 ? 0 : 1);  // 3: the mma.sync integer kernel also for M > 16
   g_xmode = xmode != 0 ? 1 : 0;
   g_force_r = rows_per_warp;
   g_force_warps = warps;
@@ -475,7 +475,7 @@ tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
   if (a.x_ss8 || a.out_scaled || a.out_ss8)
     return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: the split RMSNorm needs the persistent M = 1 kernel for this shape");
   if (a.m >= 2 && g_mma_enabled && ((a.k / 2) % 16) == 0) {
-    const bool tc5 = w4_tc5_supported(a);   // 16 and more rows: tcgen05, operand images behind the ticket header
+    const bool tc5 = w4_tc5_supported(a);   // more than 16 rows: tcgen05, operand images behind the ticket header
     if (a.xq_scratch) return tc5 ? launch_w4_tc5(a, static_cast<char*>(a.xq_scratch) + 4096, stream) : launch_w4_mma(a, a.xq_scratch, stream);
     void* tmp = nullptr;
     TB_CUDA_TRY(cudaMallocAsync(&tmp, w4_mma_scratch_bytes(a.m < 64 ? a.m : 64, a.k), stream));

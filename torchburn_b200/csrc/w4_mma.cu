@@ -117,182 +117,19 @@ struct MmaParams {
   const float* resid;
   float* out;
   int m, n, k, nb32, gshift, ng, mt_total;
-  int pdl;             // launched with programmatic stream serialization (the rows layout only)
+  int pdl;             // launched with programmatic stream serialization
   int ksplit;          // CTAs that share a row tile and split K (1 = none)
   float* ksplit_part;  // gridDim.y > 1: partial sums [y][x][row tile][activation tile][4][32]
   int* ksplit_cnt;     // gridDim.y > 1: one ticket per blockIdx.x, zero before the first launch, left zero
 };
 
-// 4 warps = WR row groups (16 weight rows each) x WM groups of MT activation tiles (8 rows
-// each).  KC blocks of K per pipeline stage, two stages (cp.async).
-// SPLITK (one activation tile only): the four warps share the same 16 weight rows and take
-// every fourth block of K instead, so that a narrow matrix still fills the machine.
-template <int MT, int WM, int EPI, int KC, bool SPLITK>
-__global__ void __launch_bounds__(128) w4_mma_kernel(const MmaParams p) {
-  constexpr int NW = EPI == 1 ? 2 : 1;
-  constexpr int WR = SPLITK ? 1 : 4 / WM;
-  constexpr int RC = 16 * WR;             // weight rows per CTA
-  constexpr int MTC = MT * WM;            // activation tiles per CTA
-  constexpr int WROW = KC * 4 + 4;        // words per staged weight row (16 bytes of padding)
-  extern __shared__ __align__(16) uint32_t sm[];
-  // stage layout: weights [NW][RC][WROW] | digits [KC][MTC][208]
-  constexpr int W_WORDS = NW * RC * WROW;
-  constexpr int X_WORDS = KC * MTC * kTileWords;
-  constexpr int STAGE = W_WORDS + X_WORDS;
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const int wr = SPLITK ? 0 : warp / WM, wm = SPLITK ? 0 : warp % WM;
-  const int row_base = blockIdx.x * RC;
-  const int mt0 = blockIdx.y * MTC;       // first activation tile of this CTA
-  const int64_t bpr = (int64_t)p.k >> 1;
-  const int nchunks = (p.nb32 + KC - 1) / KC;
-
-  auto issue = [&](int chunk, int stage) {
-    uint32_t* ws = sm + stage * STAGE;
-    uint32_t* xs = ws + W_WORDS;
-    const int b0 = chunk * KC;
-    // weights: RC rows x KC 16-byte pieces per matrix
-    for (int i = tid; i < NW * RC * KC; i += 128) {
-      const int q = i / (RC * KC), r = (i / KC) % RC, c = i % KC;
-      const int row = min(row_base + r, p.n - 1);
-      const int blk = min(b0 + c, p.nb32 - 1);
-      cp_async16(ws + (q * RC + r) * WROW + c * 4, p.w[q] + (int64_t)row * bpr + (int64_t)blk * 16);
-    }
-    // digits: KC x MTC tiles of 832 bytes
-    for (int i = tid; i < KC * MTC * (kTileWords / 4); i += 128) {
-      const int piece = i % (kTileWords / 4), tile = i / (kTileWords / 4);
-      const int c = tile / MTC, mt = tile % MTC;
-      const int blk = min(b0 + c, p.nb32 - 1);
-      const int mtg = min(mt0 + mt, p.mt_total - 1);
-      cp_async16(xs + (c * MTC + mt) * kTileWords + piece * 4,
-                 p.xq + ((size_t)blk * p.mt_total + mtg) * kTileWords + piece * 4);
-    }
-    cp_async_commit();
-  };
-
-  float acc[NW][MT][4];
-#pragma unroll
-  for (int q = 0; q < NW; ++q)
-#pragma unroll
-    for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[q][nt][i] = 0.f;
-
-  pdl_wait();
-  const int r0 = min(row_base + wr * 16 + g, p.n - 1), r1 = min(row_base + wr * 16 + g + 8, p.n - 1);
-  issue(0, 0);
-  for (int ch = 0; ch < nchunks; ++ch) {
-    if (ch + 1 < nchunks) {
-      issue(ch + 1, (ch + 1) & 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    const uint32_t* ws = sm + (ch & 1) * STAGE;
-    const uint32_t* xs = ws + W_WORDS;
-#pragma unroll
-    for (int c = 0; c < KC; ++c) {
-      const int blk = ch * KC + c;
-      if (blk < p.nb32 && (!SPLITK || (c & 3) == warp)) {
-        const int sidx = blk >> p.gshift;
-#pragma unroll
-        for (int q = 0; q < NW; ++q) {
-          const uint32_t w0 = ws[(q * RC + wr * 16 + g) * WROW + c * 4 + t];
-          const uint32_t w1 = ws[(q * RC + wr * 16 + g + 8) * WROW + c * 4 + t];
-          const uint32_t a[4] = {w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu};
-          const float s0 = __ldg(p.scales[q] + (int64_t)r0 * p.ng + sidx);
-          const float s1 = __ldg(p.scales[q] + (int64_t)r1 * p.ng + sidx);
-#pragma unroll
-          for (int nt = 0; nt < MT; ++nt) {
-            const uint32_t* tile = xs + (c * MTC + wm * MT + nt) * kTileWords;
-            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0}, c2[4] = {0, 0, 0, 0};
-            mma_u8u8(c0, a, tile[(0 * 4 + t) * 8 + g], tile[(3 * 4 + t) * 8 + g]);
-            mma_u8u8(c1, a, tile[(1 * 4 + t) * 8 + g], tile[(4 * 4 + t) * 8 + g]);
-            mma_u8s8(c2, a, tile[(2 * 4 + t) * 8 + g], tile[(5 * 4 + t) * 8 + g]);
-            const float2 sx = *reinterpret_cast<const float2*>(tile + 192 + 2 * t);
-            const float2 cr = *reinterpret_cast<const float2*>(tile + 200 + 2 * t);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float f = fmaf(65536.0f, (float)c2[i], (float)(c0[i] + (c1[i] << 8)));
-              const float d = fmaf((i & 1) ? sx.y : sx.x, f, (i & 1) ? cr.y : cr.x);
-              acc[q][nt][i] = fmaf(d, (i & 2) ? s1 : s0, acc[q][nt][i]);
-            }
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
-
-  if (SPLITK) {
-    // sum the four warps' partial accumulators (they cover disjoint blocks of K)
-    float* red = reinterpret_cast<float*>(sm);
-#pragma unroll
-    for (int q = 0; q < NW; ++q)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) red[((warp * NW + q) * 4 + i) * 32 + lane] = acc[q][0][i];
-    __syncthreads();
-    if (warp != 0) return;
-#pragma unroll
-    for (int q = 0; q < NW; ++q)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) v += red[((w * NW + q) * 4 + i) * 32 + lane];
-        acc[q][0][i] = v;
-      }
-  }
-  // accumulator i: row (g + 8 * (i >> 1)), activation row (tile * 8 + 2 * t + (i & 1))
-#pragma unroll
-  for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = row_base + wr * 16 + g + 8 * (i >> 1);
-      const int m = (mt0 + wm * MT + nt) * 8 + 2 * t + (i & 1);
-      if (row >= p.n || m >= p.m) continue;
-      float v;
-      if (EPI == 1) {
-        const float gg = acc[0][nt][i] + (p.bias[0] ? p.bias[0][row] : 0.f);
-        const float uu = acc[NW - 1][nt][i] + (p.bias[1] ? p.bias[1][row] : 0.f);
-        v = (gg / (1.0f + expf(-gg))) * uu;  // src/quantization/fused_ops.rs:1305-1311
-      } else {
-        v = acc[0][nt][i] + (p.bias[0] ? p.bias[0][row] : 0.f);
-        if (p.resid) v = p.resid[(int64_t)m * p.n + row] + v;
-      }
-      p.out[(int64_t)m * p.n + row] = v;
-    }
-}
-
-template <int MT, int WM, int EPI, int KC, bool SPLITK>
-tb_status launch_mma_cfg(const MmaParams& p, cudaStream_t stream) {
-  constexpr int NW = EPI == 1 ? 2 : 1;
-  constexpr int WR = SPLITK ? 1 : 4 / WM, RC = 16 * WR, MTC = MT * WM;
-  constexpr size_t smem = 2 * sizeof(uint32_t) * ((size_t)NW * RC * (KC * 4 + 4) + (size_t)KC * MTC * kTileWords);
-  auto kern = w4_mma_kernel<MT, WM, EPI, KC, SPLITK>;
-  static thread_local bool configured[64] = {false};
-  int dev = 0;
-  TB_CUDA_TRY(cudaGetDevice(&dev));
-  if (smem > 32 * 1024 && (dev >= 64 || !configured[dev])) {
-    TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (dev < 64) configured[dev] = true;
-  }
-  dim3 grid((unsigned)((p.n + RC - 1) / RC), (unsigned)((p.mt_total + MTC - 1) / MTC));
-  kern<<<grid, 128, smem, stream>>>(p);
-  TB_CUDA_TRY(cudaGetLastError());
-  return TB_OK;
-}
-
 // ------------------------------------------------------------------------------------------
-// Second layout of the same products: every warp keeps 16 weight rows for ALL activation tiles
-// (MT tiles of 8 activation rows, accumulators in registers), WR such warps stand side by side
-// and WK warps split the blocks of K of each stage, so that a CTA covers 16 * WR rows and the
-// digit tiles of a stage - which every warp needs - are fetched once per 16 * WR rows instead
-// of once per 16 or 32.  With 64 activation rows the digits are 13 times the bytes of the
-// weights they meet; re-reading them per small row tile was what bounded the first layout.
-// Scales ride in the stage too (no global load inside the K loop); three cp.async stages.
+// Every warp keeps 16 weight rows for ALL activation tiles (MT tiles of 8 activation rows,
+// accumulators in registers), WR such warps stand side by side and WK warps split the blocks
+// of K of each stage, so that a CTA covers 16 * WR rows and the digit tiles of a stage - which
+// every warp needs - are fetched once per 16 * WR rows.  With 64 activation rows the digits
+// are 13 times the bytes of the weights they meet.  Scales ride in the stage too (no global
+// load inside the K loop); three cp.async stages.
 // ------------------------------------------------------------------------------------------
 template <int MT, int WR, int WK, int EPI, int KC>
 __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaParams p) {
@@ -528,9 +365,6 @@ template <int MT, int EPI, int KC>
 tb_status launch_rows_mt(const MmaParams& p, cudaStream_t stream) {
   // rows per CTA so that the grid is about one CTA per SM or more; narrow matrices split K over warps
   const int per_sm = p.n / sm_count();
-  static const int e_shape = getenv("TB_MMA_ROWS_SHAPE") ? atoi(getenv("TB_MMA_ROWS_SHAPE")) : 0;  // 24, 22: force WR WK
-  if (e_shape == 24) return launch_rows_cfg<MT, 2, 4, EPI, KC>(p, stream);
-  if (e_shape == 22) return launch_rows_cfg<MT, 2, 2, EPI, KC>(p, stream);
   // Few activation tiles: the digits are small, so many small CTAs (32 rows, 3-4 resident per SM) keep more
   // warps in flight than one CTA of 96 rows per SM; many tiles: the digit traffic decides, large CTAs.
   // Measured on the Llama-3-8B shapes (tokens/s of the whole step, 32 rows per CTA in every case):
@@ -546,20 +380,6 @@ tb_status launch_rows_epi(const MmaParams& p, cudaStream_t stream) {
   if (p.mt_total <= 2) return launch_rows_mt<2, EPI, 8>(p, stream);
   if (p.mt_total <= 4) return launch_rows_mt<4, EPI, 4>(p, stream);
   return launch_rows_mt<8, EPI, 4>(p, stream);
-}
-
-template <int EPI>
-tb_status launch_mma_epi(const MmaParams& p, cudaStream_t stream) {
-  // activation tiles of 8 rows: 1 -> (MT 1, WM 1), 2 -> (1, 2), 3..4 -> (2, 2), 5..8 -> (4, 2)
-  if (p.mt_total <= 1) {
-    // narrow matrices: 16 rows per CTA with the warps splitting K keeps >= 1 CTA per SM busy
-    static const int e_thr = getenv("TB_MMA_SPLITK_BELOW") ? atoi(getenv("TB_MMA_SPLITK_BELOW")) : 64 * 2 * sm_count();
-    if (p.n < e_thr) return launch_mma_cfg<1, 1, EPI, 8, true>(p, stream);
-    return launch_mma_cfg<1, 1, EPI, 8, false>(p, stream);
-  }
-  if (p.mt_total <= 2) return launch_mma_cfg<1, 2, EPI, 8, false>(p, stream);
-  if (p.mt_total <= 4) return launch_mma_cfg<2, 2, EPI, 8, false>(p, stream);
-  return launch_mma_cfg<4, 2, EPI, 4, false>(p, stream);
 }
 
 }  // namespace
@@ -587,8 +407,7 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
   for (int m0 = 0; m0 < a.m; m0 += 64) {
     const int mc = a.m - m0 < 64 ? a.m - m0 : 64;
     const int mt = (mc + 7) / 8;
-    static const int e_layout = getenv("TB_MMA_LAYOUT") ? atoi(getenv("TB_MMA_LAYOUT")) : 2;
-    const bool pdl = a.pdl && e_layout == 2;
+    const bool pdl = a.pdl;
     {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3((unsigned)(mt * 8), (unsigned)((a.k / 32 + 127) / 128));
@@ -607,11 +426,8 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     p.xq = reinterpret_cast<const uint32_t*>(static_cast<char*>(scratch) + kSplitHeader);
     // Narrow single matrices at many activation rows: 32-row CTAs alone leave SMs idle, so 2 or 4 CTAs
     // share a row tile and split K (deterministic sum by the last one to finish).
-    static const int e_ksplit = getenv("TB_MMA_KSPLIT") ? atoi(getenv("TB_MMA_KSPLIT")) : -1;
     int ksplit = 1;
     if (!a.w2 && mt >= 2 && a.n <= kSplitMaxN && a.n / 32 < sm_count() && a.k >= 4096) ksplit = a.k >= 8192 ? 4 : 2;
-    if (e_ksplit >= 0 && !a.w2 && a.n <= kSplitMaxN && a.k >= 1024) ksplit = e_ksplit < 1 ? 1 : (e_ksplit > kSplitMax ? kSplitMax : e_ksplit);
-    if (e_layout != 2) ksplit = 1;
     p.ksplit = ksplit;
     p.ksplit_cnt = reinterpret_cast<int*>(scratch);
     p.ksplit_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + kSplitHeader + digit_bytes(mc, a.k));
@@ -625,8 +441,7 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     p.ng = (int)(a.k / a.g);
     p.mt_total = mt;
     p.pdl = pdl ? 1 : 0;
-    tb_status s = e_layout == 2 ? (a.w2 ? launch_rows_epi<1>(p, stream) : launch_rows_epi<0>(p, stream))
-                                : (a.w2 ? launch_mma_epi<1>(p, stream) : launch_mma_epi<0>(p, stream));
+    tb_status s = a.w2 ? launch_rows_epi<1>(p, stream) : launch_rows_epi<0>(p, stream);
     if (s != TB_OK) return s;
   }
   return TB_OK;

@@ -51,9 +51,7 @@ struct StreamParams {
   int stages;        // ring depth
   int stage_bytes;   // bytes of one stage
   int rounds;        // ceil(n / 8): the unit of work distribution (8 rows)
-  PrefetchList prefetch;
   unsigned long long* tl;  // timestamps of this launch or null
-  int trigger;       // where launch_dependents is signalled: 0 start, 1 after the last stage was requested, 2 end
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -182,9 +180,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
     // The producer must not signal launch_dependents: the next kernel may only start once
     // this grid's consumers are past their griddepcontrol.wait, i.e. once everything before
     // this kernel has completed (kernels further down the chain rely on that).
-    if (lane == 1) prefetch_l2_slice(p.prefetch, (int)blockIdx.x, (int)gridDim.x);
     if (lane == 0) {
-      if (p.trigger == 3) asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int i = 0; i < total_stages; ++i) {
         const int s = i % p.stages, round = i / p.stages;
         if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
@@ -206,8 +202,9 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
           bulk_g2s(d + (size_t)RS * row_bytes, p.scales[q] + (int64_t)row0 * p.ng, sb, &full[s]);
         }
       }
-      if (p.trigger == 1) {
-        // All of this CTA's HBM requests are out: the next kernel may start filling its ring.
+      {
+        // All of this CTA's HBM requests are out: the next kernel may start filling its ring
+        // (launch_dependents is signalled here, after the last stage was requested).
         // Only after the consumers are past their griddepcontrol.wait (completion must stay
         // transitive along the chain of kernels); bounded like every other wait.
         const long long t0 = clock64();
@@ -221,7 +218,6 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   // ---------------- consumers ----------------
   // Everything below reads the previous kernel's output.
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (p.trigger == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) *reinterpret_cast<volatile int*>(&s_waited) = 1;
   if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 1);
 
@@ -395,7 +391,6 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
     buf ^= 1;
   }
   if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 5);
-  if (p.trigger >= 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (s_abort && tid == 0) atomicExch(&g_stream_fault, 1);
 }
 
@@ -480,14 +475,7 @@ bool w4_stream_supported(const GemvArgs& a) {
   return true;
 }
 
-static int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : dflt;
-}
-
 tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
-  static const int e_trigger = env_int("TB_STREAM_TRIGGER", 1), e_cps = env_int("TB_STREAM_CPS", 0),
-                   e_ring = env_int("TB_STREAM_RING_KB", 0), e_epl = env_int("TB_STREAM_EPL", 0);
   StreamParams p;
   p.x = a.x;
   p.w[0] = a.w; p.w[1] = a.w2;
@@ -496,11 +484,9 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   p.norm_w = a.norm_w; p.resid = a.resid; p.out = a.out; p.x_normed_out = a.x_normed_out;
   p.x_ss8 = a.x_ss8; p.out_scaled = a.out_scaled; p.out_scale_w = a.out_scale_w; p.out_ss8 = a.out_ss8;
   p.eps = a.eps;
-  p.prefetch = a.prefetch;
   p.tl = timeline_next_block();
   // Dependents may start once this CTA's last HBM request is out (measured: start, that point and
   // the end of the kernel differ by < 1% on the decode step; the early start helps small kernels).
-  p.trigger = e_trigger;
   p.n = (int)a.n; p.k = (int)a.k; p.nb32 = (int)(a.k / 32);
   p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
   p.ng = (int)(a.k / a.g);
@@ -508,7 +494,7 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   // K split: half a block per lane in the latency regime (few tiles per CTA: more lanes work
   // on each row), a whole block per lane in the throughput regime (fewer instructions per
   // element); wide K runs one CTA per SM with twice the ring.
-  int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (e_cps > 0 ? e_cps : (p.k >= 8192 ? 1 : 3));
+  int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (p.k >= 8192 ? 1 : 3);
   int grid = sm_count() * cps;
   if (grid > p.rounds) grid = p.rounds;
   const int rounds_per_cta = (p.rounds + grid - 1) / grid;
@@ -516,7 +502,6 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   // (N = 4096, K = 7168: 13.6 us against 10.4 us with a whole block per lane)
   int epl = (rounds_per_cta <= 4 && p.nb32 <= 128) ? 16 : 32;
   if (g_force_epl == 16 || g_force_epl == 32) epl = g_force_epl;
-  else if (e_epl == 16 || e_epl == 32) epl = e_epl;
   p.nwarps = (p.k / epl + 31) / 32;
   if (p.nwarps > 15) { epl = 32; p.nwarps = (p.nb32 + 31) / 32; }
   // One consumer group: every consumer warp observes every stage of the ring in order,
@@ -525,7 +510,7 @@ tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
   const int nw = a.w2 ? 2 : 1;
   const int per_row = nw * (p.k / 2 + p.ng * 4);
   // Stage: at most ~20 KB; ring: as many stages as fit the budget (2..8).
-  const int ring_budget = g_ring_kb > 0 ? g_ring_kb * 1024 : (e_ring > 0 ? e_ring * 1024 : (cps >= 3 ? 40 * 1024 : kRingBytesMax / cps));
+  const int ring_budget = g_ring_kb > 0 ? g_ring_kb * 1024 : (cps >= 3 ? 40 * 1024 : kRingBytesMax / cps);
   int rs = 8;
   while (rs > 1 && (rs * per_row > 20 * 1024 || rs * per_row * 3 > ring_budget)) rs >>= 1;
   p.stage_bytes = rs * per_row;

@@ -1,4 +1,4 @@
-// Batched grouped-INT4 product for 16 and more activation rows on the 5th-generation tensor
+// Batched grouped-INT4 product for more than 16 activation rows on the 5th-generation tensor
 // cores (tcgen05): out[m, j] = sum_g scale[j, g] * sum_{k in g} x[m, k] * code(w[j, k])  (+ bias,
 // + residual, or the SwiGLU of a gate/up pair).  gemm_w4a32_grouped, src/quantization/gemv.rs:
 // 1690-1725; fused_swiglu_mlp_batched, src/quantization/fused_ops.rs:1267-1319.
@@ -23,9 +23,12 @@
 //   warps 4-11   two teams of 128 threads (thread = weight row, a team = half of the activation
 //                rows): per group tcgen05.ld of the accumulator, acc += scale * sum; at the
 //                end bias / residual / SwiGLU and the stores (atomic adds when K is split)
-//   warp 12      one lane: bulk copies of the activation images
-//   warp 13      allocates tensor memory; one lane issues the MMAs and commits them to the
-//                "stage free" and "group done" barriers
+//   warps 12-15  one lane each issues MMAs: issuing a tcgen05.mma costs its thread about 50 cycles
+//                whatever its size (measured), six times the arithmetic of a 128 x 16 x 16 MMA, but
+//                several warps issue side by side.  Issuer i owns accumulator slot i and takes every
+//                group of K whose number is i modulo the number of slots (2 or 4); it commits its MMAs
+//                to the "group done" and "stage free" barriers.  Warp 12 also allocates tensor memory.
+// The bulk copies of the activation images are issued by one lane of warp 0.
 //
 // Every wait is bounded.  No cluster features, no multicast.
 #include <cuda_bf16.h>
@@ -40,9 +43,10 @@ constexpr int kTileN = 128;     // weight rows per CTA (the MMA's M)
 constexpr int kKC = 64;         // K elements per stage: one 128-byte row of bf16
 constexpr int kStages = 4;
 constexpr int kPieces = 3;      // bf16 pieces of an activation
-constexpr int kThreads = 14 * 32;
+constexpr int kThreads = 16 * 32;
 constexpr int kAhead = 8;       // chunks of nibbles in flight per weight row
 constexpr int kTmemCols = 512;
+constexpr int kMinRows = 17;     // up to 16 activation rows the integer mma.sync kernel is as fast or faster (measured)
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s
 
 __device__ int g_tc5_fault = 0;
@@ -100,31 +104,67 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   }
 }
-// The same for a whole warp: one answer for all lanes, so that warp-wide instructions stay converged.
+// Ready already (the usual case for the issuing thread)?  One instruction, no loop.
+__device__ __forceinline__ bool mbar_ready(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* s_abort) { return mbar_wait(bar, parity, s_abort); }
+__device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, volatile int* s_abort) {
+  return mbar_ready(bar, parity) ? true : mbar_wait_slow(bar, parity, s_abort);
+}
+// The same for a whole warp.  ONE lane polls: hundreds of threads polling the same barriers keep the
+// barrier unit so busy that the arrivals they are waiting for queue up behind their own polls.  The other
+// lanes take the answer (one answer for all lanes keeps warp-wide instructions converged) and the
+// ordering from the warp barrier.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* s_abort) {
-  const bool ok = mbar_wait(bar, parity, s_abort);
-  return __all_sync(0xffffffffu, ok);
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_fast(bar, parity, s_abort);
+  __syncwarp();
+  return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile of 128-byte rows with the 128-byte swizzle:
-// start address (16-byte units), leading offset 1 (unused with a swizzle), 1024 bytes between
-// groups of 8 rows, descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows with the 128-byte swizzle.
+// Lower word: start address in 16-byte units (bits 0-13), leading offset 1 (bits 16-29, unused
+// with a swizzle).  Upper word: 1024 bytes between groups of 8 rows (bits 32-45, in 16-byte
+// units), descriptor version 1 (bits 46-47), layout type 2 = SWIZZLE_128B (bits 61-63).
 // D (tensor memory, fp32) (+)= A (tensor memory, bf16) * B (shared memory, bf16)^T
-__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
+// b_lo: the lower word of B's shared-memory descriptor (see above); the upper word is the same for every tile.
+// ACC 0: overwrite the accumulator, 1: add to it, 2: decided at run time by `acc`.
+template <int ACC>
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t acc = 0) {
+  constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+  if (ACC == 2) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 bd;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(acc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 bd;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "n"(ACC)
+        : "memory");
+  }
 }
 // Arrives on `bar` once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
@@ -156,15 +196,86 @@ __device__ __forceinline__ void unpack8(uint32_t word, uint32_t* out4) {
   }
 }
 
+struct IssueCtx {
+  uint64_t *full_a, *full_b, *empty, *acc_full, *acc_empty, *drained;   // drained: one per issuer
+  volatile int* s_abort;
+  uint32_t tmem, a_cols, acc_base, acc_cols, b_lo0, stage16, piece16, mp, idesc;
+  int nchunks, slots, nw;
+};
+
+// One MMA-issuing thread of x.slots.  It takes the groups of K whose number is `me` modulo the number of
+// accumulator slots and owns slot `me`.  SPG (K16 steps per group: 2, 4 or 8) is a template parameter so that
+// the unrolled body knows at compile time where a group starts and ends; descriptors are a constant upper
+// word and a lower word that only takes additions.  An issuer skips the stages that hold none of its groups;
+// a stage's "free" barrier counts the issuers that do work in it (its groups: two of 32 elements, else one).
+template <int SPG, int NW>
+__device__ __forceinline__ void issue_loop(const IssueCtx& x, const uint32_t me) {
+  const uint32_t nslots = (uint32_t)x.slots, slot_shift = x.slots == 4 ? 2u : 1u;
+  const uint32_t d_base = x.tmem + x.acc_base + me * x.acc_cols;
+  uint64_t* my_full = &x.acc_full[me];
+  uint64_t* my_empty = &x.acc_empty[me];
+  uint32_t visits = 0;   // groups this issuer has started
+  bool ok = true;
+  for (int c = 0; c < x.nchunks && ok; ++c) {
+    {  // first and last group of this stage: is one of them mine?
+      const uint32_t g0 = ((uint32_t)c * (kKC / 16)) / SPG, g1 = ((uint32_t)c * (kKC / 16) + 3) / SPG;
+      if ((g0 & (nslots - 1)) != me && (g1 & (nslots - 1)) != me) continue;
+    }
+    const uint32_t s = (uint32_t)c & (kStages - 1), par = ((uint32_t)c / kStages) & 1u;
+    ok = mbar_wait_fast(&x.full_a[s], par, x.s_abort) && mbar_wait_fast(&x.full_b[s], par, x.s_abort);
+    if (!ok) break;
+    tc_fence_after();
+    const uint32_t b_lo = x.b_lo0 + s * x.stage16;
+    const uint32_t a_base = x.tmem + s * x.a_cols;
+#pragma unroll
+    for (int ks = 0; ks < kKC / 16; ++ks) {   // 16 bf16 = 32 bytes of a row = 8 columns of tensor memory per MMA
+      const uint32_t t = (uint32_t)c * (kKC / 16) + ks;            // K16 step of this CTA
+      const uint32_t gi = SPG == 2 ? t >> 1 : (SPG == 4 ? t >> 2 : t >> 3);
+      if ((gi & (nslots - 1)) != me) continue;
+      // SPG 2: groups start at ks 0 and 2; SPG 4: at ks 0; SPG 8: at ks 0 of every other chunk
+      const bool starts = SPG == 2 ? (ks % 2 == 0) : (SPG == 4 ? ks == 0 : (ks == 0 && (c & 1) == 0));
+      const bool ends = SPG == 2 ? (ks % 2 == 1) : (SPG == 4 ? ks == 3 : (ks == 3 && (c & 1) == 1));
+      if (starts) {
+        if (visits > 0) {          // the epilogue must have read this slot's previous sums
+          ok = mbar_wait_fast(my_empty, (visits - 1u) & 1u, x.s_abort);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        ++visits;
+      }
+#pragma unroll
+      for (int pc = 0; pc < kPieces; ++pc)
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          const uint32_t d = d_base + (uint32_t)q * x.mp, a = a_base + (uint32_t)(q * 32 + ks * 8);
+          const uint32_t b = b_lo + (uint32_t)(ks * 2) + (uint32_t)pc * x.piece16;
+          if (pc > 0) mma_bf16_ts<1>(d, a, b, x.idesc);
+          else if (SPG == 8 && ks == 0) mma_bf16_ts<2>(d, a, b, x.idesc, (uint32_t)(c & 1));
+          else if ((SPG == 2 && ks % 2 == 0) || (SPG == 4 && ks == 0)) mma_bf16_ts<0>(d, a, b, x.idesc);
+          else mma_bf16_ts<1>(d, a, b, x.idesc);
+        }
+      if (ends) mma_commit(my_full);
+    }
+    mma_commit(&x.empty[s]);   // the stage is free once every issuer's MMAs have read it
+  }
+  (void)slot_shift;
+  // nothing may still be running on the tensor core when the tensor memory is given back
+  mma_commit(&x.drained[me]);
+  mbar_wait_fast(&x.drained[me], 0u, x.s_abort);
+}
+
+// MP: activation rows padded to a multiple of 16; NW: 1 matrix or a gate/up pair.  Template parameters keep
+// each variant's loops exactly as long as they need to be (the roles' loop bodies must stay in the
+// instruction cache) and its accumulator registers as few.
+template <int MP, int NW>
 __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full_a[kStages], full_b[kStages], empty[kStages], acc_full[4], acc_empty[4], drained;
+  __shared__ __align__(8) uint64_t full_a[kStages], full_b[kStages], empty[kStages], acc_full[4], acc_empty[4], drained[4];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int NW = p.pair ? 2 : 1;
-  const int b_bytes = kPieces * p.mp * 128;             // the images of the activations per stage
+  const int b_bytes = kPieces * MP * 128;             // the images of the activations per stage
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int n0 = (int)blockIdx.x * kTileN;
   const int k0 = (int)blockIdx.y * p.kper;
@@ -172,23 +283,23 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
   const int ngroups = p.kper / p.g;
   const int slots = p.slots;
   // tensor memory columns: [stage][matrix] 32 columns of codes (64 bf16), then [slot][matrix] mp columns of sums
-  const uint32_t a_cols = 32u * NW, acc_base = kStages * a_cols, acc_cols = (uint32_t)(p.mp * NW);
+  const uint32_t a_cols = 32u * NW, acc_base = kStages * a_cols, acc_cols = (uint32_t)(MP * NW);
 
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_a[s], 4);    // one lane of each unpacking warp
       mbar_init(&full_b[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], p.g == 32 ? 2u : 1u);   // the issuers of the stage's groups commit to it
     }
     for (int s = 0; s < 4; ++s) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 8);  // one lane of each epilogue warp
     }
-    mbar_init(&drained, 1);
+    for (int s = 0; s < 4; ++s) mbar_init(&drained[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 13) {
+  if (warp == 12) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -197,57 +308,24 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
-  if (warp == 12) {
-    // ---------------- activation images: one bulk copy per stage ----------------
-    if (lane == 0) {
-      for (int c = 0; c < nchunks; ++c) {
-        const int s = c % kStages;
-        if (c >= kStages && !mbar_wait(&empty[s], (uint32_t)(c / kStages - 1) & 1u, &s_abort)) break;
-        mbar_expect_tx(&full_b[s], (uint32_t)b_bytes);
-        bulk_g2s(smem + (size_t)s * b_bytes, p.xq + (size_t)(k0 / kKC + c) * b_bytes, (uint32_t)b_bytes, &full_b[s]);
-      }
-    }
-  } else if (warp == 13) {
+  if (warp >= 12) {
     // ---------------- MMA issue ----------------
-    if (lane == 0) {
+    if (lane == 0 && warp - 12 < slots) {
+      IssueCtx x;
+      x.full_a = full_a; x.full_b = full_b; x.empty = empty; x.acc_full = acc_full; x.acc_empty = acc_empty; x.drained = drained;
+      x.s_abort = &s_abort;
+      x.tmem = tmem; x.a_cols = a_cols; x.acc_base = acc_base; x.acc_cols = acc_cols;
+      x.b_lo0 = (smem_u32(smem) >> 4) | (1u << 16);
+      x.stage16 = (uint32_t)b_bytes >> 4;
+      x.piece16 = (uint32_t)(MP * 128) >> 4;
+      x.mp = (uint32_t)MP;
       // instruction descriptor: fp32 accumulator, bf16 x bf16, B K-major, N = mp, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mp >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
-      const int steps_per_group = p.g / 16;
-      bool ok = true;
-      int gi = 0, in_group = 0;
-      for (int c = 0; c < nchunks && ok; ++c) {
-        const int s = c % kStages;
-        const uint32_t par = (uint32_t)(c / kStages) & 1u;
-        ok = mbar_wait(&full_a[s], par, &s_abort) && mbar_wait(&full_b[s], par, &s_abort);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t b0 = smem_u32(smem + (size_t)s * b_bytes);
-#pragma unroll 1
-        for (int ks = 0; ks < kKC / 16; ++ks) {   // 16 bf16 = 32 bytes of a row = 8 columns of tensor memory per MMA
-          const int slot = gi % slots;
-          if (in_group == 0 && gi >= slots) {     // the epilogue must have read this slot's previous sums
-            ok = mbar_wait(&acc_empty[slot], (uint32_t)(gi / slots - 1) & 1u, &s_abort);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          for (int q = 0; q < NW; ++q) {
-            const uint32_t d = tmem + acc_base + (uint32_t)slot * acc_cols + (uint32_t)(q * p.mp);
-            const uint32_t a = tmem + (uint32_t)s * a_cols + (uint32_t)q * 32u + (uint32_t)ks * 8u;
-#pragma unroll
-            for (int pc = 0; pc < kPieces; ++pc)
-              mma_bf16_ts(d, a, smem_desc(b0 + pc * p.mp * 128 + ks * 32), idesc, (in_group > 0 || pc > 0) ? 1u : 0u);
-          }
-          if (++in_group == steps_per_group) {
-            mma_commit(&acc_full[slot]);
-            in_group = 0;
-            ++gi;
-          }
-        }
-        mma_commit(&empty[s]);   // the stage is free once these MMAs have read it
-      }
-      // nothing may still be running on the tensor core when the tensor memory is given back
-      mma_commit(&drained);
-      mbar_wait(&drained, 0u, &s_abort);
+      x.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MP >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+      x.nchunks = nchunks; x.slots = slots; x.nw = NW;
+      const uint32_t me = (uint32_t)(warp - 12);
+      if (p.g == 32) issue_loop<2, NW>(x, me);
+      else if (p.g == 64) issue_loop<4, NW>(x, me);
+      else issue_loop<8, NW>(x, me);
     }
   } else if (warp < 4) {
     // ---------------- unpacking: thread = weight row ----------------
@@ -280,6 +358,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
       asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");   // chunk c has landed
       const int s = c % kStages;
       if (c >= kStages && !mbar_wait_warp(&empty[s], (uint32_t)(c / kStages - 1) & 1u, &s_abort)) break;
+      if (tid == 0) {   // the stage's activation images: one bulk copy
+        mbar_expect_tx(&full_b[s], (uint32_t)b_bytes);
+        bulk_g2s(smem + (size_t)s * b_bytes, p.xq + (size_t)(k0 / kKC + c) * b_bytes, (uint32_t)b_bytes, &full_b[s]);
+      }
       tc_fence_after();
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
@@ -313,16 +395,16 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
     const int j = n0 + row;
     const bool live = j < p.n;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const int half = p.mp >> 1;                 // 8, 16, 24 or 32 activation rows per team
-    const int units = half >> 3;                // in blocks of 8 columns
+    constexpr int half = MP >> 1;               // 8, 16, 24 or 32 activation rows per team
+    constexpr int units = half >> 3;            // in blocks of 8 columns
     const int cb = team * half;
     const float* s0 = p.scales[0] + (size_t)(live ? j : 0) * p.ng + k0 / p.g;
     const float* s1 = (NW == 2 ? p.scales[1] : p.scales[0]) + (size_t)(live ? j : 0) * p.ng + k0 / p.g;
-    float acc[2][32];
+    float acc[NW][half];
 #pragma unroll
-    for (int q = 0; q < 2; ++q)
+    for (int q = 0; q < NW; ++q)
 #pragma unroll
-      for (int i = 0; i < 32; ++i) acc[q][i] = 0.f;
+      for (int i = 0; i < half; ++i) acc[q][i] = 0.f;
     float sc0 = live ? __ldg(s0) : 0.f, sc1 = (live && NW == 2) ? __ldg(s1) : 0.f;
     bool ok = true;
     for (int gi = 0; gi < ngroups; ++gi) {
@@ -336,26 +418,42 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
       if (!ok) break;
       tc_fence_after();
       const uint32_t d = lane_base + acc_base + (uint32_t)slot * acc_cols + (uint32_t)cb;
+      if constexpr (units * NW <= 4) {
+        // every load of the group is in flight at once (32 registers at most)
+        uint32_t r[NW][units][8];
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        if (q < NW) {
-          uint32_t r[4][8];
+        for (int q = 0; q < NW; ++q)
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (u < units) tmem_ld8(d + (uint32_t)(q * p.mp + u * 8), r[u]);
+          for (int u = 0; u < units; ++u) tmem_ld8(d + (uint32_t)(q * MP + u * 8), r[q][u]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[slot]);   // the slot's sums are in registers: hand it back before the arithmetic
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          const float cq = q ? c1 : c0;
+#pragma unroll
+          for (int u = 0; u < units; ++u)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[q][u * 8 + i] = fmaf(cq, __uint_as_float(r[q][u][i]), acc[q][u * 8 + i]);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          uint32_t r[units][8];
+#pragma unroll
+          for (int u = 0; u < units; ++u) tmem_ld8(d + (uint32_t)(q * MP + u * 8), r[u]);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (q == NW - 1) {   // the slot's sums are in registers: hand it back before the arithmetic
+          if (q == NW - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[slot]);
           }
           const float cq = q ? c1 : c0;
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (u < units) {
+          for (int u = 0; u < units; ++u)
 #pragma unroll
-              for (int i = 0; i < 8; ++i) acc[q][u * 8 + i] = fmaf(cq, __uint_as_float(r[u][i]), acc[q][u * 8 + i]);
-            }
+            for (int i = 0; i < 8; ++i) acc[q][u * 8 + i] = fmaf(cq, __uint_as_float(r[u][i]), acc[q][u * 8 + i]);
         }
       }
     }
@@ -363,12 +461,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
       const float b0 = (p.bias[0] && blockIdx.y == 0) ? __ldg(p.bias[0] + j) : 0.f;
       const float b1 = (NW == 2 && p.bias[1]) ? __ldg(p.bias[1] + j) : 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < half; ++i) {
         const int mrow = cb + i;
-        if (i < half && mrow < p.m) {
+        if (mrow < p.m) {
           float v;
           if (NW == 2) {
-            const float gg = acc[0][i] + b0, uu = acc[1][i] + b1;
+            const float gg = acc[0][i] + b0, uu = acc[NW - 1][i] + b1;
             v = (gg / (1.0f + expf(-gg))) * uu;   // src/llm/decoder.rs:1319-1322
           } else {
             v = acc[0][i] + b0;
@@ -383,7 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 13) {
+  if (warp == 12) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
@@ -470,7 +568,7 @@ size_t w4_tc5_scratch_bytes(int m, int64_t k) {
 }
 
 bool w4_tc5_supported(const GemvArgs& a) {
-  if (!g_tc5_enabled || a.m < 16) return false;
+  if (!g_tc5_enabled || a.m < kMinRows) return false;
   if (a.k % 128 != 0 || a.n < 1 || (a.g != 32 && a.g != 64 && a.g != 128)) return false;
   if (a.x_ss8 || a.out_scaled || a.out_ss8 || a.x_normed_out) return false;
   if ((reinterpret_cast<uintptr_t>(a.w) & 15) || (a.w2 && (reinterpret_cast<uintptr_t>(a.w2) & 15))) return false;
@@ -502,20 +600,25 @@ tb_status launch_w4_tc5(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     p.kper = (int)(a.k / ksplit);
     const int nw = pair ? 2 : 1;
     const int slots = (kTmemCols - kStages * 32 * nw) / (mp * nw);
-    p.slots = slots > 4 ? 4 : slots;
+    p.slots = slots >= 4 ? 4 : 2;   // a power of two (the issuing thread masks and shifts)
     const size_t smem = (size_t)kStages * kPieces * mp * 128 + (size_t)kAhead * nw * kTileN * 32 + 1024;
-    static thread_local size_t configured[64] = {0};
-    int dev = 0;
-    TB_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 64 || configured[dev] < smem) {
-      TB_CUDA_TRY(cudaFuncSetAttribute(w4_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      if (dev < 64) configured[dev] = smem;
+    void (*kern)(const Tc5Params) = nullptr;
+    switch (mp * 2 + (pair ? 1 : 0)) {
+      case 32: kern = w4_tc5_kernel<16, 1>; break;
+      case 33: kern = w4_tc5_kernel<16, 2>; break;
+      case 64: kern = w4_tc5_kernel<32, 1>; break;
+      case 65: kern = w4_tc5_kernel<32, 2>; break;
+      case 96: kern = w4_tc5_kernel<48, 1>; break;
+      case 97: kern = w4_tc5_kernel<48, 2>; break;
+      case 128: kern = w4_tc5_kernel<64, 1>; break;
+      default: kern = w4_tc5_kernel<64, 2>; break;
     }
+    TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     tc5_prep_kernel<<<dim3((unsigned)mp, (unsigned)((a.k + 2047) / 2048)), 256, 0, stream>>>(
         a.x + (size_t)m0 * a.k, a.norm_w, a.eps, static_cast<unsigned char*>(scratch), mc, mp, (int)a.k);
     TB_CUDA_TRY(cudaGetLastError());
     if (ksplit > 1) TB_CUDA_TRY(cudaMemsetAsync(p.out, 0, sizeof(float) * (size_t)mc * a.n, stream));
-    w4_tc5_kernel<<<dim3((unsigned)tiles, (unsigned)ksplit), kThreads, smem, stream>>>(p);
+    kern<<<dim3((unsigned)tiles, (unsigned)ksplit), kThreads, smem, stream>>>(p);
     TB_CUDA_TRY(cudaGetLastError());
   }
   return TB_OK;
