@@ -584,6 +584,8 @@ tb_status launch_w4_tc5(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     const int mp = (mc + 15) & ~15;
     Tc5Params p;
     p.w[0] = a.w; p.w[1] = a.w2; p.scales[0] = a.scales; p.scales[1] = a.scales2; p.bias[0] = a.bias; p.bias[1] = a.bias2;
+    // residual in place (out == resid) with K split: the partial sums are added onto the residual where it lies
+    const bool in_place = a.resid != nullptr && a.resid == a.out;
     p.resid = a.resid ? a.resid + (size_t)m0 * a.n : nullptr;
     p.out = a.out + (size_t)m0 * a.n;
     p.xq = static_cast<const unsigned char*>(scratch);
@@ -617,7 +619,8 @@ tb_status launch_w4_tc5(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     tc5_prep_kernel<<<dim3((unsigned)mp, (unsigned)((a.k + 2047) / 2048)), 256, 0, stream>>>(
         a.x + (size_t)m0 * a.k, a.norm_w, a.eps, static_cast<unsigned char*>(scratch), mc, mp, (int)a.k);
     TB_CUDA_TRY(cudaGetLastError());
-    if (ksplit > 1) TB_CUDA_TRY(cudaMemsetAsync(p.out, 0, sizeof(float) * (size_t)mc * a.n, stream));
+    if (ksplit > 1 && in_place) p.resid = nullptr;
+    else if (ksplit > 1) TB_CUDA_TRY(cudaMemsetAsync(p.out, 0, sizeof(float) * (size_t)mc * a.n, stream));
     kern<<<dim3((unsigned)tiles, (unsigned)ksplit), kThreads, smem, stream>>>(p);
     TB_CUDA_TRY(cudaGetLastError());
   }
