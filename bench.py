@@ -583,6 +583,18 @@ def run_gpu(args):
         return
 
     # ---- outside the headline region (every rank takes part where the model is sharded) ----
+    # the other form of the batch-1 step (persistent step kernel <-> chain of single kernels), same workload
+    other_form = None
+    if B == 1 and tp == 1 and not args.quick and not args.no_graph:
+        import argparse as _ap
+
+        alt_args = _ap.Namespace(**dict(vars(args), chain=not args.chain))
+        alt = make_decoder(tb, c, model, max_seq, B, tp, rank, alt_args)
+        prefill_kv(torch, alt, c, device, CONTEXT, B, tp, rank)
+        alt_ms = float(np.median(timed_steps(torch, dist, tb, alt, device, tp, B, CONTEXT, K, W, 3))) / K
+        other_form = {"form": "persistent step kernel" if args.chain else "chain of single kernels (--chain)",
+                      "tokens_per_s": B * 1e3 / alt_ms, "ms_per_step": alt_ms, "launches_per_step": alt.launches_per_step()}
+        alt.close()
     # correctness of the sharded path at this N
     tp_check = tp_correctness_check(torch, dist, tb, c, device, tp, rank, args) if tp > 1 else None
     # the other batch sizes of the workload configuration: tokens/s at batch 8 and 32
@@ -633,6 +645,7 @@ def run_gpu(args):
             "weight_bytes_per_step_per_gpu": wb, "kv_bytes_per_step_per_gpu": kvb * B,
             "weights_only_frac": wb / step_s / 1e9 / peak, "weights_plus_kv_frac": (wb + kvb * B) / step_s / 1e9 / peak,
             "peak_kind": f"of {peak_kind}", "launches_per_step": launches_per_step},
+        "step_form": "chain of single kernels" if args.chain else "persistent step kernel", "other_step_form": other_form,
         "gemv_config1": {"shape": "4096x4096 group 32, M=1", "algorithmic_bytes": c1_alg, "us_per_launch": c1_sec * 1e6,
                          "achieved_gbs": c1_alg / c1_sec / 1e9, "frac_of_measured": c1_alg / c1_sec / 1e9 / peak,
                          "frac_of_nominal_8TBs": c1_alg / c1_sec / 1e9 / NOMINAL_HBM_GBS,

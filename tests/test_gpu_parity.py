@@ -641,6 +641,40 @@ def test_decoder_speculative_accept_matches_rows_on_verified_logits(torch, tb, o
         a.speculative_accept(3, [1, 2], np.zeros(5, np.float32))
 
 
+@pytest.mark.parametrize("max_batch,k", [(8, 5), (4, 9), (32, 20)])
+def test_verify_tokens_is_one_batched_step_and_matches_sequential_steps(torch, tb, oracle, max_batch, k):
+    """verify_tokens (src/llm/decoder.rs:565-581) with a decoder built for several rows: the k positions of
+    the ONE sequence go through the batched kernels (k rows per product; the attention rows share the
+    sequence's cache, causal inside the block) in slabs of max_batch positions.  The rows must equal the
+    sequential single-position steps of a second decoder and of the oracle, the cache must hold the same
+    rows afterwards, and decoding continues from it."""
+    cfg = dict(vocab_size=211, hidden_size=128, intermediate_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+               head_dim=32, group_size=32, max_seq_len=64, rms_norm_eps=1e-6, rope_theta=1e6)
+    embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 77, oracle.quantize_int4_grouped, std=0.3)
+    a = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, max_batch=max_batch)
+    b = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    prompt = [3, 50, 7, 120, 9, 200, 1]
+    for d in (a, b, ref):
+        d.prefill_tokens(prompt, 0)
+    rng = np.random.default_rng(k)
+    toks = [int(t) for t in rng.integers(0, cfg["vocab_size"], k)]
+    launches_before = a.launches_per_step()
+    rows = a.verify_tokens(len(prompt), toks)
+    assert rows.shape == (k, cfg["vocab_size"])
+    seq = np.stack([b.step(t, len(prompt) + i) for i, t in enumerate(toks)])
+    want = np.stack([ref.step(t, len(prompt) + i) for i, t in enumerate(toks)])
+    assert max_rel_err(rows, seq) < 1e-3
+    assert max_rel_err(rows, want) < LOGIT_TOL
+    assert a.kv_len() == len(prompt) + k
+    assert max_rel_err(a.get_logits().reshape(-1)[:cfg["vocab_size"]], want[-1]) < LOGIT_TOL   # logits of the last position
+    # the cache holds every verified row: the next single step agrees with the sequential decoder
+    nxt = len(prompt) + k
+    assert max_rel_err(a.step(5, nxt), ref.step(5, nxt)) < LOGIT_TOL
+    assert tb.lib().tb_device_fault_flag() == 0
+    del launches_before
+
+
 def test_v2_layout_linear_matches_oracle_v2_kernel(torch, tb, oracle):
     # python/torchburn/quantization.py:121-190 and tests/test_parity.py:156-206: the v2 blocks carry the
     # same codes as v1 and binary16 scales; the linear on them equals the scalar v2 kernel of the

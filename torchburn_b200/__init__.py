@@ -9,6 +9,7 @@ package without the built library raises.
 """
 from ._lib import TorchBurnB200Error, abi_version, device_report, lib, last_error
 from .decoder import B200QwenDecoder, create_b200_qwen_decoder
+from .speculative import BatchedDecoder, SpeculativeDecoder
 from .quantization import (
     QuantizedLinear,
     dequantize_int4_grouped_v2,
@@ -24,7 +25,7 @@ from .quantization import (
 
 __all__ = [
     "TorchBurnB200Error", "abi_version", "device_report", "lib", "last_error",
-    "B200QwenDecoder", "create_b200_qwen_decoder", "QuantizedLinear", "fused_attention_step",
+    "B200QwenDecoder", "create_b200_qwen_decoder", "SpeculativeDecoder", "BatchedDecoder", "QuantizedLinear", "fused_attention_step",
     "fused_swiglu_mlp", "fused_swiglu_mlp_batched", "fused_transformer_layer_step", "quantize_weight_int4_grouped",
     "w4a32_grouped_linear", "quantize_weight_int4_grouped_v2", "dequantize_int4_grouped_v2", "w4a32_grouped_linear_v2",
 ]

@@ -62,6 +62,7 @@ struct AttnParams {
   int region_floats;  // floats of the ring region (also holds the combine / merge buffers)
   int64_t max_seq_len;
   int per_call_tables;
+  int shared_cache;   // every row of the batch is a position of ONE sequence: sequence 0's cache, rows appended beforehand
   float scale;
   unsigned long long* tl;  // timestamps of this launch or null
 };
@@ -358,8 +359,9 @@ __global__ void TB_ATTN_BOUNDS attn_decode_kernel(const AttnParams p) {
   const bool has_new = active && off >= t0 && off < t0 + rows;
   const int ring_rows = rows - (has_new ? 1 : 0);
   const int nchunks = active ? max(1, (ring_rows + kChunkRows - 1) / kChunkRows) : 0;
-  float* kc = p.k_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
-  float* vc = p.v_cache + ((int64_t)b * p.num_kv_heads + kvh) * p.max_seq_len * D;
+  const int cache_seq = p.shared_cache ? 0 : b;
+  float* kc = p.k_cache + ((int64_t)cache_seq * p.num_kv_heads + kvh) * p.max_seq_len * D;
+  float* vc = p.v_cache + ((int64_t)cache_seq * p.num_kv_heads + kvh) * p.max_seq_len * D;
   const int stage_floats = kStageRows * D;
 
   if (warp == kCW) {
@@ -432,8 +434,10 @@ __global__ void TB_ATTN_BOUNDS attn_decode_kernel(const AttnParams p) {
       for (int e = tid; e < D; e += kCT) {
         const float kr = rope_elem(kx, cs, sn, e, D / 2);
         const float vr = vx[e];
-        kc[(int64_t)off * D + e] = kr;
-        vc[(int64_t)off * D + e] = vr;
+        if (!p.shared_cache) {   // shared cache: rope_append_rows_kernel wrote every row before this launch
+          kc[(int64_t)off * D + e] = kr;
+          vc[(int64_t)off * D + e] = vr;
+        }
         kv_new[e] = kr;
         kv_new[D + e] = vr;
         if (p.qkv_rot_out) {
@@ -808,6 +812,36 @@ static tb_status launch_attn_d(const AttnParams& p, const cudaLaunchConfig_t& cf
   }
 }
 
+// Several positions of ONE sequence in a batch (speculative verify): row r of qkv is position offsets[r]
+// of sequence 0.  Its k (rotated) and v are appended to sequence 0's cache here, for all rows, BEFORE the
+// attention launch, which then only reads the cache (row r attends to [0, offsets[r]], so it also reads
+// the rows of its predecessors in the batch).  grid (rows, kv heads), head_dim threads.
+__global__ void rope_append_rows_kernel(const float* __restrict__ qkv, float* __restrict__ k_cache, float* __restrict__ v_cache,
+                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                        const int32_t* __restrict__ offsets, int num_heads, int num_kv_heads, int D,
+                                        int64_t max_seq_len) {
+  const int b = blockIdx.x, kvh = blockIdx.y, e = threadIdx.x;
+  const int off = offsets[b];
+  if (off < 0 || (int64_t)off >= max_seq_len || off >= kSeqCap) return;   // the attention kernel writes zeros for such a row
+  const int64_t qkv_dim = (int64_t)(num_heads + 2 * num_kv_heads) * D;
+  const float* kx = qkv + (int64_t)b * qkv_dim + (int64_t)num_heads * D + (int64_t)kvh * D;
+  const float* vx = kx + (int64_t)num_kv_heads * D;
+  const float* cs = cos_t + (int64_t)off * D;
+  const float* sn = sin_t + (int64_t)off * D;
+  const int64_t at = ((int64_t)kvh * max_seq_len + off) * D + e;
+  k_cache[at] = rope_elem(kx, cs, sn, e, D / 2);
+  v_cache[at] = vx[e];
+}
+
+tb_status launch_rope_append_rows(const AttnArgs& a, cudaStream_t stream) {
+  if (!a.qkv || !a.k_cache || !a.v_cache || !a.cos_t || !a.sin_t || !a.offsets || a.per_call_tables)
+    return fail(TB_ERR_ARG, "rope_append_rows: null operand or per-call tables");
+  rope_append_rows_kernel<<<dim3((unsigned)a.batch, (unsigned)a.num_kv_heads), a.head_dim, 0, stream>>>(
+      a.qkv, a.k_cache, a.v_cache, a.cos_t, a.sin_t, a.offsets, a.num_heads, a.num_kv_heads, a.head_dim, a.max_seq_len);
+  TB_CUDA_TRY(cudaGetLastError());
+  return TB_OK;
+}
+
 tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   if (!a.qkv || !a.k_cache || !a.v_cache || !a.cos_t || !a.sin_t || !a.offsets || !a.out || !a.scratch)
     return fail(TB_ERR_ARG, "attention: null operand");
@@ -851,6 +885,7 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.region_floats = (int)region;
   p.max_seq_len = a.max_seq_len;
   p.per_call_tables = a.per_call_tables ? 1 : 0;
+  p.shared_cache = a.shared_cache ? 1 : 0;
   p.scale = 1.0f / sqrtf((float)a.head_dim);
   p.tl = timeline_next_block();
 

@@ -93,6 +93,8 @@ struct tb_decoder {
   cudaStream_t stream = nullptr;
   cudaGraphExec_t graphs[kMaxBatch + 1] = {};
   cudaGraphExec_t graphs_greedy[kMaxBatch + 1] = {};
+  cudaGraphExec_t graphs_verify[kMaxBatch + 1] = {};   // the rows of the batch are positions of sequence 0
+  bool verify_shared = false;                           // set around a multi-position verify step
   bool use_graph = true;
   bool pdl = true;
   // Kernels launched with programmatic dependent launch (bit 0 qkv, 1 attention, 2 o_proj,
@@ -187,6 +189,14 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.scratch = d->attn_scratch; a.q_rot_out = dbg ? d->dbg_qkv : nullptr;
       a.batch = b; a.num_heads = d->nh_l; a.num_kv_heads = d->nkv_l; a.head_dim = d->hd;
       a.max_seq_len = d->S; a.pdl = pdl && !debug && (pm & 2);
+      if (d->verify_shared && b > 1) {
+        // several positions of sequence 0: every row's k and v go into the cache first; the attention kernel
+        // then only reads it (and must not start reading before that kernel has finished: no early launch)
+        a.shared_cache = true;
+        a.pdl = false;
+        TB_TRY(launch_rope_append_rows(a, st));
+        ++launches;
+      }
       // The kernel strides sequences by [Hkv, S, d]; with batch > 1 that is the layout of
       // one layer's block [B][Hkv][S][d].
       TB_TRY(launch_attention_decode(a, st));
@@ -285,7 +295,7 @@ tb_status build_graph(tb_decoder* d, int b, bool greedy, cudaGraphExec_t* out) {
 // Runs one step for b sequences whose tokens/offsets are already in d_tokens/d_offsets.
 tb_status run_step(tb_decoder* d, int b, bool greedy) {
   if (d->use_graph) {
-    cudaGraphExec_t* slot = greedy ? &d->graphs_greedy[b] : &d->graphs[b];
+    cudaGraphExec_t* slot = d->verify_shared ? &d->graphs_verify[b] : (greedy ? &d->graphs_greedy[b] : &d->graphs[b]);
     if (!*slot) {
       tb_status s = build_graph(d, b, greedy, slot);
       if (s != TB_OK) {
@@ -624,6 +634,7 @@ void tb_decoder_destroy(tb_decoder* d) {
   for (int i = 0; i <= kMaxBatch; ++i) {
     if (d->graphs[i]) cudaGraphExecDestroy(d->graphs[i]);
     if (d->graphs_greedy[i]) cudaGraphExecDestroy(d->graphs_greedy[i]);
+    if (d->graphs_verify[i]) cudaGraphExecDestroy(d->graphs_verify[i]);
   }
   if (d->tpst) tp_destroy(d->tpst);
   cudaFree(d->embed); cudaFree(d->final_norm_w); cudaFree(d->lm_w); cudaFree(d->lm_s);
@@ -714,10 +725,24 @@ tb_status tb_decoder_verify_tokens(tb_decoder* d, int64_t start_offset, const in
   if (n == 0) return TB_OK;
   if (!tokens || !logits_host || n < 0 || start_offset < 0) return fail(TB_ERR_ARG, "tb_decoder_verify_tokens: bad arguments");
   if (start_offset + n > d->S) return fail(TB_ERR_ARG, "verify exceeds max_seq_len");
-  for (int64_t i = 0; i < n; ++i) {
-    const int64_t off = start_offset + i;
-    TB_TRY(feed_and_step(d, tokens + i, &off, 1));
-    DEC_CUDA(d, cudaMemcpyAsync(logits_host + i * d->V, d->logits, sizeof(float) * d->V, cudaMemcpyDeviceToHost, d->stream));
+  // Up to max_batch positions per step: the rows of the batch are consecutive positions of sequence 0, so the
+  // projections run as one batched product per matrix and the attention rows share sequence 0's cache
+  // (causal inside the block: row r attends to [0, start + r]).  A decoder built for one row steps one
+  // position at a time, like src/llm/decoder.rs:575-579.
+  for (int64_t i = 0; i < n;) {
+    const int m = (int)(n - i < d->B ? n - i : d->B);
+    int64_t offs[kMaxBatch];
+    for (int r = 0; r < m; ++r) offs[r] = start_offset + i + r;
+    d->verify_shared = m > 1;
+    const tb_status s = feed_and_step(d, tokens + i, offs, m);
+    d->verify_shared = false;
+    TB_TRY(s);
+    DEC_CUDA(d, cudaMemcpyAsync(logits_host + i * d->V, d->logits, sizeof(float) * (size_t)m * d->V, cudaMemcpyDeviceToHost, d->stream));
+    if (m > 1) {  // the decoder's own logits are those of the last position, as after sequential steps
+      DEC_CUDA(d, cudaMemcpyAsync(d->logits, d->logits + (size_t)(m - 1) * d->V, sizeof(float) * d->V, cudaMemcpyDeviceToDevice, d->stream));
+      d->last_batch = 1;
+    }
+    i += m;
   }
   DEC_CUDA(d, cudaStreamSynchronize(d->stream));
   return TB_OK;

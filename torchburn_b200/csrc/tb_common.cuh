@@ -131,6 +131,7 @@ struct AttnArgs {
   int batch = 1, num_heads = 0, num_kv_heads = 0, head_dim = 0;
   int64_t max_seq_len = 0;
   bool per_call_tables = false; // cos/sin hold one row per sequence instead of a table
+  bool shared_cache = false;    // the rows are positions of ONE sequence (sequence 0's cache); launch_rope_append_rows goes first
   bool pdl = false;
 };
 size_t attention_scratch_bytes(int batch, int num_heads, int num_kv_heads, int head_dim,
@@ -146,6 +147,7 @@ void set_attention_tuning(int ctas_per_sm, int stages);
 // 1 once a bounded wait of the attention kernel ran out (results of that launch are invalid).
 int attention_fault_flag();
 tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream);
+tb_status launch_rope_append_rows(const AttnArgs& a, cudaStream_t stream);
 // The library's built-in scratch block for tb_attention_decode_static (attention.cu).
 size_t static_attention_scratch_capacity();
 tb_status static_attention_scratch(void** ptr);
