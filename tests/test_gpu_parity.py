@@ -668,8 +668,16 @@ def test_verify_tokens_is_one_batched_step_and_matches_sequential_steps(torch, t
     assert max_rel_err(rows, want) < LOGIT_TOL
     assert a.kv_len() == len(prompt) + k
     assert max_rel_err(a.get_logits().reshape(-1)[:cfg["vocab_size"]], want[-1]) < LOGIT_TOL   # logits of the last position
-    # the cache holds every verified row: the next single step agrees with the sequential decoder
+    # the cache holds every verified row ...
     nxt = len(prompt) + k
+    for l in range(cfg["num_layers"]):
+        gk, gv = a.read_kv_cache(l)
+        ek, ev = ref.kv_cache(l)
+        for pos in range(nxt):
+            assert max_rel_err(gk[:, pos], ek[:, pos]) < STAGE_TOL, ("k", l, pos)
+            assert max_rel_err(gv[:, pos], ev[:, pos]) < STAGE_TOL, ("v", l, pos)
+        assert not gk[:, nxt:].any() and not gv[:, nxt:].any()
+    # ... so the next single step agrees with the sequential decoder
     assert max_rel_err(a.step(5, nxt), ref.step(5, nxt)) < LOGIT_TOL
     assert tb.lib().tb_device_fault_flag() == 0
     del launches_before

@@ -133,6 +133,27 @@ def test_llama8b_width_depth2_batch1_context_4090(torch, tb, oracle, fused):
     assert tb.lib().tb_device_fault_flag() == 0
 
 
+@pytest.mark.parametrize("ranks", [4, 8])
+def test_llama8b_one_rank_of_tp_shapes_in_the_step_kernel(torch, tb, oracle, ranks):
+    """The phase shapes one rank of a tensor-parallel Llama-3-8B decoder runs in the persistent step
+    kernel, on ONE GPU (the exchange aside, which the multi-GPU tests cover): heads, kv heads, the
+    intermediate width and the vocabulary divided by the number of ranks - 8 ranks: one kv head
+    (64 attention splits), o_proj K = 512 (one warp covers K), down K = 1792, 16032 logits.  A model of
+    exactly those widths against the oracle at a context of 4090."""
+    cfg = dict(LLAMA8B_L2, num_heads=32 // ranks, num_kv_heads=8 // ranks, intermediate_size=14336 // ranks,
+               vocab_size=128256 // ranks if ranks == 8 else 8192)
+    embed, layers, fnorm, lm_w, lm_s = _llama_width_model(torch, tb, cfg, 70 + ranks)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    dec = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, fused_step=True)
+    ctx = 4090
+    _prefill_both(dec, [ref], cfg, ctx, 9, 1)
+    toks = np.random.default_rng(ranks).integers(0, cfg["vocab_size"], 4)
+    for i, t in enumerate(toks):
+        assert max_rel_err(dec.step(int(t), ctx + i), ref.step(int(t), ctx + i)) < LOGIT_TOL, i
+    assert dec.launches_per_step() == 2   # the embedding kernel + the persistent step kernel
+    assert tb.lib().tb_device_fault_flag() == 0
+
+
 @pytest.mark.parametrize("batch,steps", [(8, 2), (32, 1)])
 def test_llama8b_width_depth2_batched_steps(torch, tb, oracle, batch, steps):
     """The same model at batch 8 and 32 (step_batch: tensor-core rows kernels at true width, the

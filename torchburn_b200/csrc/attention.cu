@@ -37,6 +37,7 @@ constexpr int kRG = kWR / 4;           // groups of 4 rows per warp and stage (2
 constexpr int kMaxGq = 8;              // q heads per kv head
 constexpr int kMaxStages = 8;
 constexpr int kChunkRows = 512;        // positions whose scores are held in shared memory at a time
+constexpr size_t kCounterBytes = 16384;  // 4096 tickets: (sequence, kv head) pairs of a launch
 constexpr int kSeqCap = 32768;         // src/llm/decoder.rs:1180
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: a wait that long means a lost copy
 
@@ -773,24 +774,24 @@ int attention_fault_flag() {
   return v;
 }
 
-// Scratch = partials + ticket counters.  The counters must be zero before the
-// first launch; every launch leaves them zero again.
+// Scratch = ticket counters + partials.  The counters must be zero before the first launch; every
+// launch leaves them zero again.  They sit at the START of the block, in a region of fixed size: their
+// place must not depend on the batch of a launch, or the partials of a launch with many rows would land
+// on the counters that a later launch with fewer rows expects to be zero.
 size_t attention_scratch_bytes(int batch, int num_heads, int num_kv_heads, int head_dim,
                                int64_t max_seq_len) {
   // sized for the largest number of CTAs per (sequence, kv head) any setting can ask for
   const int nc = max_splits(max_seq_len);
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
-  return up((size_t)batch * num_heads * nc * head_dim * sizeof(float)) +
-         up((size_t)batch * num_heads * nc * 2 * sizeof(float)) +
-         up(((size_t)batch * num_kv_heads + 1) * sizeof(int));
+  return kCounterBytes + up((size_t)batch * num_heads * nc * head_dim * sizeof(float)) +
+         up((size_t)batch * num_heads * nc * 2 * sizeof(float));
 }
 
 size_t attention_counters_offset(int batch, int num_heads, int num_kv_heads, int head_dim,
                                  int64_t max_seq_len, size_t* counter_bytes) {
-  const size_t total = attention_scratch_bytes(batch, num_heads, num_kv_heads, head_dim, max_seq_len);
-  const size_t cb = (((size_t)batch * num_kv_heads + 1) * sizeof(int) + 255) & ~(size_t)255;
-  if (counter_bytes) *counter_bytes = cb;
-  return total - cb;
+  (void)batch; (void)num_heads; (void)num_kv_heads; (void)head_dim; (void)max_seq_len;
+  if (counter_bytes) *counter_bytes = kCounterBytes;
+  return 0;
 }
 
 template <int D, int GQM>
@@ -869,9 +870,11 @@ tb_status launch_attention_decode(const AttnArgs& a, cudaStream_t stream) {
   p.qkv = a.qkv; p.k_cache = a.k_cache; p.v_cache = a.v_cache;
   p.cos_t = a.cos_t; p.sin_t = a.sin_t; p.offsets = a.offsets; p.out = a.out;
   char* base = static_cast<char*>(a.scratch);
-  p.part_o = reinterpret_cast<float*>(base);
-  p.part_ml = reinterpret_cast<float*>(base + L.part_o);
+  if (((size_t)a.batch * a.num_kv_heads + 1) * sizeof(int) > cbytes)
+    return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: attention: %d x %d (sequence, kv head) pairs exceed the ticket block", a.batch, a.num_kv_heads);
   p.counters = reinterpret_cast<int*>(base + coff);
+  p.part_o = reinterpret_cast<float*>(base + coff + cbytes);
+  p.part_ml = reinterpret_cast<float*>(base + coff + cbytes + L.part_o);
   p.qkv_rot_out = a.q_rot_out;
   p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.gq = gq;
   p.fixed_per = L.fixed_per; p.nc = L.nc; p.stages = L.stages;
