@@ -321,7 +321,7 @@ def make_decoder(tb, c, model, max_seq, batch, tp, rank, args, **kw):
                               c["intermediate_size"], c["num_heads"], c["num_kv_heads"], c["head_dim"], c["group_size"],
                               c["rms_norm_eps"], max_seq, c["rope_theta"], max_batch=batch, tp_size=tp, tp_rank=rank,
                               vocab_size=c["vocab_size"], nccl_only=args.nccl_only, pdl=not args.no_pdl, debug=args.no_graph,
-                              fused_step=not args.chain, **kw)
+                              fused_step=(False if args.chain else (True if args.step_kernel else None)), **kw)
 
 
 def timed_steps(torch, dist, tb, dec, device, tp, batch, ctx, steps, warmup, repeats):
@@ -588,11 +588,12 @@ def run_gpu(args):
     if B == 1 and tp == 1 and not args.quick and not args.no_graph:
         import argparse as _ap
 
-        alt_args = _ap.Namespace(**dict(vars(args), chain=not args.chain))
+        is_step_kernel = dec.launches_per_step() == 2
+        alt_args = _ap.Namespace(**dict(vars(args), chain=is_step_kernel, step_kernel=not is_step_kernel))
         alt = make_decoder(tb, c, model, max_seq, B, tp, rank, alt_args)
         prefill_kv(torch, alt, c, device, CONTEXT, B, tp, rank)
         alt_ms = float(np.median(timed_steps(torch, dist, tb, alt, device, tp, B, CONTEXT, K, W, 3))) / K
-        other_form = {"form": "persistent step kernel" if args.chain else "chain of single kernels (--chain)",
+        other_form = {"form": "chain of single kernels (--chain)" if is_step_kernel else "persistent step kernel (--step-kernel)",
                       "tokens_per_s": B * 1e3 / alt_ms, "ms_per_step": alt_ms, "launches_per_step": alt.launches_per_step()}
         alt.close()
     # correctness of the sharded path at this N
@@ -645,7 +646,7 @@ def run_gpu(args):
             "weight_bytes_per_step_per_gpu": wb, "kv_bytes_per_step_per_gpu": kvb * B,
             "weights_only_frac": wb / step_s / 1e9 / peak, "weights_plus_kv_frac": (wb + kvb * B) / step_s / 1e9 / peak,
             "peak_kind": f"of {peak_kind}", "launches_per_step": launches_per_step},
-        "step_form": "chain of single kernels" if args.chain else "persistent step kernel", "other_step_form": other_form,
+        "step_form": "persistent step kernel" if launches_per_step == 2 else "chain of single kernels", "other_step_form": other_form,
         "gemv_config1": {"shape": "4096x4096 group 32, M=1", "algorithmic_bytes": c1_alg, "us_per_launch": c1_sec * 1e6,
                          "achieved_gbs": c1_alg / c1_sec / 1e9, "frac_of_measured": c1_alg / c1_sec / 1e9 / peak,
                          "frac_of_nominal_8TBs": c1_alg / c1_sec / 1e9 / NOMINAL_HBM_GBS,
@@ -710,7 +711,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between kernels (A/B of programmatic dependent launch)")
     ap.add_argument("--no-graph", action="store_true", help="direct launches instead of CUDA-graph replay")
-    ap.add_argument("--chain", action="store_true", help="batch-1 steps as a chain of single kernels instead of the persistent step kernel")
+    ap.add_argument("--chain", action="store_true", help="batch-1 steps as a chain of single kernels (the default on one GPU)")
+    ap.add_argument("--step-kernel", dest="step_kernel", action="store_true", help="batch-1 steps as the one persistent step kernel (the default with tensor parallelism)")
     ap.add_argument("--quick", action="store_true", help="skip the kernel-alone and CPU measurements")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -45,6 +45,7 @@ pub const TB_DECODER_NO_GRAPH: i32 = 1;
 pub const TB_DECODER_NCCL_ONLY: i32 = 2;
 pub const TB_DECODER_NO_PDL: i32 = 4;
 pub const TB_DECODER_NO_FUSED_STEP: i32 = 8;
+pub const TB_DECODER_FUSED_STEP: i32 = 16;
 
 /// Opaque handle of a quantized linear layer (QuantizedLinear).
 #[repr(C)]

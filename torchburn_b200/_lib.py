@@ -10,7 +10,7 @@ LIB_PATH = os.environ.get("TORCHBURN_B200_LIB") or os.path.join(_HERE, "lib", "l
 
 TB_OK = 0
 TB_HOST, TB_DEVICE = 0, 1
-TB_DECODER_NO_GRAPH, TB_DECODER_NCCL_ONLY, TB_DECODER_NO_PDL, TB_DECODER_NO_FUSED_STEP = 1, 2, 4, 8
+TB_DECODER_NO_GRAPH, TB_DECODER_NCCL_ONLY, TB_DECODER_NO_PDL, TB_DECODER_NO_FUSED_STEP, TB_DECODER_FUSED_STEP = 1, 2, 4, 8, 16
 STATUS_NAMES = {1: "TB_ERR_ARG", 2: "TB_ERR_SHAPE", 3: "TB_ERR_DTYPE", 4: "TB_ERR_OOM", 5: "TB_ERR_CUDA",
                 6: "TB_ERR_NCCL", 7: "TB_ERR_TIMEOUT", 8: "TB_ERR_DEVICE_LOST", 9: "TB_ERR_UNSUPPORTED"}
 

@@ -319,6 +319,7 @@ tb_status run_step(tb_decoder* d, int b, bool greedy) {
 tb_status build_step_program(tb_decoder* d) {
   d->fused_step = false;
   if (d->cfg.flags & (TB_DECODER_NO_FUSED_STEP | TB_DECODER_NO_GRAPH)) return TB_OK;
+  if (d->tp == 1 && !(d->cfg.flags & TB_DECODER_FUSED_STEP)) return TB_OK;   // one GPU: the chain of kernels is faster (measured)
   StepTp tpa;
   if (d->tp > 1 && !tp_step_areas(d->tpst, &tpa)) return TB_OK;   // no peer memory: the chain of kernels with NCCL
   if (d->d_phases) return TB_OK;

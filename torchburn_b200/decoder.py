@@ -56,8 +56,9 @@ class B200QwenDecoder:
     [input_norm, qkv_w, qkv_s, o_w, o_s, post_norm, gate_w, gate_s, up_w, up_s,
     down_w, down_s, (qkv_b)] (numpy arrays or torch tensors; dicts keyed by those
     names are accepted too).  ``max_batch``, ``tp_size``/``tp_rank``, ``debug`` and
-    ``fused_step`` (False: batch-1 steps as a chain of single kernels instead of the one
-    persistent step kernel) have no counterpart in the reference.
+    ``fused_step`` (True: batch-1 steps as the one persistent step kernel; False: as a chain of single
+    kernels; None: the faster of the two - the step kernel with tensor parallelism, the chain on one
+    GPU) have no counterpart in the reference.
     """
 
     def __init__(self, embed_tokens, layers_data: Sequence, final_norm_w, lm_head_w, lm_head_s,
@@ -65,7 +66,7 @@ class B200QwenDecoder:
                  num_kv_heads: int, head_dim: int, group_size: int = 64, rms_norm_eps: float = 1e-6,
                  max_seq_len: int = 2048, rope_theta: float = 1000000.0, max_batch: int = 1,
                  tp_size: int = 1, tp_rank: int = 0, debug: bool = False, vocab_size: Optional[int] = None,
-                 nccl_only: bool = False, pdl: bool = True, fused_step: bool = True):
+                 nccl_only: bool = False, pdl: bool = True, fused_step: Optional[bool] = None):
         self._h = None
         ops = _Operands()
         emb_p = ops.ptr(embed_tokens, np.float32)
@@ -86,7 +87,7 @@ class B200QwenDecoder:
         lw_p = ops.ptr(lm_head_w, np.uint8)
         ls_p = ops.ptr(lm_head_s, np.float32)
         flags = ((_lib.TB_DECODER_NO_GRAPH if debug else 0) | (_lib.TB_DECODER_NCCL_ONLY if nccl_only else 0)
-                 | (0 if pdl else _lib.TB_DECODER_NO_PDL) | (0 if fused_step else _lib.TB_DECODER_NO_FUSED_STEP))
+                 | (0 if pdl else _lib.TB_DECODER_NO_PDL) | (0 if fused_step is None else (_lib.TB_DECODER_FUSED_STEP if fused_step else _lib.TB_DECODER_NO_FUSED_STEP)))
         cfg = ModelConfig(vocab_size=self.vocab_size, hidden_size=hidden_size, intermediate_size=intermediate_size,
                           num_layers=num_layers, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                           group_size=group_size, rms_norm_eps=rms_norm_eps, max_seq_len=max_seq_len,
