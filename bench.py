@@ -46,6 +46,7 @@ LLAMA70B = dict(vocab_size=128256, hidden_size=8192, intermediate_size=28672, nu
 QWEN05B = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_layers=24, num_heads=14,
                num_kv_heads=2, head_dim=64, group_size=32, rms_norm_eps=1e-6, rope_theta=1000000.0)
 CONTEXT = 4096
+_RESULT_LINE = []   # the one JSON line of this process (rank 0), printed at the very end
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from an ncu
@@ -222,7 +223,7 @@ def run_reference(args):
         "note": "CPU restatement of the reference's SIMD path (the Rust reference cannot be built here); batch 1; "
                 "the same host cores at every --gpus value",
     }
-    print(json.dumps(line))
+    _RESULT_LINE.append(json.dumps(line))
 
 
 def workload_config(c, batch, n_gpus):
@@ -575,10 +576,10 @@ def run_gpu(args):
     if args.quick:
         dec.close()
         if rank == 0:
-            print(json.dumps({"value": value, "ms_per_step": ms_per_step, "e2e": e2e_value, "n_gpus": tp, "batch": B, "model": args.model,
+            _RESULT_LINE.append(json.dumps({"value": value, "ms_per_step": ms_per_step, "e2e": e2e_value, "n_gpus": tp, "batch": B, "model": args.model,
                               "launches_per_step": launches_per_step,
                               "weights_only_frac_of_measured": step_weight_bytes(c) / tp / (ms_per_step * 1e-3) / 1e9 / measured_peak()[0],
-                              "weights_plus_kv_frac_of_measured": (step_weight_bytes(c) + B * kv_bytes_per_seq(c, CONTEXT)) / tp / (ms_per_step * 1e-3) / 1e9 / measured_peak()[0]}), flush=True)
+                              "weights_plus_kv_frac_of_measured": (step_weight_bytes(c) + B * kv_bytes_per_seq(c, CONTEXT)) / tp / (ms_per_step * 1e-3) / 1e9 / measured_peak()[0]}))
         finish()
         return
 
@@ -669,7 +670,7 @@ def run_gpu(args):
         line["qwen05b_config3"] = time_config3(torch, tb, device, args)
     if args.cpu_baseline:
         line["cpu_baseline"] = {k: v for k, v in cpu_full_step(c, CONTEXT, 8, 2).items() if not k.startswith("ms_per_step")}
-    print(json.dumps(line), flush=True)
+    _RESULT_LINE.append(json.dumps(line))
     finish()
 
 
@@ -715,10 +716,22 @@ def main():
     ap.add_argument("--step-kernel", dest="step_kernel", action="store_true", help="batch-1 steps as the one persistent step kernel (the default with tensor parallelism)")
     ap.add_argument("--quick", action="store_true", help="skip the kernel-alone and CPU measurements")
     args = ap.parse_args()
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_gpu(args)
+    # Exactly ONE line reaches stdout: the JSON.  Whatever libraries print there meanwhile (NCCL's version
+    # banner, for one) goes to stderr: file descriptor 1 points at stderr until the end.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        if args.impl == "reference":
+            run_reference(args)
+        else:
+            run_gpu(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    if _RESULT_LINE:
+        print(_RESULT_LINE[-1], flush=True)
 
 
 if __name__ == "__main__":
