@@ -130,6 +130,23 @@ def test_linear_matches_oracle(torch, tb, oracle, n, k, g, m, bias):
     assert max_rel_err(out, exact) <= max(4 * max_rel_err(want, exact), 2e-6)
 
 
+@pytest.mark.parametrize("n,k,g", [(4096, 4096, 32), (1000, 1024, 32), (515, 896, 64)])
+def test_linear_one_signed_activations_keep_the_float64_bound(torch, tb, oracle, n, k, g):
+    """All-positive activations: the sum of digits times nibbles and the -8 offset of the codes are both
+    ~2^30 per block and cancel; the kernels subtract them as integers.  The result must stay as close to
+    the float64 product as for zero-mean activations (persistent M = 1 kernel and the generic one)."""
+    rng = np.random.default_rng(n + k)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    packed, scales = oracle.quantize_int4_grouped(w, g)
+    for x in (np.abs(rng.standard_normal((1, k))).astype(np.float32) + np.float32(0.5),
+              np.full((1, k), 3.25, np.float32), -np.abs(rng.standard_normal((1, k))).astype(np.float32) - np.float32(1.0)):
+        out = tb.w4a32_grouped_linear(dev(torch, x), dev(torch, packed), dev(torch, scales), None, g).cpu().numpy()
+        want = oracle.gemm_w4a32_grouped(x, packed, scales, None, g)
+        exact = oracle.gemm_w4a32_f64(x, packed, scales, None, g)
+        assert max_rel_err(out, want) < STAGE_TOL
+        assert max_rel_err(out, exact) <= max(4 * max_rel_err(want, exact), 2e-6)
+
+
 def test_linear_int4_rs_known_answer(torch, tb, oracle):
     # tests/parity/int4.rs:172-215 restated for the CUDA path (n=64, k=896, g=64)
     from helpers import rust_test_quantize_grouped

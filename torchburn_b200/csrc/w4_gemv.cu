@@ -252,13 +252,15 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
               v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
             }
             uint32_t dig[24];
-            float sx, corr;
-            quantize_block(v, dig, sx, corr);
+            float sx;
+            int S, s8hi, s8lo;
+            quantize_part_int<32>(v, abs_max<32>(v), dig, sx, S);
+            split_offset(S, s8hi, s8lo);
             uint4* dst = xs + (size_t)m * 7 * cb + blk;
 #pragma unroll
             for (int j = 0; j < 6; ++j)
               dst[j * cb] = make_uint4(dig[4 * j], dig[4 * j + 1], dig[4 * j + 2], dig[4 * j + 3]);
-            dst[6 * cb] = make_uint4(__float_as_uint(sx), __float_as_uint(corr), 0u, 0u);
+            dst[6 * cb] = make_uint4(__float_as_uint(sx), (uint32_t)s8hi, (uint32_t)s8lo, 0u);
           }
         }
       }
@@ -294,12 +296,14 @@ __global__ void __launch_bounds__(WARPS * 32) w4_gemv_kernel(const GemvParams p)
             xq[4 * j] = t.x; xq[4 * j + 1] = t.y; xq[4 * j + 2] = t.z; xq[4 * j + 3] = t.w;
           }
           const uint4 tail = src[6 * cb];
-          const float sx = __uint_as_float(tail.x), corr = __uint_as_float(tail.y);
+          const float sx = __uint_as_float(tail.x);
+          const int s8hi = (int)tail.y, s8lo = (int)tail.z;
 #pragma unroll
           for (int q = 0; q < NW; ++q)
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-              const float d = fmaf(sx, idot32(wv[q][r], xq), corr);
+              const uint32_t w4[4] = {wv[q][r].x, wv[q][r].y, wv[q][r].z, wv[q][r].w};
+              const float d = sx * idot_words_off<4>(w4, xq, s8hi, s8lo);
               acc[q][m][r] = fmaf(d, sc[q][r], acc[q][m][r]);
             }
         }

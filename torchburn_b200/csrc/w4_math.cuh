@@ -54,6 +54,35 @@ __device__ __forceinline__ float idot_words(const uint32_t (&w)[NWORDS], const u
   return fmaf(65536.0f, (float)d2, (float)i01);
 }
 
+// The same with the offset of the codes taken in the INTEGER domain: sum(q * (nibble - 8)) =
+// sum(q * nibble) - 8 * S with 8 * S = 65536 * s8hi + s8lo (0 <= s8lo < 65536).  Both sums are about
+// 2^30 when a block of x has one sign; subtracting them as floats would cost ~2^-15 of the block maximum.
+template <int NWORDS>
+__device__ __forceinline__ float idot_words_off(const uint32_t (&w)[NWORDS], const uint32_t (&xq)[NWORDS * 6], int s8hi, int s8lo) {
+  uint32_t d0 = 0, d1 = 0, e0 = 0, e1 = 0;
+  int d2 = 0, e2 = 0;
+#pragma unroll
+  for (int wd = 0; wd < NWORDS; ++wd) {
+    const uint32_t t = w[wd] & 0x0F0F0F0Fu;
+    const uint32_t u = (w[wd] >> 4) & 0x0F0F0F0Fu;
+    d0 = dp4a_uu(t, xq[wd * 6 + 0], d0);
+    d1 = dp4a_uu(t, xq[wd * 6 + 1], d1);
+    d2 = dp4a_us(t, xq[wd * 6 + 2], d2);
+    e0 = dp4a_uu(u, xq[wd * 6 + 3], e0);
+    e1 = dp4a_uu(u, xq[wd * 6 + 4], e1);
+    e2 = dp4a_us(u, xq[wd * 6 + 5], e2);
+  }
+  d0 += e0; d1 += e1; d2 += e2;
+  const int i01 = (int)(d0 + (d1 << 8)) - s8lo;  // |.| < 2^25, exact
+  return fmaf(65536.0f, (float)(d2 - s8hi), (float)i01);
+}
+// 8 * S as the two integers idot_words_off takes.
+__device__ __forceinline__ void split_offset(int S, int& s8hi, int& s8lo) {
+  const int s8 = S * 8;   // |S| <= 32 * 2^23: no overflow
+  s8hi = s8 >> 16;        // arithmetic shift: floor
+  s8lo = s8 & 0xFFFF;
+}
+
 __device__ __forceinline__ float idot32(const uint4 wv, const uint32_t (&xq)[24]) {
   const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
   return idot_words<4>(w, xq);

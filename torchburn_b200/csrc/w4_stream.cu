@@ -227,7 +227,8 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   const int blk = (part * EPL) >> 5;
   const int group_threads = nwarps * 32;
   uint32_t dig[NWD * 6];
-  float sx = 0.f, corr = 0.f;
+  float sx = 0.f;
+  int s8hi = 0, s8lo = 0;   // 8 * sum of this lane's digits-as-integers: the offset of the codes
   float inv_rms = 1.f;
   {
     float v[EPL];
@@ -276,8 +277,10 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
     }
     float amax = abs_max<EPL>(v);
     if (EPL == 16) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // the block's other half
-    quantize_part<EPL>(v, amax, dig, sx, corr);
-    if (!has_part) { sx = 0.f; corr = 0.f; }
+    int S;
+    quantize_part_int<EPL>(v, amax, dig, sx, S);
+    split_offset(S, s8hi, s8lo);
+    if (!has_part) { sx = 0.f; s8hi = 0; s8lo = 0; }
   }
 
   if (!NORM && p.x_ss8 != nullptr && gw == 0) {
@@ -337,7 +340,7 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
               wv[0] = t2.x; wv[1] = t2.y;
             }
             const float sc = *reinterpret_cast<const float*>(base + (size_t)RS * row_bytes + (size_t)r * srow_bytes + sidx * 4);
-            val = sc * fmaf(sx, idot_words<NWD>(wv, dig), corr);
+            val = sc * (sx * idot_words_off<NWD>(wv, dig, s8hi, s8lo));
           }
           pa[q][ss * RS + r] = val;
         }
