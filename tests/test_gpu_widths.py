@@ -399,6 +399,10 @@ def test_fp32_product_mode_is_selectable_and_matches_oracle(torch, tb, oracle):
     (777, 1024, 32, 17, False, True),      # SwiGLU pair, ragged n
     (4864, 896, 32, 48, True, True),       # Qwen gate/up with bias
     (14336, 4096, 32, 64, False, True),    # Llama gate/up at M = 64
+    (256, 128, 32, 20, True, False),       # K = 128: two stages only, fewer than the ring and the prefetch depth
+    (200, 256, 128, 65, False, True),      # pair with 128-element groups, a second pass of one row
+    (1536, 1024, 64, 40, True, True),      # pair with 64-element groups
+    (96, 8192, 64, 31, False, False),      # one ragged tile, K split 64 ways at most
 ])
 def test_tcgen05_batched_product_matches_oracle(torch, tb, oracle, n, k, g, m, bias, pair):
     """More than 16 activation rows take the tcgen05 kernel (bf16 codes from tensor memory, three
