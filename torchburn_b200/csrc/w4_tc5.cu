@@ -17,18 +17,20 @@
 // tensor memory), so the weights never pass through shared memory.  The activation pieces
 // arrive as ready-made 128-byte-swizzled K-major images by bulk copy.
 //
-//   warps 0-3    128 threads (thread = weight row): the nibbles of the thread's row stream into
-//                the thread's own shared-memory ring with cp.async, eight 64-element chunks
-//                ahead; the thread unpacks a chunk into its stage of tensor memory
-//   warps 4-11   two teams of 128 threads (thread = weight row, a team = half of the activation
+//   unpacking    4 or 8 warps, 128 threads per team (thread = weight row; two teams take every other
+//                stage): the nibbles of the thread's row stream into the thread's own shared-memory
+//                ring with cp.async, eight 64-element chunks ahead; the thread unpacks a chunk into
+//                its stage of tensor memory
+//   epilogue     8 warps: two teams of 128 threads (thread = weight row, a team = half of the activation
 //                rows): per group tcgen05.ld of the accumulator, acc += scale * sum; at the
 //                end bias / residual / SwiGLU and the stores (atomic adds when K is split)
-//   warps 12-15  one lane each issues MMAs: issuing a tcgen05.mma costs its thread about 50 cycles
+//   issue        4 warps, one lane each issues MMAs: issuing a tcgen05.mma costs its thread about 50 cycles
 //                whatever its size (measured), six times the arithmetic of a 128 x 16 x 16 MMA, but
 //                several warps issue side by side.  Issuer i owns accumulator slot i and takes every
 //                group of K whose number is i modulo the number of slots (2 or 4); it commits its MMAs
-//                to the "group done" and "stage free" barriers.  Warp 12 also allocates tensor memory.
-// The bulk copies of the activation images are issued by one lane of warp 0.
+//                to the "group done" and "stage free" barriers.  The first of them also allocates tensor
+//                memory.
+// The bulk copies of the activation images are issued by the first thread of an unpacking team.
 //
 // Every wait is bounded.  No cluster features, no multicast.
 #include <cuda_bf16.h>
@@ -41,9 +43,8 @@ namespace {
 
 constexpr int kTileN = 128;     // weight rows per CTA (the MMA's M)
 constexpr int kKC = 64;         // K elements per stage: one 128-byte row of bf16
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;    // one matrix: 8 stages, a pair: 4 (tensor memory: 32 columns of codes per stage and matrix)
 constexpr int kPieces = 3;      // bf16 pieces of an activation
-constexpr int kThreads = 16 * 32;
 constexpr int kAhead = 8;       // chunks of nibbles in flight per weight row
 constexpr int kTmemCols = 512;
 constexpr int kMinRows = 17;     // up to 16 activation rows the integer mma.sync kernel is as fast or faster (measured)
@@ -63,6 +64,7 @@ struct Tc5Params {
   int ksplit, kper;          // CTAs that share a row tile, K elements of each
   int pair;                  // gate/up pair with the SwiGLU epilogue
   int slots;                 // accumulator slots in tensor memory
+  int stages;                // stage ring: 8 for one matrix, 4 for a pair
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -200,28 +202,33 @@ struct IssueCtx {
   uint64_t *full_a, *full_b, *empty, *acc_full, *acc_empty, *drained;   // drained: one per issuer
   volatile int* s_abort;
   uint32_t tmem, a_cols, acc_base, acc_cols, b_lo0, stage16, piece16, mp, idesc;
-  int nchunks, slots, nw;
+  int nchunks, slots, nw, stages, qsplit;
 };
 
-// One MMA-issuing thread of x.slots.  It takes the groups of K whose number is `me` modulo the number of
-// accumulator slots and owns slot `me`.  SPG (K16 steps per group: 2, 4 or 8) is a template parameter so that
-// the unrolled body knows at compile time where a group starts and ends; descriptors are a constant upper
-// word and a lower word that only takes additions.  An issuer skips the stages that hold none of its groups;
-// a stage's "free" barrier counts the issuers that do work in it (its groups: two of 32 elements, else one).
-template <int SPG, int NW>
+// One MMA-issuing thread.  With four accumulator slots issuer i owns slot i and takes the groups of K whose
+// number is i modulo 4, both matrices of a pair.  With two slots (a pair at 48 or 64 activation rows) four
+// issuers still work: issuer i owns slot i & 1 and only matrix i >> 1 (QSPLIT); the slot's "group done" barrier
+// then counts two commits.  SPG (K16 steps per group: 2, 4 or 8) is a template parameter so that the unrolled
+// body knows at compile time where a group starts and ends; descriptors are a constant upper word and a lower
+// word that only takes additions.  An issuer skips the stages that hold none of its groups; a stage's "free"
+// barrier counts the issuers that do work in it.
+template <int SPG, int NW, bool QSPLIT>
 __device__ __forceinline__ void issue_loop(const IssueCtx& x, const uint32_t me) {
-  const uint32_t nslots = (uint32_t)x.slots, slot_shift = x.slots == 4 ? 2u : 1u;
-  const uint32_t d_base = x.tmem + x.acc_base + me * x.acc_cols;
-  uint64_t* my_full = &x.acc_full[me];
-  uint64_t* my_empty = &x.acc_empty[me];
+  const uint32_t nslots = (uint32_t)x.slots;
+  const uint32_t my_slot = QSPLIT ? (me & 1u) : me;
+  const int q0 = QSPLIT ? (int)(me >> 1) : 0, q1 = QSPLIT ? q0 + 1 : NW;
+  const uint32_t d_base = x.tmem + x.acc_base + my_slot * x.acc_cols;
+  uint64_t* my_full = &x.acc_full[my_slot];
+  uint64_t* my_empty = &x.acc_empty[my_slot];
+  const uint32_t stage_mask = (uint32_t)x.stages - 1, stage_shift = x.stages == 8 ? 3u : 2u;
   uint32_t visits = 0;   // groups this issuer has started
   bool ok = true;
   for (int c = 0; c < x.nchunks && ok; ++c) {
     {  // first and last group of this stage: is one of them mine?
       const uint32_t g0 = ((uint32_t)c * (kKC / 16)) / SPG, g1 = ((uint32_t)c * (kKC / 16) + 3) / SPG;
-      if ((g0 & (nslots - 1)) != me && (g1 & (nslots - 1)) != me) continue;
+      if ((g0 & (nslots - 1)) != my_slot && (g1 & (nslots - 1)) != my_slot) continue;
     }
-    const uint32_t s = (uint32_t)c & (kStages - 1), par = ((uint32_t)c / kStages) & 1u;
+    const uint32_t s = (uint32_t)c & stage_mask, par = ((uint32_t)c >> stage_shift) & 1u;
     ok = mbar_wait_fast(&x.full_a[s], par, x.s_abort) && mbar_wait_fast(&x.full_b[s], par, x.s_abort);
     if (!ok) break;
     tc_fence_after();
@@ -231,7 +238,7 @@ __device__ __forceinline__ void issue_loop(const IssueCtx& x, const uint32_t me)
     for (int ks = 0; ks < kKC / 16; ++ks) {   // 16 bf16 = 32 bytes of a row = 8 columns of tensor memory per MMA
       const uint32_t t = (uint32_t)c * (kKC / 16) + ks;            // K16 step of this CTA
       const uint32_t gi = SPG == 2 ? t >> 1 : (SPG == 4 ? t >> 2 : t >> 3);
-      if ((gi & (nslots - 1)) != me) continue;
+      if ((gi & (nslots - 1)) != my_slot) continue;
       // SPG 2: groups start at ks 0 and 2; SPG 4: at ks 0; SPG 8: at ks 0 of every other chunk
       const bool starts = SPG == 2 ? (ks % 2 == 0) : (SPG == 4 ? ks == 0 : (ks == 0 && (c & 1) == 0));
       const bool ends = SPG == 2 ? (ks % 2 == 1) : (SPG == 4 ? ks == 3 : (ks == 3 && (c & 1) == 1));
@@ -247,6 +254,7 @@ __device__ __forceinline__ void issue_loop(const IssueCtx& x, const uint32_t me)
       for (int pc = 0; pc < kPieces; ++pc)
 #pragma unroll
         for (int q = 0; q < NW; ++q) {
+          if (q < q0 || q >= q1) continue;
           const uint32_t d = d_base + (uint32_t)q * x.mp, a = a_base + (uint32_t)(q * 32 + ks * 8);
           const uint32_t b = b_lo + (uint32_t)(ks * 2) + (uint32_t)pc * x.piece16;
           if (pc > 0) mma_bf16_ts<1>(d, a, b, x.idesc);
@@ -258,7 +266,6 @@ __device__ __forceinline__ void issue_loop(const IssueCtx& x, const uint32_t me)
     }
     mma_commit(&x.empty[s]);   // the stage is free once every issuer's MMAs have read it
   }
-  (void)slot_shift;
   // nothing may still be running on the tensor core when the tensor memory is given back
   mma_commit(&x.drained[me]);
   mbar_wait_fast(&x.drained[me], 0u, x.s_abort);
@@ -267,10 +274,12 @@ __device__ __forceinline__ void issue_loop(const IssueCtx& x, const uint32_t me)
 // MP: activation rows padded to a multiple of 16; NW: 1 matrix or a gate/up pair.  Template parameters keep
 // each variant's loops exactly as long as they need to be (the roles' loop bodies must stay in the
 // instruction cache) and its accumulator registers as few.
-template <int MP, int NW>
-__global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) {
+// DW: unpacking warps, 4 or 8 (two teams that take every other stage; 20 warps leave 96 registers per thread, which
+// the single-matrix variants fit).
+template <int MP, int NW, int DW>
+__global__ void __launch_bounds__((DW + 12) * 32, 1) w4_tc5_kernel(const Tc5Params p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full_a[kStages], full_b[kStages], empty[kStages], acc_full[4], acc_empty[4], drained[4];
+  __shared__ __align__(8) uint64_t full_a[kMaxStages], full_b[kMaxStages], empty[kMaxStages], acc_full[4], acc_empty[4], drained[4];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
 
@@ -282,6 +291,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
   const int nchunks = p.kper / kKC;
   const int ngroups = p.kper / p.g;
   const int slots = p.slots;
+  constexpr int kStages = NW == 1 ? 8 : 4;
+  const bool qsplit = NW == 2 && slots == 2;   // two slots: the four issuers split by matrix as well
   // tensor memory columns: [stage][matrix] 32 columns of codes (64 bf16), then [slot][matrix] mp columns of sums
   const uint32_t a_cols = 32u * NW, acc_base = kStages * a_cols, acc_cols = (uint32_t)(MP * NW);
 
@@ -290,16 +301,17 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_a[s], 4);    // one lane of each unpacking warp
       mbar_init(&full_b[s], 1);
-      mbar_init(&empty[s], p.g == 32 ? 2u : 1u);   // the issuers of the stage's groups commit to it
+      mbar_init(&empty[s], (p.g == 32 ? 2u : 1u) * (qsplit ? 2u : 1u));   // the issuers of the stage's groups commit to it
     }
     for (int s = 0; s < 4; ++s) {
-      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_full[s], qsplit ? 2u : 1u);
       mbar_init(&acc_empty[s], 8);  // one lane of each epilogue warp
     }
     for (int s = 0; s < 4; ++s) mbar_init(&drained[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 12) {
+  constexpr int kIssue0 = DW + 8;   // first issuing warp
+  if (warp == kIssue0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -308,9 +320,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
-  if (warp >= 12) {
+  if (warp >= kIssue0) {
     // ---------------- MMA issue ----------------
-    if (lane == 0 && warp - 12 < slots) {
+    if (lane == 0 && (warp - kIssue0 < slots || qsplit)) {
       IssueCtx x;
       x.full_a = full_a; x.full_b = full_b; x.empty = empty; x.acc_full = acc_full; x.acc_empty = acc_empty; x.drained = drained;
       x.s_abort = &s_abort;
@@ -321,21 +333,29 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
       x.mp = (uint32_t)MP;
       // instruction descriptor: fp32 accumulator, bf16 x bf16, B K-major, N = mp, M = 128
       x.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MP >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
-      x.nchunks = nchunks; x.slots = slots; x.nw = NW;
-      const uint32_t me = (uint32_t)(warp - 12);
-      if (p.g == 32) issue_loop<2, NW>(x, me);
-      else if (p.g == 64) issue_loop<4, NW>(x, me);
-      else issue_loop<8, NW>(x, me);
+      x.nchunks = nchunks; x.slots = slots; x.nw = NW; x.stages = kStages; x.qsplit = qsplit ? 1 : 0;
+      const uint32_t me = (uint32_t)(warp - kIssue0);
+      if (NW == 2 && qsplit) {
+        if (p.g == 32) issue_loop<2, NW, NW == 2>(x, me);
+        else if (p.g == 64) issue_loop<4, NW, NW == 2>(x, me);
+        else issue_loop<8, NW, NW == 2>(x, me);
+      } else {
+        if (p.g == 32) issue_loop<2, NW, false>(x, me);
+        else if (p.g == 64) issue_loop<4, NW, false>(x, me);
+        else issue_loop<8, NW, false>(x, me);
+      }
     }
-  } else if (warp < 4) {
-    // ---------------- unpacking: thread = weight row ----------------
-    const int row = tid;
+  } else if (warp < DW) {
+    // ---------------- unpacking: thread = weight row; with 8 warps two teams take every other stage ----------------
+    constexpr int TS = DW / 4;                 // teams
+    constexpr int PD = kAhead / TS - 1;        // own chunks in flight
+    const int team = warp >> 2, row = tid & 127;
     const int j = n0 + row;
     const bool live = j < p.n;
     const size_t roff = (size_t)(live ? j : 0) * (size_t)(p.k >> 1) + (size_t)(k0 >> 1);
     const uint8_t* w0 = p.w[0] + roff;
     const uint8_t* w1 = (NW == 2 ? p.w[1] : p.w[0]) + roff;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     // the thread's ring: [slot][matrix][row][32 bytes], the two 16-byte halves swapped for rows 4..7 of
     // every 8 so that a quarter warp touches every bank once
     const uint32_t ring = smem_u32(smem + (size_t)kStages * b_bytes);
@@ -352,13 +372,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
       }
       asm volatile("cp.async.commit_group;" ::: "memory");   // one group per chunk, empty ones included
     };
-    for (int c = 0; c < kAhead - 1; ++c) fetch(c);
-    for (int c = 0; c < nchunks; ++c) {
-      fetch(c + kAhead - 1);
-      asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");   // chunk c has landed
+    for (int i = 0; i < PD; ++i) fetch(team + i * TS);
+    for (int c = team; c < nchunks; c += TS) {
+      fetch(c + PD * TS);
+      asm volatile("cp.async.wait_group %0;" ::"n"(PD) : "memory");   // chunk c has landed
       const int s = c % kStages;
       if (c >= kStages && !mbar_wait_warp(&empty[s], (uint32_t)(c / kStages - 1) & 1u, &s_abort)) break;
-      if (tid == 0) {   // the stage's activation images: one bulk copy
+      if (row == 0) {   // the stage's activation images: one bulk copy
         mbar_expect_tx(&full_b[s], (uint32_t)b_bytes);
         bulk_g2s(smem + (size_t)s * b_bytes, p.xq + (size_t)(k0 / kKC + c) * b_bytes, (uint32_t)b_bytes, &full_b[s]);
       }
@@ -391,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
     asm volatile("cp.async.wait_all;" ::: "memory");
   } else {
     // ---------------- per-group scaling and the epilogue: thread = weight row, team = half of the activation rows ----------------
-    const int team = (warp - 4) >> 2, row = tid & 127;
+    const int team = (warp - DW) >> 2, row = tid & 127;
     const int j = n0 + row;
     const bool live = j < p.n;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -405,9 +425,54 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
     for (int q = 0; q < NW; ++q)
 #pragma unroll
       for (int i = 0; i < half; ++i) acc[q][i] = 0.f;
-    float sc0 = live ? __ldg(s0) : 0.f, sc1 = (live && NW == 2) ? __ldg(s1) : 0.f;
     bool ok = true;
-    for (int gi = 0; gi < ngroups; ++gi) {
+    // Four slots and 32-element groups: TWO groups (one 64-element stage) per visit - one wait for both slots, all
+    // their loads in flight at once (64 registers at most), one hand-back.  The fixed cost of a visit (barrier,
+    // tcgen05.ld latency, fences, arrival: ~400 cycles whatever the number of activation rows) is what bounds
+    // the kernel at few rows; the groups of a stage finish together anyway.
+    const bool two_per_visit = slots == 4 && p.g == 32;
+    if constexpr (units * NW <= 4) {
+      if (two_per_visit) {
+        float2 sa = live ? __ldg(reinterpret_cast<const float2*>(s0)) : make_float2(0.f, 0.f);
+        float2 sb = (live && NW == 2) ? __ldg(reinterpret_cast<const float2*>(s1)) : make_float2(0.f, 0.f);
+        for (int gi = 0; gi < ngroups && ok; gi += 2) {
+          const float2 ca = sa, cb2 = sb;
+          if (gi + 2 < ngroups) {
+            sa = live ? __ldg(reinterpret_cast<const float2*>(s0 + gi + 2)) : make_float2(0.f, 0.f);
+            if (NW == 2) sb = live ? __ldg(reinterpret_cast<const float2*>(s1 + gi + 2)) : make_float2(0.f, 0.f);
+          }
+          const int slot = gi & 3;   // 0 or 2: this visit takes slots slot and slot + 1
+          const uint32_t par = (uint32_t)(gi >> 2) & 1u;
+          ok = mbar_wait_warp(&acc_full[slot], par, &s_abort) && mbar_wait_warp(&acc_full[slot + 1], par, &s_abort);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d = lane_base + acc_base + (uint32_t)slot * acc_cols + (uint32_t)cb;
+          uint32_t r[2][NW][units][8];
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int q = 0; q < NW; ++q)
+#pragma unroll
+              for (int u = 0; u < units; ++u) tmem_ld8(d + (uint32_t)h * acc_cols + (uint32_t)(q * MP + u * 8), r[h][q][u]);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(&acc_empty[slot]); mbar_arrive(&acc_empty[slot + 1]); }
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int q = 0; q < NW; ++q) {
+              const float cq = q ? (h ? cb2.y : cb2.x) : (h ? ca.y : ca.x);
+#pragma unroll
+              for (int u = 0; u < units; ++u)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[q][u * 8 + i] = fmaf(cq, __uint_as_float(r[h][q][u][i]), acc[q][u * 8 + i]);
+            }
+        }
+      }
+    }
+    float sc0 = live ? __ldg(s0) : 0.f, sc1 = (live && NW == 2) ? __ldg(s1) : 0.f;
+    for (int gi = 0; gi < ngroups && !(two_per_visit && units * NW <= 4); ++gi) {
       const float c0 = sc0, c1 = sc1;
       if (gi + 1 < ngroups) {
         sc0 = live ? __ldg(s0 + gi + 1) : 0.f;
@@ -481,7 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_tc5_kernel(const Tc5Params p) 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) {
+  if (warp == kIssue0) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
@@ -601,19 +666,22 @@ tb_status launch_w4_tc5(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     p.ksplit = ksplit;
     p.kper = (int)(a.k / ksplit);
     const int nw = pair ? 2 : 1;
-    const int slots = (kTmemCols - kStages * 32 * nw) / (mp * nw);
+    const int stages = nw == 1 ? 8 : 4;
+    p.stages = stages;
+    const int slots = (kTmemCols - stages * 32 * nw) / (mp * nw);
     p.slots = slots >= 4 ? 4 : 2;   // a power of two (the issuing thread masks and shifts)
-    const size_t smem = (size_t)kStages * kPieces * mp * 128 + (size_t)kAhead * nw * kTileN * 32 + 1024;
+    const size_t smem = (size_t)stages * kPieces * mp * 128 + (size_t)kAhead * nw * kTileN * 32 + 1024;
     void (*kern)(const Tc5Params) = nullptr;
+    int threads = 16 * 32;
     switch (mp * 2 + (pair ? 1 : 0)) {
-      case 32: kern = w4_tc5_kernel<16, 1>; break;
-      case 33: kern = w4_tc5_kernel<16, 2>; break;
-      case 64: kern = w4_tc5_kernel<32, 1>; break;
-      case 65: kern = w4_tc5_kernel<32, 2>; break;
-      case 96: kern = w4_tc5_kernel<48, 1>; break;
-      case 97: kern = w4_tc5_kernel<48, 2>; break;
-      case 128: kern = w4_tc5_kernel<64, 1>; break;
-      default: kern = w4_tc5_kernel<64, 2>; break;
+      case 32: kern = w4_tc5_kernel<16, 1, 8>; threads = 20 * 32; break;
+      case 33: kern = w4_tc5_kernel<16, 2, 8>; threads = 20 * 32; break;
+      case 64: kern = w4_tc5_kernel<32, 1, 8>; threads = 20 * 32; break;
+      case 65: kern = w4_tc5_kernel<32, 2, 4>; break;
+      case 96: kern = w4_tc5_kernel<48, 1, 8>; threads = 20 * 32; break;
+      case 97: kern = w4_tc5_kernel<48, 2, 4>; break;
+      case 128: kern = w4_tc5_kernel<64, 1, 8>; threads = 20 * 32; break;
+      default: kern = w4_tc5_kernel<64, 2, 4>; break;
     }
     TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     tc5_prep_kernel<<<dim3((unsigned)mp, (unsigned)((a.k + 2047) / 2048)), 256, 0, stream>>>(
@@ -621,7 +689,7 @@ tb_status launch_w4_tc5(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     TB_CUDA_TRY(cudaGetLastError());
     if (ksplit > 1 && in_place) p.resid = nullptr;
     else if (ksplit > 1) TB_CUDA_TRY(cudaMemsetAsync(p.out, 0, sizeof(float) * (size_t)mc * a.n, stream));
-    kern<<<dim3((unsigned)tiles, (unsigned)ksplit), kThreads, smem, stream>>>(p);
+    kern<<<dim3((unsigned)tiles, (unsigned)ksplit), threads, smem, stream>>>(p);
     TB_CUDA_TRY(cudaGetLastError());
   }
   return TB_OK;
