@@ -314,6 +314,8 @@ tb_status run_step(tb_decoder* d, int b, bool greedy) {
   return TB_OK;
 }
 
+tb_status fault_word(tb_decoder* d, int** dev_ptr);
+
 // Lays out the batch-1 step for the persistent kernel when every projection fits its rules
 // (otherwise the decoder keeps the chain of single kernels).
 tb_status build_step_program(tb_decoder* d) {
@@ -409,10 +411,8 @@ tb_status build_step_program(tb_decoder* d) {
   TB_CUDA_TRY(cudaMemset(d->d_step_sync, 0, 8 * sizeof(unsigned)));
   TB_TRY(dalloc(&d->step_part_o, (size_t)d->nh_l * nc * d->hd));
   TB_TRY(dalloc(&d->step_part_ml, (size_t)d->nh_l * nc * 2));
-  TB_CUDA_TRY(cudaHostAlloc((void**)&d->h_step_fault, sizeof(int), cudaHostAllocMapped));
-  *d->h_step_fault = 0;
   int* dev_fault = nullptr;
-  TB_CUDA_TRY(cudaHostGetDevicePointer((void**)&dev_fault, d->h_step_fault, 0));
+  TB_TRY(fault_word(d, &dev_fault));
   StepProgram& g = d->prog;
   g.phases = d->d_phases; g.nphases = (int)ph.size(); g.grid = grid; g.sync = d->d_step_sync;
   g.host_fault = dev_fault;
@@ -421,6 +421,16 @@ tb_status build_step_program(tb_decoder* d) {
   g.num_heads = d->nh_l; g.num_kv_heads = d->nkv_l; g.head_dim = d->hd; g.nc = nc; g.max_seq_len = d->S;
   if (tpm) { g.tp = tpa; g.n_exchanges = n_exch; }
   d->fused_step = true;
+  return TB_OK;
+}
+
+// The host-mapped fault word of a decoder (allocated on first use); returns its device pointer.
+tb_status fault_word(tb_decoder* d, int** dev_ptr) {
+  if (!d->h_step_fault) {
+    TB_CUDA_TRY(cudaHostAlloc((void**)&d->h_step_fault, sizeof(int), cudaHostAllocMapped));
+    *d->h_step_fault = 0;
+  }
+  TB_CUDA_TRY(cudaHostGetDevicePointer((void**)dev_ptr, d->h_step_fault, 0));
   return TB_OK;
 }
 
@@ -995,6 +1005,11 @@ tb_status tb_decoder_tp_init(tb_decoder* d, const uint8_t id[128], tb_allgather_
     cudaFree(d->logits);
     d->logits = shared_logits;
     d->logits_shared = true;
+  }
+  {  // a wait of an exchange kernel that runs out is reported like one of the step kernel: TB_ERR_TIMEOUT
+    int* dev_fault = nullptr;
+    TB_TRY(fault_word(d, &dev_fault));
+    tp_set_host_fault(d->tpst, dev_fault);
   }
   TB_TRY(build_step_program(d));
   // warm-up with an out-of-range token (collective: every rank runs it)

@@ -94,6 +94,7 @@ struct PeerArgs {
   uint32_t* epoch;               // device word: number of completed exchanges
   int* done_ctas;                // ticket for the epoch increment
   int* err;
+  int* host_fault;               // optional host-mapped word: set with err, read by the host without a copy
   float* x;                      // residual stream, updated in place
   int rank, size;
   int count4;                    // float4 elements
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(1024) peer_allreduce_residual_kernel(const Pee
       if (clock64() - t0 > kPeerWaitCycles) {  // a peer never arrived: give up, flag the error
         s_ok = 0;
         atomicExch(a.err, 1);
+        if (a.host_fault) *reinterpret_cast<volatile int*>(a.host_fault) = 1;
         break;
       }
     }
@@ -178,6 +180,7 @@ struct LLArgs {
   uint4* peer_recv[kMaxRanks];      // the same area in every peer's memory
   uint32_t* epoch;
   int* err;
+  int* host_fault;
   float* x;
   const float* scale_w;             // optional: next norm's weights [count]
   float* out_scaled;                // optional: x * scale_w
@@ -217,7 +220,10 @@ __global__ void __launch_bounds__(1024) ll_allreduce_residual_kernel(const LLArg
             asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(line.x), "=r"(line.y), "=r"(line.z), "=r"(line.w) : "l"(src) : "memory");
             if (line.y == want && line.w == want) break;
             if (!ok || ((spin & 1023) == 1023 && clock64() - t0 > kPeerWaitCycles)) {  // the peer never arrived
-              if (ok) atomicExch(a.err, 1);
+              if (ok) {
+                atomicExch(a.err, 1);
+                if (a.host_fault) *reinterpret_cast<volatile int*>(a.host_fault) = 1;
+              }
               ok = false;
               break;
             }
@@ -268,6 +274,7 @@ struct TpState {
   bool fused = false;
   size_t max_count = 0;       // floats per partial
   // fused path
+  int* host_fault = nullptr;  // host-mapped word the exchange kernels raise when a bounded wait runs out
   char* block = nullptr;      // my shared block: [2][max_count] floats | flags | epoch | ticket | err
   char* peer_block[kMaxRanks] = {};
   size_t flags_off = 0;
@@ -314,6 +321,7 @@ tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int
     uint32_t* words = reinterpret_cast<uint32_t*>(st->block + st->flags_off);
     a.epoch = words + 20;
     a.err = reinterpret_cast<int*>(words + 18);
+    a.host_fault = st->host_fault;
     a.x = x;
     a.scale_w = scale_w; a.out_scaled = out_scaled; a.out_ss8 = out_ss8;
     a.rank = st->rank; a.size = st->size;
@@ -337,6 +345,7 @@ tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int
     a.epoch = words + 16;
     a.done_ctas = reinterpret_cast<int*>(words + 17);
     a.err = reinterpret_cast<int*>(words + 18);
+    a.host_fault = st->host_fault;
     a.x = x;
     a.rank = st->rank; a.size = st->size;
     a.count4 = (int)(count / 4);
@@ -388,6 +397,10 @@ bool tp_step_areas(TpState* st, StepTp* t) {
 }
 float* tp_step_logits(TpState* st) {
   return st && st->fused && st->logit_floats ? reinterpret_cast<float*>(st->block + st->step_logits_off) : nullptr;
+}
+
+void tp_set_host_fault(TpState* st, int* device_pointer_of_mapped_word) {
+  if (st) st->host_fault = device_pointer_of_mapped_word;
 }
 
 int tp_error_flag(TpState* st) {

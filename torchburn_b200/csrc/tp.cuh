@@ -32,5 +32,7 @@ float* tp_step_logits(TpState* st);
 float* tp_partial_buffer(TpState* st, float* fallback);
 // 1 after a bounded wait on a peer ran out.
 int tp_error_flag(TpState* st);
+// The exchange kernels also raise this host-mapped word (device pointer) when a bounded wait runs out.
+void tp_set_host_fault(TpState* st, int* device_pointer_of_mapped_word);
 
 }  // namespace tb
