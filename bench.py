@@ -601,6 +601,7 @@ def run_gpu(args):
     tp_check = tp_correctness_check(torch, dist, tb, c, device, tp, rank, args) if tp > 1 else None
     # the other batch sizes of the workload configuration: tokens/s at batch 8 and 32
     batch_sweep = None
+    verify = None
     if args.model == "llama8b" and B == 1 and args.batch_sweep:
         dec.close()
         dec = None
@@ -614,6 +615,26 @@ def run_gpu(args):
             m = float(np.median(r_ms)) / 8
             batch_sweep[str(bb)] = {"tokens_per_s": bb * 1e3 / m, "ms_per_step": m,
                                     "weights_plus_kv_frac": (step_weight_bytes(c) + bb * kv_bytes_per_seq(c, CONTEXT)) / tp / (m * 1e-3) / 1e9 / measured_peak()[0]}
+        # speculative verify (src/llm/decoder.rs:565-581): K + 1 = 5 positions of one sequence as ONE batched step
+        # against 5 single-position steps, through the host API (token ids in, 5 rows of logits out)
+        if tp == 1:
+            vt = [11, 22, 33, 44, 55]
+
+            def wall(fn, reps=5):
+                fn()
+                torch.cuda.synchronize(device)
+                best = None
+                for _ in range(reps):
+                    t0 = time.perf_counter()
+                    fn()
+                    dt = (time.perf_counter() - t0) * 1e3
+                    best = dt if best is None else min(best, dt)
+                return best
+
+            ms_b = wall(lambda: big.verify_tokens(CONTEXT, vt))
+            ms_s = wall(lambda: [big.step(t, CONTEXT + i) for i, t in enumerate(vt)])
+            verify = {"positions": len(vt), "ms_one_batched_step": ms_b, "ms_single_steps": ms_s,
+                      "note": "best of 5 wall-clock calls of verify_tokens / of 5 step() calls, context 4096"}
         big.close()
     if rank != 0:
         if dec is not None:
@@ -648,6 +669,7 @@ def run_gpu(args):
             "weights_only_frac": wb / step_s / 1e9 / peak, "weights_plus_kv_frac": (wb + kvb * B) / step_s / 1e9 / peak,
             "peak_kind": f"of {peak_kind}", "launches_per_step": launches_per_step},
         "step_form": "persistent step kernel" if launches_per_step == 2 else "chain of single kernels", "other_step_form": other_form,
+        "verify_tokens": verify,
         "gemv_config1": {"shape": "4096x4096 group 32, M=1", "algorithmic_bytes": c1_alg, "us_per_launch": c1_sec * 1e6,
                          "achieved_gbs": c1_alg / c1_sec / 1e9, "frac_of_measured": c1_alg / c1_sec / 1e9 / peak,
                          "frac_of_nominal_8TBs": c1_alg / c1_sec / 1e9 / NOMINAL_HBM_GBS,
