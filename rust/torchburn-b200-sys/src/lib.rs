@@ -144,6 +144,7 @@ extern "C" {
     pub fn tb_debug_timeline_blocks() -> i32;
     pub fn tb_debug_step_flags(flags: i32);
     pub fn tb_debug_wait_probe(limit_cycles: i64) -> tb_status;
+    pub fn tb_debug_step_wait_limit(cycles: i64);
     pub fn tb_debug_step_gemv(x: *const f32, w: *const u8, scales: *const f32, bias: *const f32, w2: *const u8, scales2: *const f32, out: *mut f32, n: i64, k: i64, group_size: i32, stream: *mut c_void) -> tb_status;
     pub fn tb_set_attention_chunk(positions: i32);
     pub fn tb_set_attention_tuning(ctas_per_sm: i32, ring_stages: i32);

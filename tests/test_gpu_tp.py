@@ -106,3 +106,94 @@ def test_tp_decoder_matches_oracle(world, variant):
             assert launches == 2, launches   # the embedding kernel + the one persistent step kernel
         elif variant in ("chain", "widechain"):
             assert launches > 2
+
+
+def _rank_peer_missing(rank, world, port, q):
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.dirname(HERE))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import time
+
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import torchburn_b200 as tb
+        from helpers import synth_model
+        from oracle import oracle as o
+        from torchburn_b200.tp import init_tensor_parallel
+        from tp_helpers import shard_model
+
+        cfg = dict(vocab_size=1024, hidden_size=1024, intermediate_size=2048, num_layers=2, num_heads=16,
+                   num_kv_heads=8, head_dim=64, group_size=32, max_seq_len=64, rms_norm_eps=1e-6, rope_theta=5e5)
+        embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 3, o.quantize_int4_grouped, qkv_bias=True)
+        layers_r, lw_r, ls_r = shard_model(tb, cfg, layers, lm_w, lm_s, rank, world)
+        order = ["input_norm_w", "qkv_w", "qkv_s", "o_w", "o_s", "post_norm_w", "gate_w", "gate_s", "up_w", "up_s",
+                 "down_w", "down_s", "qkv_b"]
+        dec = tb.B200QwenDecoder(embed, [[lw[k] for k in order] for lw in layers_r], fnorm, lw_r, ls_r,
+                                 cfg["num_layers"], cfg["hidden_size"], cfg["intermediate_size"], cfg["num_heads"],
+                                 cfg["num_kv_heads"], cfg["head_dim"], cfg["group_size"], cfg["rms_norm_eps"],
+                                 cfg["max_seq_len"], cfg["rope_theta"], tp_size=world, tp_rank=rank,
+                                 vocab_size=cfg["vocab_size"], fused_step=True)
+        init_tensor_parallel(dec, dist, torch.device("cuda", rank))
+        dec.step(3, 0)                      # a normal step of both ranks
+        dist.barrier()
+        status, lost, seconds = None, None, None
+        if rank == 0:
+            tb.lib().tb_debug_step_wait_limit(1_500_000_000)   # under a second at 1.9 GHz
+            t0 = time.perf_counter()
+            try:
+                dec.step(5, 1)              # rank 1 never runs this step: its partial rows never arrive
+                status = 0
+            except tb.TorchBurnB200Error as e:
+                status = e.status
+            seconds = time.perf_counter() - t0
+            lost = dec.is_device_lost()
+            try:
+                dec.step(6, 2)              # a lost decoder refuses further work
+                after = 0
+            except tb.TorchBurnB200Error as e:
+                after = e.status
+            q.put((rank, status, lost, seconds, after))
+        else:
+            time.sleep(8)                   # stays away from the step; launches nothing meanwhile
+            q.put((rank, None, dec.is_device_lost(), None, None))
+        dist.barrier()                      # both ranks are alive: no kernel of either is waiting for the other
+        dec.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_peer_that_never_arrives_is_reported_as_timeout():
+    """Failure detection without a fault: rank 1 stays away from a step (on the host, between steps, with
+    nothing in flight); the bounded waits of rank 0's step kernel run out, the kernel ends, the call
+    returns TB_ERR_TIMEOUT within seconds and the decoder is marked lost.  Plain peer stores and
+    loads only (no multimem), NVLS off in NCCL."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("no CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29980 + (os.getpid() % 15)
+    procs = [ctx.Process(target=_rank_peer_missing, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict((r[0], r) for r in (q.get(timeout=300) for _ in procs))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    _, status, lost, seconds, after = results[0]
+    assert status == 7, status              # TB_ERR_TIMEOUT
+    assert lost
+    assert seconds < 10
+    assert after == 8                       # TB_ERR_DEVICE_LOST
+    assert not results[1][2]                # the rank that stayed away is unaffected

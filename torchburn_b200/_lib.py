@@ -68,6 +68,7 @@ SIGNATURES = {
     "tb_debug_timeline_blocks": (_i32, []),
     "tb_debug_step_flags": (None, [_i32]),
     "tb_debug_wait_probe": (_i32, [_i64]),
+    "tb_debug_step_wait_limit": (None, [_i64]),
     "tb_debug_step_gemv": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _p]),
     "tb_set_attention_chunk": (None, [_i32]),
     "tb_set_attention_tuning": (None, [_i32, _i32]),
