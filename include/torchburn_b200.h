@@ -172,8 +172,8 @@ void tb_debug_step_flags(int32_t flags);
  * waits must give up and raise the fault word.  Returns TB_ERR_TIMEOUT when they did (the word is
  * cleared again), TB_ERR_CUDA on any other outcome.  Nothing hangs, traps or faults. */
 tb_status tb_debug_wait_probe(int64_t limit_cycles);
-/* The limit, in clock cycles, of every bounded wait of the persistent step kernel (0 = the default of
- * about two seconds).  Failure-detection tests shorten it so that a peer that never arrives is reported
+/* The limit, in clock cycles, of every bounded wait of the persistent step kernel and of the tensor-parallel
+ * exchange kernels' waits for their peers (0 = the defaults of about two and ten seconds).  Failure-detection tests shorten it so that a peer that never arrives is reported
  * (TB_ERR_TIMEOUT, decoder marked lost) within a second.  Process-wide. */
 void tb_debug_step_wait_limit(int64_t cycles);
 /* One projection through the persistent step kernel's code path (a program of one phase):

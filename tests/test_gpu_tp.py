@@ -108,7 +108,7 @@ def test_tp_decoder_matches_oracle(world, variant):
             assert launches > 2
 
 
-def _rank_peer_missing(rank, world, port, q):
+def _rank_peer_missing(rank, world, port, q, fused):
     sys.path.insert(0, HERE)
     sys.path.insert(0, os.path.dirname(HERE))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -138,7 +138,7 @@ def _rank_peer_missing(rank, world, port, q):
                                  cfg["num_layers"], cfg["hidden_size"], cfg["intermediate_size"], cfg["num_heads"],
                                  cfg["num_kv_heads"], cfg["head_dim"], cfg["group_size"], cfg["rms_norm_eps"],
                                  cfg["max_seq_len"], cfg["rope_theta"], tp_size=world, tp_rank=rank,
-                                 vocab_size=cfg["vocab_size"], fused_step=True)
+                                 vocab_size=cfg["vocab_size"], fused_step=fused)
         init_tensor_parallel(dec, dist, torch.device("cuda", rank))
         dec.step(3, 0)                      # a normal step of both ranks
         dist.barrier()
@@ -168,11 +168,13 @@ def _rank_peer_missing(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_tp_peer_that_never_arrives_is_reported_as_timeout():
+def test_tp_peer_that_never_arrives_is_reported_as_timeout(fused=True):
     """Failure detection without a fault: rank 1 stays away from a step (on the host, between steps, with
     nothing in flight); the bounded waits of rank 0's step kernel run out, the kernel ends, the call
     returns TB_ERR_TIMEOUT within seconds and the decoder is marked lost.  Plain peer stores and
-    loads only (no multimem), NVLS off in NCCL."""
+    loads only (no multimem), NVLS off in NCCL.  (Only the persistent step kernel is tested this way:
+    the chain of kernels gathers the logits with ncclAllGather, whose wait for a missing peer is NCCL's
+    own and is not bounded by this library.)"""
     import torch
 
     if not torch.cuda.is_available():
@@ -183,8 +185,8 @@ def test_tp_peer_that_never_arrives_is_reported_as_timeout():
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29980 + (os.getpid() % 15)
-    procs = [ctx.Process(target=_rank_peer_missing, args=(r, 2, port, q)) for r in range(2)]
+    port = 29960 + (os.getpid() % 15) + (20 if fused else 0)
+    procs = [ctx.Process(target=_rank_peer_missing, args=(r, 2, port, q, fused)) for r in range(2)]
     for p in procs:
         p.start()
     results = dict((r[0], r) for r in (q.get(timeout=300) for _ in procs))

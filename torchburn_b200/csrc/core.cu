@@ -5,6 +5,7 @@
 #include <new>
 
 #include "tb_common.cuh"
+#include "tp.cuh"
 
 namespace tb {
 
@@ -238,7 +239,10 @@ void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb,
 void tb_debug_timeline(void* device_buffer, int64_t bytes) { timeline_register(device_buffer, bytes); }
 void tb_debug_step_flags(int32_t flags) { set_step_debug(flags); }
 tb_status tb_debug_wait_probe(int64_t limit_cycles) { return step_wait_probe((long long)limit_cycles); }
-void tb_debug_step_wait_limit(int64_t cycles) { set_step_wait_limit((long long)cycles); }
+void tb_debug_step_wait_limit(int64_t cycles) {
+  set_step_wait_limit((long long)cycles);
+  tp_set_wait_limit((long long)cycles);
+}
 
 tb_status tb_debug_step_gemv(const float* x, const uint8_t* w, const float* scales, const float* bias, const uint8_t* w2,
                              const float* scales2, float* out, int64_t n, int64_t k, int32_t group_size, void* stream) {

@@ -86,6 +86,7 @@ NcclApi* nccl() {
 constexpr int kMaxRanks = 8;
 constexpr int kLLLines = 8192;     // float2 lines per rank in the low-latency receive area (16384 floats)
 constexpr long long kPeerWaitCycles = 20000000000ll;  // ~10 s: ranks may be apart by a graph instantiation
+long long g_peer_wait_cycles = 0;   // test hook: a shorter limit (0 = the default above)
 
 struct PeerArgs {
   const float* bufs[kMaxRanks];  // every rank's partial for this call, [count] floats
@@ -95,6 +96,7 @@ struct PeerArgs {
   int* done_ctas;                // ticket for the epoch increment
   int* err;
   int* host_fault;               // optional host-mapped word: set with err, read by the host without a copy
+  long long wait_cycles;         // limit of the wait for the peers
   float* x;                      // residual stream, updated in place
   int rank, size;
   int count4;                    // float4 elements
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(1024) peer_allreduce_residual_kernel(const Pee
   if (threadIdx.x < a.size) {
     const long long t0 = clock64();
     while (ld_acquire_sys(a.my_flags + threadIdx.x) < want) {
-      if (clock64() - t0 > kPeerWaitCycles) {  // a peer never arrived: give up, flag the error
+      if (clock64() - t0 > a.wait_cycles) {  // a peer never arrived: give up, flag the error
         s_ok = 0;
         atomicExch(a.err, 1);
         if (a.host_fault) *reinterpret_cast<volatile int*>(a.host_fault) = 1;
@@ -181,6 +183,7 @@ struct LLArgs {
   uint32_t* epoch;
   int* err;
   int* host_fault;
+  long long wait_cycles;
   float* x;
   const float* scale_w;             // optional: next norm's weights [count]
   float* out_scaled;                // optional: x * scale_w
@@ -219,7 +222,7 @@ __global__ void __launch_bounds__(1024) ll_allreduce_residual_kernel(const LLArg
           for (uint32_t spin = 0;; ++spin) {
             asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(line.x), "=r"(line.y), "=r"(line.z), "=r"(line.w) : "l"(src) : "memory");
             if (line.y == want && line.w == want) break;
-            if (!ok || ((spin & 1023) == 1023 && clock64() - t0 > kPeerWaitCycles)) {  // the peer never arrived
+            if (!ok || ((spin & 1023) == 1023 && clock64() - t0 > a.wait_cycles)) {  // the peer never arrived
               if (ok) {
                 atomicExch(a.err, 1);
                 if (a.host_fault) *reinterpret_cast<volatile int*>(a.host_fault) = 1;
@@ -322,6 +325,7 @@ tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int
     a.epoch = words + 20;
     a.err = reinterpret_cast<int*>(words + 18);
     a.host_fault = st->host_fault;
+    a.wait_cycles = g_peer_wait_cycles > 0 ? g_peer_wait_cycles : kPeerWaitCycles;
     a.x = x;
     a.scale_w = scale_w; a.out_scaled = out_scaled; a.out_ss8 = out_ss8;
     a.rank = st->rank; a.size = st->size;
@@ -346,6 +350,7 @@ tb_status tp_allreduce_residual(TpState* st, const float* partial, float* x, int
     a.done_ctas = reinterpret_cast<int*>(words + 17);
     a.err = reinterpret_cast<int*>(words + 18);
     a.host_fault = st->host_fault;
+    a.wait_cycles = g_peer_wait_cycles > 0 ? g_peer_wait_cycles : kPeerWaitCycles;
     a.x = x;
     a.rank = st->rank; a.size = st->size;
     a.count4 = (int)(count / 4);
@@ -398,6 +403,8 @@ bool tp_step_areas(TpState* st, StepTp* t) {
 float* tp_step_logits(TpState* st) {
   return st && st->fused && st->logit_floats ? reinterpret_cast<float*>(st->block + st->step_logits_off) : nullptr;
 }
+
+void tp_set_wait_limit(long long cycles) { g_peer_wait_cycles = cycles; }
 
 void tp_set_host_fault(TpState* st, int* device_pointer_of_mapped_word) {
   if (st) st->host_fault = device_pointer_of_mapped_word;

@@ -34,5 +34,7 @@ float* tp_partial_buffer(TpState* st, float* fallback);
 int tp_error_flag(TpState* st);
 // The exchange kernels also raise this host-mapped word (device pointer) when a bounded wait runs out.
 void tp_set_host_fault(TpState* st, int* device_pointer_of_mapped_word);
+// Test hook: limit in clock cycles of the exchange kernels' waits for their peers (0 = default, ~10 s).
+void tp_set_wait_limit(long long cycles);
 
 }  // namespace tb
