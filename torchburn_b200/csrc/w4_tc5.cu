@@ -14,7 +14,8 @@
 // The weights are the M = 128 side of the MMA (a CTA owns 128 weight rows), the activation
 // rows its N = 16..64.  A weight row lives in one LANE of tensor memory: the thread that
 // dequantises row r writes its codes with tcgen05.st straight from registers (A operand from
-// tensor memory), so the weights never pass through shared memory.  The activation pieces
+// tensor memory), so the weights pass through shared memory only as packed nibbles (the per-thread
+// copy ring), never in operand form.  The activation pieces
 // arrive as ready-made 128-byte-swizzled K-major images by bulk copy.
 //
 //   unpacking    4 or 8 warps, 128 threads per team (thread = weight row; two teams take every other
@@ -26,10 +27,10 @@
 //                end bias / residual / SwiGLU and the stores (atomic adds when K is split)
 //   issue        4 warps, one lane each issues MMAs: issuing a tcgen05.mma costs its thread about 50 cycles
 //                whatever its size (measured), six times the arithmetic of a 128 x 16 x 16 MMA, but
-//                several warps issue side by side.  Issuer i owns accumulator slot i and takes every
-//                group of K whose number is i modulo the number of slots (2 or 4); it commits its MMAs
-//                to the "group done" and "stage free" barriers.  The first of them also allocates tensor
-//                memory.
+//                several warps issue side by side.  With four accumulator slots issuer i owns slot i and
+//                takes every group of K whose number is i modulo 4; with two slots (a pair at 48 or 64
+//                rows) issuer i owns slot i & 1 and matrix i >> 1.  An issuer commits its MMAs to the
+//                "group done" and "stage free" barriers.  The first of them also allocates tensor memory.
 // The bulk copies of the activation images are issued by the first thread of an unpacking team.
 //
 // Every wait is bounded.  No cluster features, no multicast.
