@@ -131,14 +131,14 @@ struct MmaParams {
 // are 13 times the bytes of the weights they meet.  Scales ride in the stage too (no global
 // load inside the K loop); three cp.async stages.
 // ------------------------------------------------------------------------------------------
-template <int MT, int WR, int WK, int EPI, int KC>
+template <int MT, int WR, int WK, int EPI, int KC, int NS = 3>
 __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaParams p) {
   constexpr int NW = EPI == 1 ? 2 : 1;
   constexpr int NT = 32 * WR * WK;        // threads
   constexpr int RC = 16 * WR;             // weight rows per CTA
   constexpr int WROW = KC * 4 + 4;        // words per staged weight row (16 bytes of padding)
   constexpr int SROW = KC + 1;            // staged scales per row (padded)
-  constexpr int NS = 3;                   // stages
+  constexpr int PD = NS - 1;              // chunks requested ahead
   extern __shared__ __align__(16) uint32_t sm[];
   // stage layout: weights [NW][RC][WROW] | scales [NW][RC][SROW] | digits [KC][MT][208]
   constexpr int W_WORDS = NW * RC * WROW;
@@ -200,21 +200,23 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[q][nt][i] = 0.f;
 
-  issue_w(0, 0);
-  if (nchunks > 1) issue_w(1, 1);
+#pragma unroll
+  for (int i = 0; i < PD; ++i)
+    if (i < nchunks) issue_w(i, i);
   pdl_wait();
   pdl_launch_dependents();
-  issue_x(0, 0);
-  if (nchunks > 1) issue_x(1, 1);
+#pragma unroll
+  for (int i = 0; i < PD; ++i)
+    if (i < nchunks) issue_x(i, i);
   for (int ch = 0; ch < nchunks; ++ch) {
-    if (ch + 2 < nchunks) {
-      issue(ch + 2, (ch + 2) % NS);
-      cp_async_wait<2>();
-    } else if (ch + 1 < nchunks) {
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    if (ch + PD < nchunks) issue(ch + PD, (ch + PD) % NS);
+    const int pend = min(PD, nchunks - 1 - ch);   // copy groups that may stay in flight while chunk ch is used
+    if (pend >= 5) cp_async_wait<5>();
+    else if (pend == 4) cp_async_wait<4>();
+    else if (pend == 3) cp_async_wait<3>();
+    else if (pend == 2) cp_async_wait<2>();
+    else if (pend == 1) cp_async_wait<1>();
+    else cp_async_wait<0>();
     __syncthreads();
     const uint32_t* ws = sm + (ch % NS) * STAGE;
     const float* ss = reinterpret_cast<const float*>(ws + W_WORDS);
@@ -331,15 +333,15 @@ __global__ void __launch_bounds__(32 * WR * WK) w4_mma_rows_kernel(const MmaPara
     }
 }
 
-template <int MT, int WR, int WK, int EPI, int KC>
+template <int MT, int WR, int WK, int EPI, int KC, int NS = 3>
 tb_status launch_rows_cfg(const MmaParams& p, cudaStream_t stream) {
   constexpr int NW = EPI == 1 ? 2 : 1;
   constexpr int RC = 16 * WR;
   constexpr size_t stage_words = (size_t)NW * RC * (KC * 4 + 4) + (((size_t)NW * RC * (KC + 1) + 3) & ~(size_t)3) + (size_t)KC * MT * kTileWords;
   constexpr size_t red_words = WK > 1 ? (size_t)WR * WK * NW * MT * 4 * 32 : 0;
-  constexpr size_t smem = sizeof(uint32_t) * (3 * stage_words > red_words ? 3 * stage_words : red_words);
+  constexpr size_t smem = sizeof(uint32_t) * (NS * stage_words > red_words ? NS * stage_words : red_words);
   static_assert(smem <= 200 * 1024, "stage too large");
-  auto kern = w4_mma_rows_kernel<MT, WR, WK, EPI, KC>;
+  auto kern = w4_mma_rows_kernel<MT, WR, WK, EPI, KC, NS>;
   static thread_local bool configured[64] = {false};
   int dev = 0;
   TB_CUDA_TRY(cudaGetDevice(&dev));
@@ -365,11 +367,16 @@ template <int MT, int EPI, int KC>
 tb_status launch_rows_mt(const MmaParams& p, cudaStream_t stream) {
   // rows per CTA so that the grid is about one CTA per SM or more; narrow matrices split K over warps
   const int per_sm = p.n / sm_count();
-  // Few activation tiles: the digits are small, so many small CTAs (32 rows, 3-4 resident per SM) keep more
-  // warps in flight than one CTA of 96 rows per SM; many tiles: the digit traffic decides, large CTAs.
-  // Measured on the Llama-3-8B shapes (tokens/s of the whole step, 32 rows per CTA in every case):
-  // batch 8 / 16: 4 warps, K split in two, 1466 / 1840 against 965 / 1254 with 96-row CTAs; batch 32: 8 warps,
-  // K split in four, 1980 against 1919; batch 64: 4 warps, 2166 against 1952.
+  // Up to 16 activation rows (MT <= 2), graph-timed on the Llama-3-8B shapes at 8 / 16 rows: CTAs of 64 weight
+  // rows with 8 warps (4 side by side, K of a stage split in two) against CTAs of 32 rows with 4 warps: gate/up
+  // pair 42.7 / 61.9 us against 46.5 / 71.8; the K = 14336 projection 33.2 (K split over 4 CTAs) / 44.0 against
+  // 40.1 / 49.4.  The narrow K = 4096 projections at 8 rows stay with 32-row CTAs of 8 warps (19.7 against 24.8 us).
+  // A fourth stage, stages of 128 elements of K and CTAs of 16 or 128 rows were measured too: none is faster.
+  // More than 16 rows (reached only with the tcgen05 kernel switched off): the digit traffic decides.
+  if (MT <= 2) {
+    if (MT == 2 || per_sm >= 64 || p.ksplit > 1) return launch_rows_cfg<MT, 4, 2, EPI, KC>(p, stream);
+    return launch_rows_cfg<MT, 2, 4, EPI, KC>(p, stream);
+  }
   if (MT != 4 && per_sm >= 64) return launch_rows_cfg<MT, 2, 2, EPI, KC>(p, stream);
   return launch_rows_cfg<MT, 2, 4, EPI, KC>(p, stream);
 }
@@ -427,7 +434,7 @@ tb_status launch_w4_mma(const GemvArgs& a, void* scratch, cudaStream_t stream) {
     // Narrow single matrices at many activation rows: 32-row CTAs alone leave SMs idle, so 2 or 4 CTAs
     // share a row tile and split K (deterministic sum by the last one to finish).
     int ksplit = 1;
-    if (!a.w2 && mt >= 2 && a.n <= kSplitMaxN && a.n / 32 < sm_count() && a.k >= 4096) ksplit = a.k >= 8192 ? 4 : 2;
+    if (!a.w2 && (mt >= 2 || a.k >= 8192) && a.n <= kSplitMaxN && a.n / 32 < sm_count() && a.k >= 4096) ksplit = a.k >= 8192 ? 4 : 2;
     p.ksplit = ksplit;
     p.ksplit_cnt = reinterpret_cast<int*>(scratch);
     p.ksplit_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + kSplitHeader + digit_bytes(mc, a.k));
