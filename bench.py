@@ -602,6 +602,7 @@ def run_gpu(args):
     # the other batch sizes of the workload configuration: tokens/s at batch 8 and 32
     batch_sweep = None
     verify = None
+    prefill = None
     if args.model == "llama8b" and B == 1 and args.batch_sweep:
         dec.close()
         dec = None
@@ -635,6 +636,13 @@ def run_gpu(args):
             ms_s = wall(lambda: [big.step(t, CONTEXT + i) for i, t in enumerate(vt)])
             verify = {"positions": len(vt), "ms_one_batched_step": ms_b, "ms_single_steps": ms_s,
                       "note": "best of 5 wall-clock calls of verify_tokens / of 5 step() calls, context 4096"}
+            # prompt processing (src/llm/decoder.rs:431-447): 128 prompt positions ending at the context length,
+            # 32 per batched step on this decoder against one step per token
+            pt = [int(t) for t in np.random.default_rng(5).integers(0, c["vocab_size"], 128)]
+            ms_pb = wall(lambda: big.prefill_tokens(pt, CONTEXT - 128), reps=3)
+            ms_ps = wall(lambda: [big.step(t, CONTEXT - 128 + i) for i, t in enumerate(pt)], reps=2)
+            prefill = {"tokens": len(pt), "ms_batched": ms_pb, "ms_token_by_token": ms_ps, "tokens_per_s_batched": len(pt) * 1e3 / ms_pb,
+                       "note": "wall clock, positions 3968..4095 of one sequence; decoder built for 32 rows"}
         big.close()
     if rank != 0:
         if dec is not None:
@@ -669,7 +677,7 @@ def run_gpu(args):
             "weights_only_frac": wb / step_s / 1e9 / peak, "weights_plus_kv_frac": (wb + kvb * B) / step_s / 1e9 / peak,
             "peak_kind": f"of {peak_kind}", "launches_per_step": launches_per_step},
         "step_form": "persistent step kernel" if launches_per_step == 2 else "chain of single kernels", "other_step_form": other_form,
-        "verify_tokens": verify,
+        "verify_tokens": verify, "prefill_tokens": prefill,
         "gemv_config1": {"shape": "4096x4096 group 32, M=1", "algorithmic_bytes": c1_alg, "us_per_launch": c1_sec * 1e6,
                          "achieved_gbs": c1_alg / c1_sec / 1e9, "frac_of_measured": c1_alg / c1_sec / 1e9 / peak,
                          "frac_of_nominal_8TBs": c1_alg / c1_sec / 1e9 / NOMINAL_HBM_GBS,

@@ -385,8 +385,11 @@ tb_status tb_decoder_step(tb_decoder* dec, int64_t token_id, int64_t offset, flo
  * running one decoder object per sequence (python/torchburn/llm/speculative.py:293-379). */
 tb_status tb_decoder_step_batch(tb_decoder* dec, const int64_t* token_ids, const int64_t* offsets,
                                 int32_t batch, float* logits_host);
-/* prefill_tokens, src/llm/decoder.rs:431-447: sequential steps; *end_offset =
- * start_offset + n; TB_ERR_ARG when it would pass max_seq_len. */
+/* prefill_tokens, src/llm/decoder.rs:431-447: the prompt's positions in order;
+ * *end_offset = start_offset + n; TB_ERR_ARG when it would pass max_seq_len.
+ * A decoder built for one row steps token by token like the reference; one
+ * built with max_batch > 1 takes max_batch positions of sequence 0 per
+ * batched step (one pass over the weights for all of them). */
 tb_status tb_decoder_prefill_tokens(tb_decoder* dec, const int64_t* tokens, int64_t n,
                                     int64_t start_offset, int64_t* end_offset);
 /* prefill, src/llm/decoder.rs:545-558: tokens at offsets 0..n-1, last logits out. */

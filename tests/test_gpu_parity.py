@@ -700,6 +700,38 @@ def test_verify_tokens_is_one_batched_step_and_matches_sequential_steps(torch, t
     del launches_before
 
 
+@pytest.mark.parametrize("max_batch,n", [(8, 21), (32, 41)])
+def test_prefill_on_a_decoder_with_several_rows_runs_batched_and_matches_sequential_steps(torch, tb, oracle, max_batch, n):
+    """prefill_tokens / prefill (src/llm/decoder.rs:431-447, 545-558) on a decoder built for several rows take
+    max_batch positions of the prompt per step (several slabs here, the last one ragged, and a second call that
+    continues at an offset).  Cache rows and logits must equal those of the token-by-token oracle."""
+    cfg = dict(vocab_size=211, hidden_size=128, intermediate_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+               head_dim=32, group_size=32, max_seq_len=64, rms_norm_eps=1e-6, rope_theta=1e6)
+    embed, layers, fnorm, lm_w, lm_s = synth_model(cfg, 78, oracle.quantize_int4_grouped, std=0.3)
+    a = _make(tb, cfg, embed, layers, fnorm, lm_w, lm_s, max_batch=max_batch)
+    ref = oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+    toks = [int(t) for t in np.random.default_rng(n).integers(0, cfg["vocab_size"], n)]
+    steps_before = a.launches_per_step()
+    assert a.prefill_tokens(toks[:5], 0) == 5
+    assert a.prefill_tokens(toks[5:], 5) == n
+    assert a.kv_len() == n
+    want = [ref.step(t, i) for i, t in enumerate(toks)]
+    assert max_rel_err(a.get_logits().reshape(-1)[:cfg["vocab_size"]], want[-1]) < LOGIT_TOL
+    for l in range(cfg["num_layers"]):
+        gk, gv = a.read_kv_cache(l)
+        ek, ev = ref.kv_cache(l)
+        for pos in range(n):
+            assert max_rel_err(gk[:, pos], ek[:, pos]) < STAGE_TOL, ("k", l, pos)
+            assert max_rel_err(gv[:, pos], ev[:, pos]) < STAGE_TOL, ("v", l, pos)
+        assert not gk[:, n:].any() and not gv[:, n:].any()
+    assert max_rel_err(a.step(7, n), ref.step(7, n)) < LOGIT_TOL
+    # prefill(): from position 0 again, logits of the last prompt token
+    a.reset_kv_cache()
+    assert max_rel_err(a.prefill(toks), want[-1]) < LOGIT_TOL
+    assert tb.lib().tb_device_fault_flag() == 0
+    del steps_before
+
+
 def test_v2_layout_linear_matches_oracle_v2_kernel(torch, tb, oracle):
     # python/torchburn/quantization.py:121-190 and tests/test_parity.py:156-206: the v2 blocks carry the
     # same codes as v1 and binary16 scales; the linear on them equals the scalar v2 kernel of the

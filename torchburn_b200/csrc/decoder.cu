@@ -463,6 +463,46 @@ tb_status feed_and_step(tb_decoder* d, const int64_t* tokens, const int64_t* off
   return run_step(d, b, false);
 }
 
+// n consecutive positions of sequence 0, max_batch of them per step: the rows of a step are positions of the
+// ONE sequence (batched products, attention rows sharing sequence 0's cache, causal inside the block).  All
+// tokens and offsets are staged in pinned memory first, every step copying from its own part, so that the host
+// never rewrites words an earlier, still queued copy has yet to read.  rows_host (optional) receives the
+// logits of every position.  Afterwards the decoder's own logits are those of the last position.
+tb_status run_positions(tb_decoder* d, const int64_t* tokens, int64_t n, int64_t start_offset, float* rows_host) {
+  if (n > d->feed_cap) {
+    cudaFreeHost(d->h_feed);
+    d->h_feed = nullptr;
+    d->feed_cap = 0;
+    DEC_CUDA(d, cudaMallocHost((void**)&d->h_feed, sizeof(int32_t) * 2 * n));
+    d->feed_cap = n;
+  }
+  for (int64_t i = 0; i < n; ++i) {
+    d->h_feed[i] = clamp_i32(tokens[i]);
+    d->h_feed[n + i] = clamp_i32(start_offset + i);
+    note_kv(d, tokens[i], start_offset + i);
+  }
+  int last_m = 1;
+  for (int64_t i = 0; i < n;) {
+    const int m = (int)(n - i < d->B ? n - i : d->B);
+    DEC_CUDA(d, cudaMemcpyAsync(d->d_tokens, d->h_feed + i, sizeof(int32_t) * m, cudaMemcpyHostToDevice, d->stream));
+    DEC_CUDA(d, cudaMemcpyAsync(d->d_offsets, d->h_feed + n + i, sizeof(int32_t) * m, cudaMemcpyHostToDevice, d->stream));
+    d->last_batch = m;
+    d->verify_shared = m > 1;
+    const tb_status s = run_step(d, m, false);
+    d->verify_shared = false;
+    TB_TRY(s);
+    if (rows_host)
+      DEC_CUDA(d, cudaMemcpyAsync(rows_host + i * d->V, d->logits, sizeof(float) * (size_t)m * d->V, cudaMemcpyDeviceToHost, d->stream));
+    last_m = m;
+    i += m;
+  }
+  if (last_m > 1)
+    DEC_CUDA(d, cudaMemcpyAsync(d->logits, d->logits + (size_t)(last_m - 1) * d->V, sizeof(float) * d->V, cudaMemcpyDeviceToDevice, d->stream));
+  d->last_batch = 1;
+  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
+  return check_step_fault(d);
+}
+
 }  // namespace
 
 extern "C" {
@@ -698,6 +738,15 @@ tb_status tb_decoder_prefill_tokens(tb_decoder* d, const int64_t* tokens, int64_
   if (!tokens || n < 0 || start_offset < 0) return fail(TB_ERR_ARG, "tb_decoder_prefill_tokens: bad arguments");
   if (start_offset + n > d->S)
     return fail(TB_ERR_ARG, "prefill %lld tokens at offset %lld exceeds max_seq_len %lld", (long long)n, (long long)start_offset, (long long)d->S);
+  if (d->B > 1 && n > 1) {
+    // A decoder built for several rows takes max_batch positions of the prompt per step, like
+    // tb_decoder_verify_tokens: one pass over the weights for every max_batch tokens instead of one per token
+    // (the reference steps token by token, src/llm/decoder.rs:436-445; the cache rows and the last logits are
+    // the same up to the summation order of the batched products).
+    TB_TRY(run_positions(d, tokens, n, start_offset, nullptr));
+    if (end_offset) *end_offset = start_offset + n;
+    return TB_OK;
+  }
   if (n > d->feed_cap) {
     cudaFreeHost(d->h_feed);
     d->h_feed = nullptr;
@@ -740,23 +789,7 @@ tb_status tb_decoder_verify_tokens(tb_decoder* d, int64_t start_offset, const in
   // projections run as one batched product per matrix and the attention rows share sequence 0's cache
   // (causal inside the block: row r attends to [0, start + r]).  A decoder built for one row steps one
   // position at a time, like src/llm/decoder.rs:575-579.
-  for (int64_t i = 0; i < n;) {
-    const int m = (int)(n - i < d->B ? n - i : d->B);
-    int64_t offs[kMaxBatch];
-    for (int r = 0; r < m; ++r) offs[r] = start_offset + i + r;
-    d->verify_shared = m > 1;
-    const tb_status s = feed_and_step(d, tokens + i, offs, m);
-    d->verify_shared = false;
-    TB_TRY(s);
-    DEC_CUDA(d, cudaMemcpyAsync(logits_host + i * d->V, d->logits, sizeof(float) * (size_t)m * d->V, cudaMemcpyDeviceToHost, d->stream));
-    if (m > 1) {  // the decoder's own logits are those of the last position, as after sequential steps
-      DEC_CUDA(d, cudaMemcpyAsync(d->logits, d->logits + (size_t)(m - 1) * d->V, sizeof(float) * d->V, cudaMemcpyDeviceToDevice, d->stream));
-      d->last_batch = 1;
-    }
-    i += m;
-  }
-  DEC_CUDA(d, cudaStreamSynchronize(d->stream));
-  return TB_OK;
+  return run_positions(d, tokens, n, start_offset, logits_host);
 }
 
 tb_status tb_decoder_speculative_accept(tb_decoder* d, int64_t offset, const int64_t* draft_tokens, int64_t k,
