@@ -70,6 +70,19 @@ def _rank_main(rank, world, port, q, variant):
             got = dec.step_batch(tk, [off] * B)
             for b in range(B):
                 worst = max(worst, max_rel_err(got[b], refs[b].step(tk[b], off)))
+        # prompt processing and verify on the sharded decoder: B positions of sequence 0 per batched step
+        # (attention rows share the rank's part of sequence 0's cache), the last slab ragged
+        ref2 = o.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s)
+        V = cfg["vocab_size"]
+        dec.reset_kv_cache()
+        ptoks = [(13 * i + 5) % V for i in range(2 * B + 1)]
+        assert dec.prefill_tokens(ptoks, 0) == len(ptoks)
+        want = [ref2.step(t, i) for i, t in enumerate(ptoks)]
+        worst = max(worst, max_rel_err(dec.get_logits().reshape(-1)[:V], want[-1]))
+        vt = [(29 * i + 2) % V for i in range(B + 1)]
+        rows = dec.verify_tokens(len(ptoks), vt)
+        for i, t in enumerate(vt):
+            worst = max(worst, max_rel_err(rows[i], ref2.step(t, len(ptoks) + i)))
         fault = tb.lib().tb_device_fault_flag()
         q.put((rank, worst, fault, launches, greedy_ok))
         dec.close()
