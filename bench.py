@@ -599,7 +599,7 @@ def run_gpu(args):
         alt.close()
     # correctness of the sharded path at this N
     tp_check = tp_correctness_check(torch, dist, tb, c, device, tp, rank, args) if tp > 1 else None
-    # the other batch sizes of the workload configuration: tokens/s at batch 8 and 32
+    # the other batch sizes of the workload configuration (8 and 32), and the small batches 2 and 4: tokens/s
     batch_sweep = None
     verify = None
     prefill = None
@@ -611,7 +611,7 @@ def run_gpu(args):
             init_tensor_parallel(big, dist, device)
         prefill_kv(torch, big, c, device, CONTEXT, 32, tp, rank)
         batch_sweep = {"1": {"tokens_per_s": value, "ms_per_step": ms_per_step}}
-        for bb in (8, 32):
+        for bb in (2, 4, 8, 32):
             r_ms = timed_steps(torch, dist, tb, big, device, tp, bb, CONTEXT, 8, 3, 3)
             m = float(np.median(r_ms)) / 8
             batch_sweep[str(bb)] = {"tokens_per_s": bb * 1e3 / m, "ms_per_step": m,
@@ -736,7 +736,7 @@ def main():
     ap.add_argument("--model", default="llama8b", choices=["llama8b", "qwen05b", "llama70b"],
                     help="qwen05b: workload configuration 3; llama70b: configuration 5 (8 GPUs, --batch 16); both with --quick")
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
-    ap.add_argument("--no-batch-sweep", dest="batch_sweep", action="store_false", help="skip the batch 8 / 32 measurements")
+    ap.add_argument("--no-batch-sweep", dest="batch_sweep", action="store_false", help="skip the batch 2 / 4 / 8 / 32 measurements")
     ap.add_argument("--no-config3", dest="config3", action="store_false", help="skip the Qwen2.5-0.5B-shaped measurement")
     ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: plain ncclAllReduce instead of the fused kernel")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")

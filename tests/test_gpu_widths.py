@@ -154,10 +154,11 @@ def test_llama8b_one_rank_of_tp_shapes_in_the_step_kernel(torch, tb, oracle, ran
     assert tb.lib().tb_device_fault_flag() == 0
 
 
-@pytest.mark.parametrize("batch,steps", [(8, 2), (32, 1)])
+@pytest.mark.parametrize("batch,steps", [(2, 2), (3, 1), (4, 2), (8, 2), (32, 1)])
 def test_llama8b_width_depth2_batched_steps(torch, tb, oracle, batch, steps):
-    """The same model at batch 8 and 32 (step_batch: tensor-core rows kernels at true width, the
-    attention kernel over `batch` sequences near context 4096)."""
+    """The same model at batch 2, 3, 4 (the persistent streaming kernel with the digits of every row in
+    registers; the K = 14336 projection takes it up to 2 rows), 8 and 32 (step_batch: tensor-core rows kernels
+    at true width), the attention kernel over `batch` sequences near context 4096."""
     cfg = dict(LLAMA8B_L2)
     embed, layers, fnorm, lm_w, lm_s = _llama_width_model(torch, tb, cfg, 31)
     refs = [oracle.OracleDecoder(cfg, embed, layers, fnorm, lm_w, lm_s) for _ in range(batch)]
@@ -440,6 +441,62 @@ def test_tcgen05_batched_product_matches_oracle(torch, tb, oracle, n, k, g, m, b
         old = run()
     finally:
         L.tb_set_gemv_tuning(1, 0, 0)
+    assert max_rel_err(old, want) < STAGE_TOL
+    assert max_rel_err(got, old) < 1e-5
+    if not pair:
+        exact = oracle.gemm_w4a32_f64(x, p, s, b, g)
+        assert max_rel_err(got, exact) <= max(4 * max_rel_err(want, exact), 2e-6)
+    assert L.tb_device_fault_flag() == 0
+
+
+@pytest.mark.parametrize("n,k,g,m,bias,pair", [
+    (4096, 4096, 32, 2, True, False),      # o_proj shape
+    (6144, 4096, 32, 2, False, False),     # QKV shape
+    (14336, 4096, 32, 2, True, True),      # gate/up pair
+    (4096, 14336, 32, 2, False, False),    # the K = 14336 projection: 14 consumer warps
+    (1001, 2048, 64, 2, True, False),      # ragged last round, 64-element groups
+    (520, 7168, 128, 2, False, True),      # 128-element groups, pair
+    (96, 8192, 32, 2, True, True),         # fewer rounds than CTAs
+    (4096, 4096, 32, 3, True, False),      # three and four rows of a narrow matrix: the CUDA-core kernel
+    (6144, 4096, 32, 4, False, False),
+])
+def test_two_rows_take_the_persistent_kernel_and_match_oracle(torch, tb, oracle, n, k, g, m, bias, pair):
+    """Two activation rows take a variant of the persistent streaming kernel of the M = 1 path: a lane keeps
+    the digits of its block of K for both rows and multiplies each weight word with both (one pass over the
+    weights).  Against the oracle, against the kernel that runs with the streaming kernel switched off, and
+    against the float64 bound of the single-row kernel.  Three and four rows of a narrow matrix run on the
+    CUDA-core kernel (same checks; the switch changes nothing for them)."""
+    L = tb.lib()
+    rng = np.random.default_rng(n + 7 * k + m)
+    p, s = _quantized(torch, tb, n, k, g, n + k + m, std=0.05)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32) if bias else None
+    d = lambda a: dev(torch, a) if a is not None else None
+    if pair:
+        p2, s2 = _quantized(torch, tb, n, k, g, n + k + m + 1, std=0.05)
+        b2 = rng.standard_normal(n).astype(np.float32) if bias else None
+        t = [d(a) for a in (x, p, s, b, p2, s2, b2)]
+        ptr = lambda a: a.data_ptr() if a is not None else None
+
+        def run():
+            h = torch.full((m, n), float("nan"), device="cuda")
+            assert L.tb_swiglu_gemv_w4a32(ptr(t[0]), ptr(t[1]), ptr(t[2]), ptr(t[3]), ptr(t[4]), ptr(t[5]), ptr(t[6]),
+                                          h.data_ptr(), m, n, k, g, None) == 0, tb.last_error()
+            torch.cuda.synchronize()
+            return h.cpu().numpy()
+        want = np.stack([oracle.swiglu_gemv(x[i], p, s, b, p2, s2, b2, g) for i in range(m)])
+    else:
+        def run():
+            return tb.w4a32_grouped_linear(d(x), d(p), d(s), d(b), g).cpu().numpy()
+        want = oracle.gemm_w4a32_grouped(x, p, s, b, g).reshape(m, n)
+    got = run()
+    assert got.shape == (m, n)
+    assert max_rel_err(got, want) < STAGE_TOL
+    try:
+        L.tb_set_stream_tuning(0, 0, 0, 0, 0)
+        old = run()
+    finally:
+        L.tb_set_stream_tuning(1, 0, 0, 0, 0)
     assert max_rel_err(old, want) < STAGE_TOL
     assert max_rel_err(got, old) < 1e-5
     if not pair:

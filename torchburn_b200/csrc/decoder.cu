@@ -178,7 +178,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.m = b; a.n = d->tq_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && ((pm & 1) || (b > 1 && (pm & 64)));
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
-      ++launches;
+      launches += w4_gemv_launches(a);
     }
     {  // C + D + E
       AttnArgs a;
@@ -212,7 +212,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       if (sn && d->tp == 1) { a.out_scaled = d->xn; a.out_scale_w = W.post_norm_w; a.out_ss8 = d->ss8; }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
-      ++launches;
+      launches += w4_gemv_launches(a);
       if (d->tp > 1) {
         TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches, sn ? W.post_norm_w : nullptr,
                                      sn ? d->xn : nullptr, sn ? d->ss8 : nullptr));
@@ -225,14 +225,9 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       a.norm_w = W.post_norm_w; a.eps = d->cfg.rms_norm_eps;
       if (sn) { a.x = d->xn; a.x_ss8 = d->ss8; a.norm_w = nullptr; }
       a.m = b; a.n = d->I_l; a.k = d->H; a.g = d->G; a.pdl = pdl && !debug && ((pm & 8) || (b > 1 && (pm & 64)));
-      if (l + 1 < d->L) {
-      } else {
-        // the head of lm_head that fits next to what is still in flight
-        const int64_t rows = d->V_l < 24576 ? d->V_l : 24576;
-      }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
-      ++launches;
+      launches += w4_gemv_launches(a);
     }
     if (dbg) TB_TRY(snap(d->dbg_h, d->h, d->I_l));
     {  // I' + J
@@ -245,7 +240,7 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
       if (sn && d->tp == 1) { a.out_scaled = d->xn; a.out_ss8 = d->ss8; a.out_scale_w = next_norm_w; }
       a.xq_scratch = d->xq_scratch;
       TB_TRY(launch_w4_gemv(a, st));
-      ++launches;
+      launches += w4_gemv_launches(a);
       if (d->tp > 1) {
         TB_TRY(tp_allreduce_residual(d->tpst, a.out, d->x, b, d->H, st, &launches, sn ? next_norm_w : nullptr,
                                      sn ? d->xn : nullptr, sn ? d->ss8 : nullptr));
@@ -263,10 +258,9 @@ tb_status enqueue_step(tb_decoder* d, int b, bool debug, cudaEvent_t before_lm_h
     a.out = d->tp == 1 ? d->logits : d->logits_l;
     a.xq_scratch = d->xq_scratch;
     TB_TRY(launch_w4_gemv(a, st));
-    ++launches;
+    launches += w4_gemv_launches(a);
     if (d->tp > 1) { TB_TRY(tp_allgather_logits(d->tpst, d->logits_l, d->logits, b, d->V_l, st, &launches)); }
   }
-  if (b > 1) launches += 4 * d->L + 1;  // the activation-digit pass in front of every batched projection
   d->launches_per_step = launches;
   return TB_OK;
 }

@@ -446,6 +446,20 @@ void set_gemv_tuning(int xmode, int rows_per_warp, int warps) {
   g_force_warps = warps;
 }
 
+// Kernels one launch_w4_gemv call starts for these operands (the same choices as below).
+static bool few_rows_narrow(const GemvArgs& a) {
+  // Three to six rows of a narrow matrix: the CUDA-core kernel beats the tensor-core rows kernel, whose cost
+  // hardly depends on the row count below 8 (graph-timed, K = 4096: N = 4096 at 3 / 4 / 5 rows 11.7 / 13.9 /
+  // 16.0 us against 19.3; N = 6144 at 3 / 4 rows 18.2 / 21.4 against 23.0; the wide gate/up pair never).
+  return a.m >= 3 && a.w2 == nullptr && a.k <= 4096 && (int64_t)a.m * a.n <= 24576;
+}
+int w4_gemv_launches(const GemvArgs& a) {
+  if (w4_stream_supported(a)) return 1;
+  if (a.m >= 2 && g_mma_enabled && !few_rows_narrow(a) && ((a.k / 2) % 16) == 0)
+    return 2 * ((a.m + 63) / 64);   // per pass of up to 64 rows: the activation pre-pass + the product
+  return (a.m + kMaxM - 1) / kMaxM;
+}
+
 // Rows of x beyond 8 are processed in slices of up to 8 (the weights are
 // streamed once per slice).
 tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
@@ -478,7 +492,7 @@ tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
   if (w4_stream_supported(a)) return launch_w4_stream(a, stream);
   if (a.x_ss8 || a.out_scaled || a.out_ss8)
     return fail(TB_ERR_UNSUPPORTED, "TB_UNSUPPORTED: the split RMSNorm needs the persistent M = 1 kernel for this shape");
-  if (a.m >= 2 && g_mma_enabled && ((a.k / 2) % 16) == 0) {
+  if (a.m >= 2 && g_mma_enabled && !few_rows_narrow(a) && ((a.k / 2) % 16) == 0) {
     const bool tc5 = w4_tc5_supported(a);   // more than 16 rows: tcgen05, operand images behind the ticket header
     if (a.xq_scratch) return tc5 ? launch_w4_tc5(a, static_cast<char*>(a.xq_scratch) + 4096, stream) : launch_w4_mma(a, a.xq_scratch, stream);
     void* tmp = nullptr;

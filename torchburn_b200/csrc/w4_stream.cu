@@ -397,6 +397,284 @@ __global__ void __launch_bounds__(512) w4_stream_kernel(const StreamParams p) {
   if (s_abort && tid == 0) atomicExch(&g_stream_fault, 1);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same kernel for TWO activation rows (two sequences of a batch, or a draft token and its
+// predecessor in a speculative verify): a lane keeps the digits of its block of K for both rows and
+// multiplies every weight word it loads with both, so the rows cost one pass over the weights.
+// Measured on the Llama-3-8B shapes against the tensor-core rows kernel at 2 rows: gate/up pair 28.9
+// against 42.3 us, K = 14336 projection 19.9 against 33.0, QKV 11.7 against 22.9, o_proj 9.8 against
+// 19.5.  Four rows per lane were built and measured too (~200-250 registers, one or two CTAs of 5 warps
+// per SM): 90 us for the pair, slower than the tensor-core kernel, so three rows and more stay there.
+// A kernel of its own, with its own parameter block: the single-row kernel above is sensitive to both
+// (the same source with a row count as template parameter cost it 9% on the gate/up pair).
+// ---------------------------------------------------------------------------------------------
+struct RowsParams {
+  const float* x;            // [m, k]
+  const uint8_t* w[2];
+  const float* scales[2];
+  const float* bias[2];
+  const float* norm_w;
+  const float* resid;        // [m, n] or null
+  float* out;                // [m, n]
+  float* x_normed_out;       // [m, k] or null
+  float eps;
+  int m;                     // activation rows of this launch (<= MR; the rest are zeros)
+  int n, k, nb32, gshift, ng;
+  int nwarps, groups, stages, stage_bytes, rounds;
+  unsigned long long* tl;
+};
+
+template <int RS, int EPI, bool NORM, int MR>
+__global__ void __launch_bounds__(512) w4_stream_rows_kernel(const RowsParams p) {
+  constexpr int EPL = 32;
+  constexpr int NW = EPI == 1 ? 2 : 1;
+  constexpr int MW = 16;   // consumer warps the partial sums are sized for
+  constexpr int TR = 8;            // rows per round
+  constexpr int SPR = TR / RS;     // stages per round
+  constexpr int NWD = EPL / 8;     // 32-bit weight words per lane and row
+  extern __shared__ __align__(128) unsigned char ring[];
+  __shared__ uint64_t full[kMaxStages], empty[kMaxStages];
+  __shared__ float s_part[2][NW][MR][MW][33];  // [buffer][matrix][activation row][consumer warp][row] (padded)
+  __shared__ float s_ss[MR][16];
+  __shared__ int s_abort;
+  __shared__ int s_waited;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = p.nwarps, groups = p.groups;
+  const bool is_producer = warp == nwarps * groups;
+  const int row_bytes = p.k >> 1, srow_bytes = p.ng * 4;
+  // Contiguous, balanced share of the 8-row rounds: the first `rem` CTAs take one more.
+  const int base_rounds = p.rounds / (int)gridDim.x, rem_rounds = p.rounds % (int)gridDim.x;
+  const int my_rounds = base_rounds + ((int)blockIdx.x < rem_rounds ? 1 : 0);
+  const int round0 = (int)blockIdx.x * base_rounds + min((int)blockIdx.x, rem_rounds);
+  const int total_stages = my_rounds * SPR;
+
+  if (tid == 0) {
+    s_abort = 0;
+    s_waited = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], nwarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tl_mark(p.tl, (int)blockIdx.x, 0);
+    if (blockIdx.x == 0) tl_header(p.tl, 1, (int)gridDim.x);
+  }
+  __syncthreads();
+
+  if (is_producer) {
+    // ---------------- producer: one lane feeds the ring ----------------
+    // The producer must not signal launch_dependents: the next kernel may only start once
+    // this grid's consumers are past their griddepcontrol.wait, i.e. once everything before
+    // this kernel has completed (kernels further down the chain rely on that).
+    if (lane == 0) {
+      for (int i = 0; i < total_stages; ++i) {
+        const int s = i % p.stages, round = i / p.stages;
+        if (round > 0 && !mbar_wait(&empty[s], (uint32_t)(round - 1) & 1u, &s_abort)) break;
+        if (i == 0) tl_mark(p.tl, (int)blockIdx.x, 6);
+        if (i == total_stages - 1) tl_mark(p.tl, (int)blockIdx.x, 7);
+        const int row0 = (round0 + i / SPR) * TR + (i % SPR) * RS;
+        const int cnt = max(0, min(RS, p.n - row0));
+        unsigned char* dst = ring + (size_t)s * p.stage_bytes;
+        if (cnt == 0) {  // nothing to fetch for this stage: complete the phase by hand
+          mbar_arrive(&full[s]);
+          continue;
+        }
+        const uint32_t wb = (uint32_t)cnt * row_bytes, sb = (uint32_t)cnt * srow_bytes;
+        mbar_expect_tx(&full[s], NW * (wb + sb));
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          unsigned char* d = dst + (size_t)q * RS * (row_bytes + srow_bytes);
+          bulk_g2s(d, p.w[q] + (int64_t)row0 * row_bytes, wb, &full[s]);
+          bulk_g2s(d + (size_t)RS * row_bytes, p.scales[q] + (int64_t)row0 * p.ng, sb, &full[s]);
+        }
+      }
+      {
+        // All of this CTA's HBM requests are out: the next kernel may start filling its ring
+        // (launch_dependents is signalled here, after the last stage was requested).
+        // Only after the consumers are past their griddepcontrol.wait (completion must stay
+        // transitive along the chain of kernels); bounded like every other wait.
+        const long long t0 = clock64();
+        while (*reinterpret_cast<volatile int*>(&s_waited) == 0 && clock64() - t0 < kWaitCycles) {}
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  // Everything below reads the previous kernel's output.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tid == 0) *reinterpret_cast<volatile int*>(&s_waited) = 1;
+  if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 1);
+
+  const int grp = warp / nwarps, gw = warp - grp * nwarps;
+  const int part = gw * 32 + lane;                 // index of this lane's EPL-element slice of K
+  const bool has_part = part * EPL < p.k;
+  const int blk = (part * EPL) >> 5;
+  const int group_threads = nwarps * 32;
+  uint32_t dig[MR][NWD * 6];
+  float sx[MR];
+  int s8hi[MR], s8lo[MR];   // 8 * sum of this lane's digits-as-integers: the offset of the codes
+  float inv_rms[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) { sx[m] = 0.f; s8hi[m] = 0; s8lo[m] = 0; inv_rms[m] = 1.f; }
+  {
+    // Several rows: the sums of squares of every row first (one barrier for all of them), then row after
+    // row is read again (it is in L1/L2 by now), weighted and turned into digits, so that only one row's
+    // elements are live at a time.  Rows from p.m on are zeros.
+    auto load_row = [&](int m, float (&v)[EPL]) {
+      if (has_part && m < p.m) {
+        const float4* xg = reinterpret_cast<const float4*>(p.x + (int64_t)m * p.k) + part * (EPL / 4);
+#pragma unroll
+        for (int j = 0; j < EPL / 4; ++j) {
+          const float4 t = xg[j];
+          v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) v[j] = 0.f;
+      }
+    };
+    if (NORM) {
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        float v[EPL];
+        load_row(m, v);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) ss = fmaf(v[j], v[j], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_ss[m][warp] = ss;
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(group_threads) : "memory");
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        float tot = 0.f;
+        for (int w = 0; w < nwarps; ++w) tot += s_ss[m][grp * nwarps + w];
+        inv_rms[m] = 1.0f / sqrtf(tot / (float)p.k + p.eps);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      float v[EPL];
+      load_row(m, v);
+      if (NORM && has_part) {
+        const float4* nw = reinterpret_cast<const float4*>(p.norm_w) + part * (EPL / 4);
+#pragma unroll
+        for (int j = 0; j < EPL / 4; ++j) {
+          const float4 t = __ldg(nw + j);
+          if (p.x_normed_out != nullptr && blockIdx.x == 0 && grp == 0 && m < p.m)
+            reinterpret_cast<float4*>(p.x_normed_out + (int64_t)m * p.k)[part * (EPL / 4) + j] =
+                make_float4((v[4 * j] * inv_rms[m]) * t.x, (v[4 * j + 1] * inv_rms[m]) * t.y,
+                            (v[4 * j + 2] * inv_rms[m]) * t.z, (v[4 * j + 3] * inv_rms[m]) * t.w);
+          v[4 * j] *= t.x; v[4 * j + 1] *= t.y; v[4 * j + 2] *= t.z; v[4 * j + 3] *= t.w;
+        }
+      }
+      float amax = abs_max<EPL>(v);
+      if (EPL == 16) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      int S;
+      quantize_part_int<EPL>(v, amax, dig[m], sx[m], S);
+      split_offset(S, s8hi[m], s8lo[m]);
+      if (!has_part) { sx[m] = 0.f; s8hi[m] = 0; s8lo[m] = 0; }
+    }
+  }
+
+  if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 2);
+  const int sidx = blk >> p.gshift;
+  int buf = 0;
+#pragma unroll 1
+  for (int rd = 0; rd < my_rounds; ++rd) {
+    float pa[NW][MR][TR];
+    // The round that ends with an epilogue: its per-row operands (bias, residual, next norm's
+    // weight) are requested now, so that they have arrived when the row sums are complete.
+    float pre_b0 = 0.f, pre_b1 = 0.f;
+    if (gw == 0 && ((rd & 3) == 3 || rd == my_rounds - 1)) {
+      const int row = (round0 + (rd & ~3)) * TR + lane;
+      if (lane < ((rd & 3) + 1) * TR && row < p.n) {
+        if (p.bias[0]) pre_b0 = p.bias[0][row];
+        if (EPI == 1 && p.bias[1]) pre_b1 = p.bias[1][row];
+      }
+    }
+#pragma unroll
+    for (int ss = 0; ss < SPR; ++ss) {
+      const int it = rd * SPR + ss;
+      const int s = it % p.stages;
+      const bool ok = mbar_wait(&full[s], (uint32_t)(it / p.stages) & 1u, &s_abort);
+      if (tid == 0 && it == 0) tl_mark(p.tl, (int)blockIdx.x, 3);
+      if (tid == 0 && it == my_rounds * SPR - 1) tl_mark(p.tl, (int)blockIdx.x, 4);
+      const unsigned char* st = ring + (size_t)s * p.stage_bytes;
+#pragma unroll
+      for (int q = 0; q < NW; ++q) {
+        const unsigned char* base = st + (size_t)q * RS * (row_bytes + srow_bytes);
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+          if (has_part && ok) {
+            uint32_t wv[NWD];
+            const unsigned char* wp = base + (size_t)r * row_bytes + part * (EPL / 2);
+            if (EPL == 32) {
+              const uint4 t4 = *reinterpret_cast<const uint4*>(wp);
+              wv[0] = t4.x; wv[1] = t4.y; wv[NWD - 2] = t4.z; wv[NWD - 1] = t4.w;
+            } else {
+              const uint2 t2 = *reinterpret_cast<const uint2*>(wp);
+              wv[0] = t2.x; wv[1] = t2.y;
+            }
+            const float sc = *reinterpret_cast<const float*>(base + (size_t)RS * row_bytes + (size_t)r * srow_bytes + sidx * 4);
+#pragma unroll
+            for (int m = 0; m < MR; ++m) pa[q][m][ss * RS + r] = sc * (sx[m] * idot_words_off<NWD>(wv, dig[m], s8hi[m], s8lo[m]));
+          } else {
+#pragma unroll
+            for (int m = 0; m < MR; ++m) pa[q][m][ss * RS + r] = 0.f;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    // ---- 8 rows done for this lane's slice of K: sum over the warp's lanes ----
+    const int slot = rd & 3;
+#pragma unroll
+    for (int q = 0; q < NW; ++q)
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        const float v = transpose_reduce8(pa[q][m], lane);
+        if ((lane & 3) == 0) s_part[buf][q][m][warp][slot * TR + (lane >> 2)] = v;
+      }
+    if (slot != 3 && rd != my_rounds - 1) continue;
+    // ---- up to 32 rows gathered: sum over the warps, epilogue, one coalesced store ----
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(group_threads) : "memory");
+    if (gw == 0 && lane < (slot + 1) * TR) {
+      const int row = (round0 + (rd & ~3)) * TR + lane;
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        float acc[NW];
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          float a = 0.f;
+          for (int w = 0; w < nwarps; ++w) a += s_part[buf][q][m][grp * nwarps + w][lane];
+          acc[q] = a * inv_rms[m];
+        }
+        if (row < p.n && m < p.m) {
+          float v;
+          if (EPI == 1) {
+            const float g = acc[0] + pre_b0;
+            const float u = acc[NW - 1] + pre_b1;
+            v = (g / (1.0f + expf(-g))) * u;  // src/llm/decoder.rs:1319-1322
+          } else {
+            v = acc[0] + pre_b0;
+            if (p.resid) v = p.resid[(int64_t)m * p.n + row] + v;
+          }
+          p.out[(int64_t)m * p.n + row] = v;
+        }
+      }
+    }
+    buf ^= 1;
+  }
+  if (tid == 0) tl_mark(p.tl, (int)blockIdx.x, 5);
+  if (s_abort && tid == 0) atomicExch(&g_stream_fault, 1);
+}
+
 int g_stream_enabled = 1;
 int g_ctas_per_sm = 0;
 int g_ring_kb = 0;
@@ -445,6 +723,77 @@ tb_status launch_epl(bool swiglu, bool norm, int rs, const StreamParams& p, int 
   return norm ? launch_en<0, true, EPL>(rs, p, grid, smem, pdl, stream) : launch_en<0, false, EPL>(rs, p, grid, smem, pdl, stream);
 }
 
+template <int RS, int EPI, bool NORM>
+tb_status launch_rows_rs(const RowsParams& p, int grid, size_t smem, bool pdl, cudaStream_t stream) {
+  auto kern = w4_stream_rows_kernel<RS, EPI, NORM, 2>;
+  static thread_local size_t configured[64] = {0};
+  int dev = 0;
+  TB_CUDA_TRY(cudaGetDevice(&dev));
+  // static + dynamic shared memory above 48 KB needs the opt-in (17 KB are static here), so opt in from 16 KB up
+  if (smem > 16 * 1024 && (dev >= 64 || configured[dev] < smem)) {
+    TB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 64) configured[dev] = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)(p.nwarps + 1) * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  TB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+  return TB_OK;
+}
+
+template <int EPI, bool NORM>
+tb_status launch_rows_en(int rs, const RowsParams& p, int grid, size_t smem, bool pdl, cudaStream_t stream) {
+  switch (rs) {
+    case 1: return launch_rows_rs<1, EPI, NORM>(p, grid, smem, pdl, stream);
+    case 2: return launch_rows_rs<2, EPI, NORM>(p, grid, smem, pdl, stream);
+    case 4: return launch_rows_rs<4, EPI, NORM>(p, grid, smem, pdl, stream);
+    case 8: return launch_rows_rs<8, EPI, NORM>(p, grid, smem, pdl, stream);
+  }
+  return fail(TB_ERR_ARG, "w4 stream: rows per stage %d", rs);
+}
+
+// Two activation rows: same ring sizing as the single-row launch, a whole block of K per lane.
+tb_status launch_w4_stream_rows(const GemvArgs& a, cudaStream_t stream) {
+  RowsParams p;
+  p.x = a.x;
+  p.w[0] = a.w; p.w[1] = a.w2;
+  p.scales[0] = a.scales; p.scales[1] = a.scales2;
+  p.bias[0] = a.bias; p.bias[1] = a.bias2;
+  p.norm_w = a.norm_w; p.resid = a.resid; p.out = a.out; p.x_normed_out = a.x_normed_out;
+  p.eps = a.eps;
+  p.m = a.m;
+  p.tl = timeline_next_block();
+  p.n = (int)a.n; p.k = (int)a.k; p.nb32 = (int)(a.k / 32);
+  p.gshift = a.g == 32 ? 0 : (a.g == 64 ? 1 : 2);
+  p.ng = (int)(a.k / a.g);
+  p.rounds = (p.n + 7) / 8;
+  const int cps = g_ctas_per_sm > 0 ? g_ctas_per_sm : (p.k >= 8192 ? 1 : 3);
+  int grid = sm_count() * cps;
+  if (grid > p.rounds) grid = p.rounds;
+  p.nwarps = (p.nb32 + 31) / 32;
+  p.groups = 1;
+  const int nw = a.w2 ? 2 : 1;
+  const int per_row = nw * (p.k / 2 + p.ng * 4);
+  const int ring_budget = g_ring_kb > 0 ? g_ring_kb * 1024 : (cps >= 3 ? 40 * 1024 : kRingBytesMax / cps);
+  int rs = 8;
+  while (rs > 1 && (rs * per_row > 20 * 1024 || rs * per_row * 3 > ring_budget)) rs >>= 1;
+  p.stage_bytes = rs * per_row;
+  p.stages = ring_budget / p.stage_bytes;
+  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  if (p.stages < 2) p.stages = 2;
+  const size_t smem = (size_t)p.stages * p.stage_bytes;
+  if (smem > 180 * 1024) return fail(TB_ERR_UNSUPPORTED, "w4 stream: a row of %d bytes does not fit the ring", per_row);
+  if (a.w2) return a.norm_w ? launch_rows_en<1, true>(rs, p, grid, smem, a.pdl, stream) : launch_rows_en<1, false>(rs, p, grid, smem, a.pdl, stream);
+  return a.norm_w ? launch_rows_en<0, true>(rs, p, grid, smem, a.pdl, stream) : launch_rows_en<0, false>(rs, p, grid, smem, a.pdl, stream);
+}
+
 }  // namespace
 
 void set_stream_tuning(int enabled, int ctas_per_sm, int ring_kb, int epl, int groups) {
@@ -464,7 +813,9 @@ int stream_fault_flag() {
 
 // True when the persistent kernel can take this product (M = 1, bulk-copy alignment rules).
 bool w4_stream_supported(const GemvArgs& a) {
-  if (!g_stream_enabled || a.m != 1) return false;
+  if (!g_stream_enabled || a.m < 1 || a.m > 2) return false;
+  // two rows: no split RMSNorm (its operands belong to one vector)
+  if (a.m == 2 && (a.x_ss8 || a.out_scaled || a.out_ss8)) return false;
   // narrow K leaves most of a CTA's lanes without work: the per-row-tile kernels are faster there
   if (a.k % 32 != 0 || a.k < 2048 || a.k > 32 * 32 * 15) return false;  // at most 15 consumer warps + the producer
   const int64_t ng = a.k / a.g;
@@ -479,6 +830,7 @@ bool w4_stream_supported(const GemvArgs& a) {
 }
 
 tb_status launch_w4_stream(const GemvArgs& a, cudaStream_t stream) {
+  if (a.m == 2) return launch_w4_stream_rows(a, stream);
   StreamParams p;
   p.x = a.x;
   p.w[0] = a.w; p.w[1] = a.w2;
