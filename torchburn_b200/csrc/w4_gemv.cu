@@ -448,10 +448,12 @@ void set_gemv_tuning(int xmode, int rows_per_warp, int warps) {
 
 // Kernels one launch_w4_gemv call starts for these operands (the same choices as below).
 static bool few_rows_narrow(const GemvArgs& a) {
-  // Three to six rows of a narrow matrix: the CUDA-core kernel beats the tensor-core rows kernel, whose cost
+  // Three or four rows of a narrow matrix: the CUDA-core kernel beats the tensor-core rows kernel, whose cost
   // hardly depends on the row count below 8 (graph-timed, K = 4096: N = 4096 at 3 / 4 / 5 rows 11.7 / 13.9 /
   // 16.0 us against 19.3; N = 6144 at 3 / 4 rows 18.2 / 21.4 against 23.0; the wide gate/up pair never).
-  return a.m >= 3 && a.w2 == nullptr && a.k <= 4096 && (int64_t)a.m * a.n <= 24576;
+  // Every CTA of that kernel prepares all rows of x itself (with a fused RMSNorm: twice over them), so it is
+  // kept to four rows, three with the norm.
+  return a.m >= 3 && a.m <= (a.norm_w ? 3 : 4) && a.w2 == nullptr && a.k <= 4096 && (int64_t)a.m * a.n <= 24576;
 }
 int w4_gemv_launches(const GemvArgs& a) {
   if (w4_stream_supported(a)) return 1;
