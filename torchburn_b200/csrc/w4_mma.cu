@@ -370,11 +370,13 @@ tb_status launch_rows_mt(const MmaParams& p, cudaStream_t stream) {
   // Up to 16 activation rows (MT <= 2), graph-timed on the Llama-3-8B shapes at 8 / 16 rows: CTAs of 64 weight
   // rows with 8 warps (4 side by side, K of a stage split in two) against CTAs of 32 rows with 4 warps: gate/up
   // pair 42.7 / 61.9 us against 46.5 / 71.8; the K = 14336 projection 33.2 (K split over 4 CTAs) / 44.0 against
-  // 40.1 / 49.4.  The narrow K = 4096 projections at 8 rows stay with 32-row CTAs of 8 warps (19.7 against 24.8 us).
+  // 40.1 / 49.4.  Only where 64-row CTAs still cover every SM: the narrow projections and the shards of a
+  // tensor-parallel rank stay with 32-row CTAs of 8 warps (N = 4096, K = 4096 at 8 rows: 19.7 against 24.8 us).
   // A fourth stage, stages of 128 elements of K and CTAs of 16 or 128 rows were measured too: none is faster.
   // More than 16 rows (reached only with the tcgen05 kernel switched off): the digit traffic decides.
   if (MT <= 2) {
-    if (MT == 2 || per_sm >= 64 || p.ksplit > 1) return launch_rows_cfg<MT, 4, 2, EPI, KC>(p, stream);
+    const int ctas64 = ((p.n + 63) / 64) * (EPI == 0 && p.ksplit > 1 ? p.ksplit : 1);
+    if (ctas64 >= sm_count()) return launch_rows_cfg<MT, 4, 2, EPI, KC>(p, stream);
     return launch_rows_cfg<MT, 2, 4, EPI, KC>(p, stream);
   }
   if (MT != 4 && per_sm >= 64) return launch_rows_cfg<MT, 2, 2, EPI, KC>(p, stream);
