@@ -207,6 +207,12 @@ void tb_set_gemv_tuning(int32_t product_mode, int32_t rows_per_warp, int32_t war
  * the number of tiles a CTA works on at once (0 = choose from the shape). */
 void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb,
                           int32_t elements_per_lane, int32_t groups);
+/* The stateless products (tb_gemm_w4a32_grouped, tb_swiglu_gemv_w4a32, tb_linear_forward, ...) with two or more
+ * activation rows need a workspace (digit form of x, partial sums of a K split).  The library keeps one block
+ * per (device, stream), allocated at the first such call on the stream outside a graph capture and grown on
+ * demand - the reference allocates its outputs per call too (src/quantization/packed_v2.rs:598-606).  This frees
+ * all of them (after a device synchronize); later calls allocate again. */
+void tb_release_workspaces(void);
 /* 1 after a bounded device-side wait ran out in any kernel of this library on the current
  * device (the results of that launch are invalid), 0 otherwise, -1 if the flag could not
  * be read.  Device-side waits never spin without a limit. */

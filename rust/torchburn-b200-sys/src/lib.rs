@@ -150,6 +150,7 @@ extern "C" {
     pub fn tb_set_attention_tuning(ctas_per_sm: i32, ring_stages: i32);
     pub fn tb_set_gemv_tuning(product_mode: i32, rows_per_warp: i32, warps: i32);
     pub fn tb_set_stream_tuning(enabled: i32, ctas_per_sm: i32, ring_kb: i32, elements_per_lane: i32, groups: i32);
+    pub fn tb_release_workspaces();
     pub fn tb_device_fault_flag() -> i32;
     pub fn tb_linear_create(out: *mut *mut tb_linear, qweight: *const u8, scales: *const f32, bias: *const f32, out_features: i64, in_features: i64, group_size: i32, weight_space: tb_space) -> tb_status;
     pub fn tb_linear_destroy(lin: *mut tb_linear);

@@ -505,6 +505,49 @@ def test_two_rows_take_the_persistent_kernel_and_match_oracle(torch, tb, oracle,
     assert L.tb_device_fault_flag() == 0
 
 
+def test_products_with_several_rows_keep_a_workspace_per_stream(torch, tb, oracle):
+    """Stateless products with two or more rows keep their workspace per (device, stream): a second call reuses
+    it, a wider K grows it, another stream gets its own, tb_release_workspaces frees them and the next call
+    allocates again.  Results stay those of the oracle throughout, also when calls are captured into a graph."""
+    L = tb.lib()
+    rng = np.random.default_rng(5)
+    g = 32
+    cases = []
+    for n, k, m in ((256, 1024, 8), (192, 4096, 12), (256, 1024, 40)):
+        p, s = _quantized(torch, tb, n, k, g, n + k + m, std=0.05)
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        cases.append((dev(torch, x), dev(torch, p), dev(torch, s), oracle.gemm_w4a32_grouped(x, p, s, None, g).reshape(m, n), m, n, k))
+
+    def check(stream=None):
+        for x, p, s, want, m, n, k in cases:
+            y = torch.full((m, n), float("nan"), device="cuda")
+            st = stream.cuda_stream if stream is not None else None
+            assert L.tb_gemm_w4a32_grouped(x.data_ptr(), p.data_ptr(), s.data_ptr(), None, y.data_ptr(), m, n, k, g, st) == 0, tb.last_error()
+            (stream.synchronize() if stream is not None else torch.cuda.synchronize())
+            assert max_rel_err(y.cpu().numpy(), want) < STAGE_TOL
+
+    check()
+    check()
+    side = torch.cuda.Stream()
+    check(side)
+    # captured: the block of the stream exists already, so the graph holds kernels only
+    x, p, s, want, m, n, k = cases[1]
+    y = torch.zeros((m, n), device="cuda")
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        assert L.tb_gemm_w4a32_grouped(x.data_ptr(), p.data_ptr(), s.data_ptr(), None, y.data_ptr(), m, n, k, g,
+                                       torch.cuda.current_stream().cuda_stream) == 0, tb.last_error()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert max_rel_err(y.cpu().numpy(), want) < STAGE_TOL
+    del graph
+    L.tb_release_workspaces()
+    check()
+    check(side)
+    L.tb_release_workspaces()
+    assert L.tb_device_fault_flag() == 0
+
+
 def test_bounded_device_wait_runs_out_and_reports_timeout(torch, tb):
     """Failure detection without a fault: a wait of the step kernel on a barrier that nothing
     completes, with a limit of a millisecond.  The kernel must return, raise the fault word and

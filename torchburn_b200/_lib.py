@@ -74,6 +74,7 @@ SIGNATURES = {
     "tb_set_attention_tuning": (None, [_i32, _i32]),
     "tb_set_gemv_tuning": (None, [_i32, _i32, _i32]),
     "tb_set_stream_tuning": (None, [_i32, _i32, _i32, _i32, _i32]),
+    "tb_release_workspaces": (None, []),
     "tb_device_fault_flag": (_i32, []),
     "tb_linear_create": (_i32, [_PP, _p, _p, _p, _i64, _i64, _i32, _i32]),
     "tb_f32_to_f16": (C.c_uint16, [_f32]),

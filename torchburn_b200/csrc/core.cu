@@ -232,6 +232,8 @@ void tb_set_attention_tuning(int32_t ctas_per_sm, int32_t ring_stages) {
 
 void tb_set_gemv_tuning(int32_t xmode, int32_t rows_per_warp, int32_t warps) { set_gemv_tuning(xmode, rows_per_warp, warps); }
 
+void tb_release_workspaces(void) { release_workspaces(); }
+
 void tb_set_stream_tuning(int32_t enabled, int32_t ctas_per_sm, int32_t ring_kb, int32_t epl, int32_t groups) {
   set_stream_tuning(enabled, ctas_per_sm, ring_kb, epl, groups);
 }

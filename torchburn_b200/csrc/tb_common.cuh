@@ -100,6 +100,8 @@ struct GemvArgs {
 tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream);
 // Kernels that call starts (1, or 2 with the activation pre-pass of the tensor-core kernels).
 int w4_gemv_launches(const GemvArgs& a);
+// Frees the per-stream workspaces that calls with several activation rows and no workspace of their own keep.
+void release_workspaces();
 // Tuning hook: xmode 0 = fp32 products (M = 1 only), 1 = integer products; rows_per_warp /
 // warps force the launch shape of the M = 1 kernels (0 = automatic).
 void set_gemv_tuning(int xmode, int rows_per_warp, int warps);

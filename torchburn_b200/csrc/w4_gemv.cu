@@ -21,6 +21,9 @@
 // was pre-multiplied by 16^-p when it was staged in shared memory.  All of
 // these scalings are by powers of two, so every product is the bit-exact
 // fp32 product x * (code4 - 8) the reference computes.
+#include <mutex>
+#include <vector>
+
 #include "tb_common.cuh"
 #include "w4_math.cuh"
 
@@ -446,6 +449,60 @@ void set_gemv_tuning(int xmode, int rows_per_warp, int warps) {
   g_force_warps = warps;
 }
 
+// Workspace of the products with several activation rows (digit form of x, partial sums and tickets of the K
+// split) for callers that bring none: one block per (device, stream), kept between calls and grown when a call
+// needs more.  Calls on one stream are ordered, so they can share it; calls on different streams get different
+// blocks.  Without it every call would allocate, clear and free stream-ordered memory - three extra nodes when
+// the calls are captured into a CUDA graph.  Nothing is allocated while the stream is being captured: a call
+// that then finds no block large enough takes stream-ordered memory for its own duration, as before.
+namespace {
+struct Workspace { int dev; cudaStream_t stream; void* ptr; size_t bytes; };
+std::mutex g_ws_mu;
+std::vector<Workspace> g_ws;
+
+void* workspace_for(cudaStream_t stream, size_t bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  std::lock_guard<std::mutex> lock(g_ws_mu);
+  Workspace* e = nullptr;
+  for (Workspace& w : g_ws)
+    if (w.dev == dev && w.stream == stream) { e = &w; break; }
+  if (e && e->bytes >= bytes) return e->ptr;
+  if (cap != cudaStreamCaptureStatusNone) return nullptr;
+  if (e) {  // grow: earlier calls on the stream may still use the old block
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return nullptr;
+    cudaFree(e->ptr);
+    e->ptr = nullptr;
+    e->bytes = 0;
+  } else {
+    g_ws.push_back(Workspace{dev, stream, nullptr, 0});
+    e = &g_ws.back();
+  }
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (cudaMemsetAsync(p, 0, 4096, stream) != cudaSuccess) { cudaGetLastError(); cudaFree(p); return nullptr; }  // the tickets start at zero; every launch leaves them zero
+  e->ptr = p;
+  e->bytes = bytes;
+  return p;
+}
+}  // namespace
+
+void release_workspaces() {
+  std::lock_guard<std::mutex> lock(g_ws_mu);
+  int cur = 0;
+  cudaGetDevice(&cur);
+  for (Workspace& w : g_ws) {
+    if (!w.ptr) continue;
+    cudaSetDevice(w.dev);
+    cudaDeviceSynchronize();
+    cudaFree(w.ptr);
+  }
+  g_ws.clear();
+  cudaSetDevice(cur);
+}
+
 // Kernels one launch_w4_gemv call starts for these operands (the same choices as below).
 static bool few_rows_narrow(const GemvArgs& a) {
   // Three or four rows of a narrow matrix: the CUDA-core kernel beats the tensor-core rows kernel, whose cost
@@ -497,8 +554,10 @@ tb_status launch_w4_gemv(const GemvArgs& a, cudaStream_t stream) {
   if (a.m >= 2 && g_mma_enabled && !few_rows_narrow(a) && ((a.k / 2) % 16) == 0) {
     const bool tc5 = w4_tc5_supported(a);   // more than 16 rows: tcgen05, operand images behind the ticket header
     if (a.xq_scratch) return tc5 ? launch_w4_tc5(a, static_cast<char*>(a.xq_scratch) + 4096, stream) : launch_w4_mma(a, a.xq_scratch, stream);
+    const size_t need = w4_mma_scratch_bytes(a.m < 64 ? a.m : 64, a.k);
+    if (void* ws = workspace_for(stream, need)) return tc5 ? launch_w4_tc5(a, static_cast<char*>(ws) + 4096, stream) : launch_w4_mma(a, ws, stream);
     void* tmp = nullptr;
-    TB_CUDA_TRY(cudaMallocAsync(&tmp, w4_mma_scratch_bytes(a.m < 64 ? a.m : 64, a.k), stream));
+    TB_CUDA_TRY(cudaMallocAsync(&tmp, need, stream));
     TB_CUDA_TRY(cudaMemsetAsync(tmp, 0, 4096, stream));  // the tickets of the K split
     const tb_status s = tc5 ? launch_w4_tc5(a, static_cast<char*>(tmp) + 4096, stream) : launch_w4_mma(a, tmp, stream);
     cudaFreeAsync(tmp, stream);
